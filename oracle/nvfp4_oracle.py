@@ -1,0 +1,408 @@
+"""CPU oracle for the NVFP4 linear-layer hot path.  TEST INFRASTRUCTURE ONLY.
+
+This file restates, in plain numpy float32/uint arithmetic, the algorithm of the reference
+(Not4right/nvfp4-training).  It is the checker the CUDA library is compared with; the product
+never imports it.  Only the test-suite, the smoke check and the benchmark's CPU-baseline leg
+may call it.
+
+Parity status: PINNED.  `tests/test_oracle_golden.py` checks every quantizer here bit-for-bit
+against fixtures produced by importing the reference's own torch fake-quant
+(`small-model/model_ref.py`: `nvfp4_1d`, `nvfp4_2d`, `fp4_round`, `e4m3`, `hadamard16`) with
+`tests/golden/make_golden.py`; the E4M3 coder is also checked against `torch.float8_e4m3fn`
+over every float16-representable magnitude, and the E2M1 rounder against all 2^16 bf16 patterns
+of `model_ref.fp4_round`.
+
+Conventions shared with the CUDA library
+  * codes: E2M1, two per byte, low nibble = lower index (llm-1b/nvq.cu:2)
+  * block scale: one unsigned E4M3 byte per 16 values along the contraction dim
+  * tensor scale: gs = amax / 2688 (2688 = 6 * 448), FP32, division (small-model/model_ref.py:42)
+  * `y = (x / gs) / max(bs, 1e-30)` -- the division order of model_ref.nvfp4_1d
+    (small-model/model_ref.py:43-46); the reference kernels use the algebraically equal
+    `x * (2688/amax / bs)` (llm-1b/nvq.cu:47-54), which is not bit-identical in general.
+  * a block whose scale byte is 0 stores code 0 with the sign of x (llm-1b/nvq.cu:50: k = 0);
+    model_ref dequantizes such a block to 0 as well, so dequantized values always agree.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+FP4_MAX = np.float32(6.0)
+E4M3_MAX = np.float32(448.0)
+FP4_E4M3 = np.float32(2688.0)          # 6 * 448  (llm-1b/nvq.cu:11)
+TINY = np.float32(1e-30)               # clamp used by model_ref.py:42,45
+
+# value of each 4-bit code (llm-1b/nvq.py:100, llm-1b/fp4ops.py:84)
+E2M1_TABLE = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
+
+SR_NONE = 0        # round to nearest even
+SR_DITHER_NVQ = 1  # mantissa-dither SR, random stream of llm-1b/nvq.cu:43-63
+SR_DITHER_FP4K = 2  # mantissa-dither SR, random stream of llm-1b/fp4k.cu:43-63
+SR_HW = 3          # cvt.rs.satfinite.e2m1x4.f32 of sm_100a, counter-based stream of this library
+
+
+# ----------------------------------------------------------------------------- bit helpers
+def f2u(x):
+    return np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+
+
+def u2f(b):
+    return np.ascontiguousarray(b, dtype=np.uint32).view(np.float32)
+
+
+def bf16_bits_to_f32(bits_u16):
+    """uint16 bf16 bit patterns -> float32 values (exact)."""
+    return (np.asarray(bits_u16, dtype=np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def f32_to_bf16_bits(x):
+    """float32 -> bf16 bit patterns, round to nearest even (what torch .bfloat16() does)."""
+    b = f2u(x).astype(np.uint64)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    nan = np.isnan(np.asarray(x, dtype=np.float32))
+    return np.where(nan, np.uint16(0x7FC0), r)
+
+
+def hash32(x):
+    """32-bit mixer of llm-1b/nvq.cu:13-15 (identical in llm-1b/fp4k.cu:10-12)."""
+    x = np.asarray(x, dtype=np.uint32).copy()
+    x ^= x >> np.uint32(16)
+    x *= np.uint32(0x7FEB352D)
+    x ^= x >> np.uint32(15)
+    x *= np.uint32(0x846CA68B)
+    x ^= x >> np.uint32(16)
+    return x
+
+
+# ----------------------------------------------------------------------------- E4M3 / E2M1 coders
+def _build_e4m3_table():
+    t = np.zeros(256, dtype=np.float32)
+    for b in range(256):
+        e, m = (b >> 3) & 15, b & 7
+        if e == 0:
+            v = m * 2.0 ** -9
+        elif e == 15 and m == 7:
+            v = np.nan
+        else:
+            v = (1 + m / 8.0) * 2.0 ** (e - 7)
+        t[b] = -v if b & 0x80 else v
+    return t
+
+
+E4M3_TABLE = _build_e4m3_table()
+
+
+def e4m3_encode(v):
+    """Non-negative float32 -> E4M3 byte, round to nearest even, clamped to 448.
+
+    Follows `e4m3()` of small-model/model_ref.py:35-36 (clamp, then the IEEE-style cast) and the
+    hardware `cvt.rn.satfinite.e4m3x2.f32` used by llm-1b/nvq.cu:16-20.
+    """
+    v = np.minimum(np.asarray(v, dtype=np.float32), E4M3_MAX)
+    b = f2u(v).astype(np.uint64)
+    # normal range: keep 3 mantissa bits, RN-even on the integer representation
+    r = (b + 0x7FFFF + ((b >> 20) & 1)) >> 20
+    normal = r.astype(np.int64) - ((127 - 7) << 3)
+    # subnormal range (< 2^-6): multiples of 2^-9; v*512 is exact, rint is RN-even
+    sub = np.rint(v.astype(np.float64) * 512.0).astype(np.int64)
+    out = np.where(v < np.float32(2.0 ** -6), sub, normal)
+    return np.clip(out, 0, 0x7E).astype(np.uint8)
+
+
+def e4m3_decode(b):
+    return E4M3_TABLE[np.asarray(b, dtype=np.uint8)]
+
+
+_E2M1_BOUNDS = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+# a tie at bound j goes to the even code index: up when the lower index j is odd
+_TIE_UP = np.array([False, True, False, True, False, True, False])
+
+
+def e2m1_rn_code(y):
+    """float32 -> 4-bit E2M1 code, round to nearest even, saturating at 6, sign kept on zero.
+
+    Same grid and tie rule as `fp4_round` (small-model/model_ref.py:19-32) and the hardware
+    `cvt.rn.satfinite.e2m1x2.f32` (llm-1b/nvq.cu:26-30).
+    """
+    y = np.asarray(y, dtype=np.float32)
+    a = np.abs(y)
+    idx = np.zeros(a.shape, dtype=np.uint8)
+    for j in range(7):
+        idx += ((a > _E2M1_BOUNDS[j]) | ((a == _E2M1_BOUNDS[j]) & _TIE_UP[j])).astype(np.uint8)
+    return idx | (np.signbit(y).astype(np.uint8) << 3)
+
+
+def sr_dither(v, rnd):
+    """`sr_fp4` of llm-1b/nvq.cu:32-39: stochastic rounding onto the E2M1 grid by adding 22
+    random bits below the kept mantissa bit and truncating.  Returns a value on the grid."""
+    v = np.asarray(v, dtype=np.float32)
+    rnd = np.asarray(rnd, dtype=np.uint32)
+    a = np.minimum(np.abs(v), FP4_MAX)
+    sub = a < np.float32(1.0)
+    b = np.where(sub, a + np.float32(1.0), a).astype(np.float32)
+    bits = (f2u(b) + (rnd & np.uint32(0x3FFFFF))) & np.uint32(0xFFC00000)
+    r = u2f(bits) - np.where(sub, np.float32(1.0), np.float32(0.0)).astype(np.float32)
+    return np.copysign(np.minimum(r, FP4_MAX), v).astype(np.float32)
+
+
+def sr_hw_code(y, rb8):
+    """Model of `cvt.rs.satfinite.e2m1x4.f32` for one element: y float32, rb8 the element's 8
+    random bits.  Sign-magnitude: the 8 bits are added below the last kept magnitude bit and the
+    sum is truncated toward zero; magnitudes of 6 and above saturate to 6.
+
+    In fixed point with 8 fraction bits per grid step: up iff frac8 + rb8 >= 256, where frac8 is
+    the top 8 bits of the part of |y| below the grid point (bits further down are ignored).
+    Fitted to, and checked bit-for-bit against, the instruction on a B200 (tests/test_sr.py).
+    """
+    y = np.asarray(y, dtype=np.float32)
+    rb8 = np.asarray(rb8, dtype=np.uint32) & np.uint32(0xFF)
+    a = np.abs(y).astype(np.float64)
+    a = np.where(np.isnan(a), 6.0, a)
+    step = np.where(a < 2, 0.5, np.where(a < 4, 1.0, 2.0))
+    lo = np.floor(a / step) * step
+    frac8 = np.floor((a - lo) / step * 256.0).astype(np.int64)     # exact: a has 24 bits
+    up = (frac8 + rb8.astype(np.int64)) >= 256
+    q = np.minimum(np.where(up, lo + step, lo), 6.0).astype(np.float32)
+    q = np.where(a >= 6.0, np.float32(6.0), q)
+    return e2m1_rn_code(np.copysign(q, y))
+
+
+# ----------------------------------------------------------------------------- random streams
+def sr_bits_nvq(seed, blk_idx):
+    """22-bit dither words for the 16 elements of blocks `blk_idx` (llm-1b/nvq.cu:52-59):
+    h = hash32(seed ^ hash32(idx)); pair i: h1 = hash32(h + i); element i takes h1,
+    element i+1 takes h1 rotated right by 10."""
+    blk_idx = np.asarray(blk_idx, dtype=np.uint32)
+    h = hash32(np.uint32(seed & 0xFFFFFFFF) ^ hash32(blk_idx))
+    out = np.empty(blk_idx.shape + (16,), dtype=np.uint32)
+    for i in range(0, 16, 2):
+        h1 = hash32(h + np.uint32(i))
+        out[..., i] = h1
+        out[..., i + 1] = (h1 >> np.uint32(10)) | (h1 << np.uint32(22))
+    return out
+
+
+def sr_bits_fp4k(seed, elt_idx):
+    """Dither words of llm-1b/fp4k.cu:53-58: h = hash32(seed ^ (idx + i) * 0x9E3779B9) with idx
+    the element index of the block start; element i+1 takes h rotated right by 10."""
+    elt_idx = np.asarray(elt_idx, dtype=np.uint32)
+    out = np.empty(elt_idx.shape + (16,), dtype=np.uint32)
+    for i in range(0, 16, 2):
+        h = hash32(np.uint32(seed & 0xFFFFFFFF) ^ ((elt_idx + np.uint32(i)) * np.uint32(0x9E3779B9)))
+        out[..., i] = h
+        out[..., i + 1] = (h >> np.uint32(10)) | (h << np.uint32(22))
+    return out
+
+
+def sr_bits_hw(seed, blk_idx):
+    """Counter-based stream of this library for the hardware-SR mode: one 32-bit word per group of
+    four elements, hb = hash32(seed ^ hash32(blk)); word g = hash32(hb + 0x9E3779B9 * (g + 1)).
+    Element j of the group takes byte j (bits 8j..8j+7).  Returns [..., 16] bytes as uint32."""
+    blk_idx = np.asarray(blk_idx, dtype=np.uint32)
+    hb = hash32(np.uint32(seed & 0xFFFFFFFF) ^ hash32(blk_idx))
+    out = np.empty(blk_idx.shape + (16,), dtype=np.uint32)
+    for g in range(4):
+        w = hash32(hb + np.uint32((0x9E3779B9 * (g + 1)) & 0xFFFFFFFF))
+        for j in range(4):
+            out[..., 4 * g + j] = (w >> np.uint32(8 * j)) & np.uint32(0xFF)
+    return out
+
+
+# ----------------------------------------------------------------------------- layouts
+def pack_codes(codes):
+    """[..., C] 4-bit codes -> [..., C/2] bytes, low nibble = lower index."""
+    c = np.asarray(codes, dtype=np.uint8)
+    return (c[..., 0::2] | (c[..., 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_codes(packed):
+    p = np.asarray(packed, dtype=np.uint8)
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.uint8)
+    out[..., 0::2] = p & 15
+    out[..., 1::2] = p >> 4
+    return out
+
+
+def swizzle_scales(s):
+    """Row-major [R, C16] scale bytes -> flat 128x4-tile layout of llm-1b/nvq.cu:40-42 (`sw_off`):
+    offset = ((r>>7)*ncb + (c>>2))*512 + (r&31)*16 + ((r>>5)&3)*4 + (c&3)."""
+    s = np.asarray(s, dtype=np.uint8)
+    R, C16 = s.shape
+    assert R % 128 == 0 and C16 % 4 == 0, (R, C16)
+    t = s.reshape(R // 128, 4, 32, C16 // 4, 4)        # rb, (r%128)/32, r%32, cb, c%4
+    return np.ascontiguousarray(t.transpose(0, 3, 2, 1, 4)).reshape(-1)
+
+
+def unswizzle_scales(flat, R, C16):
+    """Inverse of `swizzle_scales` (llm-1b/nvq.py:103-107)."""
+    t = np.asarray(flat, dtype=np.uint8).reshape(R // 128, C16 // 4, 32, 4, 4)
+    return np.ascontiguousarray(t.transpose(0, 3, 2, 1, 4)).reshape(R, C16)
+
+
+def sw_off(r, c, ncb):
+    """Scalar form of llm-1b/nvq.cu:40-42, used to cross-check the tensor form."""
+    return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3)
+
+
+# ----------------------------------------------------------------------------- quantizers
+def amax_f32(x):
+    """Per-tensor max|x| as float32 (llm-1b/nvq.cu:69-90)."""
+    x = np.asarray(x, dtype=np.float32)
+    return np.float32(np.max(np.abs(x))) if x.size else np.float32(0)
+
+
+def global_scale(amax, k=1.0):
+    """gs = (k*amax) / 2688 clamped to 1e-30 (small-model/model_ref.py:42; k = 4 for the RHT
+    operands, llm-1b/nvq.cu:138)."""
+    am = np.float32(amax) * np.float32(k)
+    return np.maximum(np.float32(am / FP4_E4M3), TINY).astype(np.float32)
+
+
+def _quant_blocks(xb, sr_mode, rnd):
+    """xb: [..., 16] float32 already divided by gs, one scale per leading index.
+    Returns (codes [...,16] uint8, scale bytes [...])."""
+    bmax = np.max(np.abs(xb), axis=-1)
+    sbyte = e4m3_encode((bmax / FP4_MAX).astype(np.float32))
+    bs = e4m3_decode(sbyte)
+    y = (xb / np.maximum(bs, TINY)[..., None]).astype(np.float32)
+    return _round_blocks(xb, y, sbyte, sr_mode, rnd), sbyte
+
+
+def _round_blocks(xb, y, sbyte, sr_mode, rnd):
+    if sr_mode == SR_NONE:
+        codes = e2m1_rn_code(y)
+    elif sr_mode in (SR_DITHER_NVQ, SR_DITHER_FP4K):
+        codes = e2m1_rn_code(sr_dither(y, rnd))
+    elif sr_mode == SR_HW:
+        codes = sr_hw_code(y, rnd)
+    else:
+        raise ValueError(sr_mode)
+    zero_scale = np.broadcast_to((sbyte == 0)[..., None], codes.shape)
+    zcode = (np.signbit(xb).astype(np.uint8) << 3)
+    return np.where(zero_scale, zcode, codes).astype(np.uint8)
+
+
+def _stream(sr_mode, seed, blk_idx, elt_idx):
+    if sr_mode == SR_NONE:
+        return None
+    if sr_mode == SR_DITHER_NVQ:
+        return sr_bits_nvq(seed, blk_idx)
+    if sr_mode == SR_DITHER_FP4K:
+        return sr_bits_fp4k(seed, elt_idx)
+    if sr_mode == SR_HW:
+        return sr_bits_hw(seed, blk_idx)
+    raise ValueError(sr_mode)
+
+
+def quant_rows(x, amax=None, sr_mode=SR_NONE, seed=0):
+    """1x16 blocks along the last dim (small-model/model_ref.py:39-47 `nvfp4_1d`; kernel
+    llm-1b/nvq.cu:93-116).  x: [R, C] float32 holding bf16 values.
+    Returns (packed codes [R, C/2], scale bytes [R, C/16] row-major, gs float32).
+    SR block index = r*(C/16)+c (nvq.cu:113); fp4k element index = 16 * that (fp4k.cu:84)."""
+    x = np.asarray(x, dtype=np.float32)
+    R, C = x.shape
+    assert C % 16 == 0
+    am = amax_f32(x) if amax is None else np.float32(amax)
+    gs = global_scale(am)
+    xb = (x.reshape(R, C // 16, 16) / gs).astype(np.float32)
+    blk = np.arange(R * (C // 16), dtype=np.uint64).reshape(R, C // 16)
+    rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
+    codes, sbyte = _quant_blocks(xb, sr_mode, rnd)
+    return pack_codes(codes.reshape(R, C)), sbyte, gs
+
+
+def rht16_cols(x, signs):
+    """Transpose + sign flip + 16-point Walsh-Hadamard butterflies along the token dim, x0.25
+    (llm-1b/nvq.cu:136-152).  x: [M, C] float32 -> [C, M/16, 16] float32.  Bit i of `signs`
+    negates token i of every 16-token block; stages h = 1, 2, 4, 8, each `a+b, a-b` in FP32."""
+    x = np.asarray(x, dtype=np.float32)
+    M, C = x.shape
+    assert M % 16 == 0
+    v = np.ascontiguousarray(x.T).reshape(C, M // 16, 16).copy()
+    for i in range(16):
+        if (signs >> i) & 1:
+            v[..., i] = -v[..., i]
+    h = 1
+    while h < 16:
+        for i in range(16):
+            if not (i & h):
+                a, b = v[..., i].copy(), v[..., i + h].copy()
+                v[..., i] = a + b
+                v[..., i + h] = a - b
+        h <<= 1
+    return (v * np.float32(0.25)).astype(np.float32)
+
+
+def quant_cols_rht(x, signs, amax=None, sr_mode=SR_NONE, seed=0):
+    """Quantize x^T along tokens after the RHT16 (llm-1b/nvq.cu:122-158): global scale from
+    4*amax(x).  Returns (packed codes [C, M/2], scale bytes [C, M/16], gs float32 incl. the x4).
+    SR block index = c*(M/16)+mb (nvq.cu:155); fp4k element index = c*M + mb*16 (fp4k.cu:114)."""
+    x = np.asarray(x, dtype=np.float32)
+    M, C = x.shape
+    am = amax_f32(x) if amax is None else np.float32(amax)
+    gs = global_scale(am, 4.0)
+    t = rht16_cols(x, signs)
+    xb = (t / gs).astype(np.float32)
+    blk = np.arange(C * (M // 16), dtype=np.uint64).reshape(C, M // 16)
+    rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
+    codes, sbyte = _quant_blocks(xb, sr_mode, rnd)
+    return pack_codes(codes.reshape(C, M)), sbyte, gs
+
+
+def quant_w2d(w, amax=None):
+    """16x16 blocks (small-model/model_ref.py:50-58 `nvfp4_2d`; kernel llm-1b/nvq.cu:162-196).
+    Returns (codes [N,K/2], scales [N,K/16], codesT [K,N/2], scalesT [K,N/16], gs): the
+    transposed operand holds the same code values and the same scale byte at (bk*16+r, bn)."""
+    w = np.asarray(w, dtype=np.float32)
+    N, K = w.shape
+    assert N % 16 == 0 and K % 16 == 0
+    am = amax_f32(w) if amax is None else np.float32(amax)
+    gs = global_scale(am)
+    wb = (w.reshape(N // 16, 16, K // 16, 16).transpose(0, 2, 1, 3) / gs).astype(np.float32)   # bn,bk,r,c
+    bmax = np.max(np.abs(wb), axis=(-1, -2))
+    sbyte = e4m3_encode((bmax / FP4_MAX).astype(np.float32))                                   # [bn,bk]
+    bs = e4m3_decode(sbyte)
+    y = (wb / np.maximum(bs, TINY)[..., None, None]).astype(np.float32)
+    codes = e2m1_rn_code(y)
+    zero = np.broadcast_to((sbyte == 0)[..., None, None], codes.shape)
+    codes = np.where(zero, np.signbit(wb).astype(np.uint8) << 3, codes).astype(np.uint8)
+    full = codes.transpose(0, 2, 1, 3).reshape(N, K)
+    s = np.repeat(sbyte, 16, axis=0)                      # [N, K/16]
+    st = np.repeat(sbyte.T, 16, axis=0)                   # [K, N/16]
+    return pack_codes(full), s, pack_codes(np.ascontiguousarray(full.T)), np.ascontiguousarray(st), gs
+
+
+# ----------------------------------------------------------------------------- decode / GEMM
+def dequant(packed, scales, gs):
+    """value * block scale * tensor scale, in that order (llm-1b/nvq.py:110-117)."""
+    v = E2M1_TABLE[unpack_codes(packed)]
+    s = np.repeat(e4m3_decode(scales), 16, axis=1)
+    return ((v * s).astype(np.float32) * np.float32(gs)).astype(np.float32)
+
+
+def gemm_dequant(a, sa, gsa, b, sb, gsb):
+    """FP32 `deq(A) @ deq(B)^T` (llm-1b/test_nvq.py:12, small-model/test_fp4ops.py:26)."""
+    return dequant(a, sa, gsa) @ dequant(b, sb, gsb).T
+
+
+def gemm_unit(a, sa, b, sb):
+    """Block-scaled product without tensor scales, accumulated in float64: what the tensor core
+    computes before alpha (every product is exact in FP32)."""
+    da = (E2M1_TABLE[unpack_codes(a)] * np.repeat(e4m3_decode(sa), 16, axis=1)).astype(np.float64)
+    db = (E2M1_TABLE[unpack_codes(b)] * np.repeat(e4m3_decode(sb), 16, axis=1)).astype(np.float64)
+    return da @ db.T
+
+
+# ----------------------------------------------------------------------------- whole linear layer
+def linear_fwd_bwd(x, w, gy, signs, seed=0, sr_mode=SR_DITHER_NVQ):
+    """fprop / dgrad / wgrad recipe of `FP4LinearFn` (llm-1b/model.py:45-69) on dequantized
+    operands in FP32.  x [T,K], w [N,K], gy [T,N] float32 holding bf16 values."""
+    qx = quant_rows(x)
+    qw, sw, qwt, swt, gw_ = quant_w2d(w)
+    y = gemm_dequant(qx[0], qx[1], qx[2], qw, sw, gw_)
+    ag = amax_f32(gy)
+    qg = quant_rows(gy, amax=ag, sr_mode=sr_mode, seed=seed)
+    gx = gemm_dequant(qg[0], qg[1], qg[2], qwt, swt, gw_)
+    qgt = quant_cols_rht(gy, signs, amax=ag, sr_mode=sr_mode, seed=seed ^ 0x5BD1E995)
+    qxt = quant_cols_rht(x, signs)
+    gw = gemm_dequant(qgt[0], qgt[1], qgt[2], qxt[0], qxt[1], qxt[2])
+    return y, gx, gw
