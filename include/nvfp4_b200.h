@@ -1,0 +1,163 @@
+/*
+ * nvfp4_b200 -- C ABI of the B200 (sm_100a) NVFP4 linear-layer kernels.
+ *
+ * Drop-in boundary: these entry points take the place of the CUDA kernels the reference
+ * (Not4right/nvfp4-training) compiles at run time with NVRTC and launches through CuPy
+ * (llm-1b/nvrtc_util.py:53-67).  Each declaration names the reference kernel/launcher it replaces.
+ *
+ * Conventions (inherited from the reference launcher):
+ *   - every pointer is a DEVICE pointer unless stated otherwise; the caller owns all memory;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns at once:
+ *     no host synchronisation, no device-scalar read-back, no allocation;
+ *   - device scalars (amax, gs) stay on the device;
+ *   - return value: 0 = enqueued, negative = rejected before any launch (see nvfp4_error_string).
+ *
+ * Data formats (llm-1b/nvq.cu:1-7):
+ *   codes   E2M1, two per byte, low nibble = lower index, rows contiguous along the contraction dim
+ *   scales  one unsigned E4M3 byte per 16 values along the contraction dim, either
+ *           NVFP4_SCALES_SWIZZLED: 128-row x 4-column tiles of 512 bytes, tiles row-block-major,
+ *                                  byte (r%32)*16 + ((r%128)/32)*4 + (c%4) inside a tile
+ *                                  (llm-1b/nvq.cu:40-42; the layout tcgen05 block-scaled MMA and
+ *                                  cuBLASLt consume), or
+ *           NVFP4_SCALES_LINEAR:   row-major [R, C/16] (llm-1b/fp4k.cu:66-87)
+ *   tensor scale  gs = amax / 2688, FP32, not folded into the scales
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_OK               0
+#define NVFP4_ERR_NULL        -1   /* a required pointer is null */
+#define NVFP4_ERR_SHAPE       -2   /* a size violates the divisibility rules of the entry point */
+#define NVFP4_ERR_ALIGN       -3   /* a pointer or stride is not aligned as required */
+#define NVFP4_ERR_ENUM        -4   /* unknown layout / dtype / mode value */
+#define NVFP4_ERR_CUDA        -5   /* a CUDA runtime or driver call failed (launch, attribute, tensor map) */
+#define NVFP4_ERR_WORKSPACE   -6   /* workspace missing or too small */
+#define NVFP4_ERR_TOO_LARGE   -7   /* a size exceeds a documented maximum */
+
+#define NVFP4_SCALES_SWIZZLED  0
+#define NVFP4_SCALES_LINEAR    1
+
+#define NVFP4_DTYPE_BF16       0
+#define NVFP4_DTYPE_FP32       1
+
+/* rounding of the codes */
+#define NVFP4_ROUND_NEAREST     0  /* round to nearest even (cvt.rn.satfinite.e2m1x2.f32)               */
+#define NVFP4_ROUND_SR_DITHER   1  /* mantissa-dither SR + random stream of llm-1b/nvq.cu:32-39,52-59   */
+#define NVFP4_ROUND_SR_DITHER_K 2  /* same rounding, random stream of llm-1b/fp4k.cu:53-58              */
+#define NVFP4_ROUND_SR_HW       3  /* cvt.rs.satfinite.e2m1x4.f32, counter-based stream of this library */
+
+/* how nvfp4_gemm forms the output scale alpha */
+#define NVFP4_ALPHA_ONE         0  /* alpha = 1                       (llm-1b/nvq.py:94 scale=False)    */
+#define NVFP4_ALPHA_GS          1  /* alpha = *pa * *pb               (llm-1b/nvq.py:93: gsA*gsB)       */
+#define NVFP4_ALPHA_AMAX        2  /* alpha = *pa * *pb * ka*kb/2688^2 (llm-1b/fp4k.cu:261)             */
+
+/* Library version, major*10000 + minor*100 + patch. */
+int nvfp4_version(void);
+
+/* Static text for a status code returned by this library. */
+const char* nvfp4_error_string(int status);
+
+/*
+ * Per-tensor max|x| of a contiguous bf16 tensor into *out (FP32).  *out is set to 0 first.
+ * Replaces kernel `amax_bf16` (llm-1b/nvq.cu:69-90) and launcher `nvq.amax` (llm-1b/nvq.py:32-40).
+ * Requires n % 8 == 0, x 16-byte aligned.  n == 0 gives 0.
+ */
+int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream);
+
+/*
+ * 1x16 block quantization of x [R, C] bf16 (row stride ldx elements) along C.
+ * Replaces kernel `quant_rows` (llm-1b/nvq.cu:93-116, llm-1b/fp4k.cu:66-87) and launchers
+ * `nvq.quant_rows` (llm-1b/nvq.py:47-57), `fp4ops.quant_rows` (llm-1b/fp4ops.py:30-38).
+ * codes [R, C/2] bytes, contiguous.  scales: R*C/16 bytes in `scale_layout`.
+ * amax: device FP32 scalar, max|x| of the whole tensor (or a larger bound).
+ * gs_out: optional device FP32 scalar that receives the tensor scale gs (`nvq._gs`, llm-1b/nvq.py:43-44).
+ * Requires C % 16 == 0, ldx % 8 == 0, x 16-byte aligned; SWIZZLED also R % 128 == 0, C % 64 == 0.
+ * Arithmetic: gs = max(amax/2688, 1e-30); bs = e4m3(min((max16|x|/gs)/6, 448));
+ * code = round((x/gs)/bs) -- the operation order of small-model/model_ref.py:39-47, IEEE FP32.
+ */
+int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, void* scales,
+                     int scale_layout, const float* amax, float* gs_out, int rounding, unsigned seed,
+                     void* stream);
+
+/*
+ * Quantization of x^T along the token dim after a 16-point random Hadamard transform:
+ * x [M, C] bf16 contiguous -> codes [C, M/2], scales for [C, M/16]; tensor scale uses 4*amax.
+ * Bit i of `signs` negates token i of every 16-token block; butterflies of strides 1,2,4,8 in FP32,
+ * then x0.25; gs_out (optional) receives gs = 4*amax/2688.  Replaces kernel `quant_cols_rht` (llm-1b/nvq.cu:122-158, llm-1b/fp4k.cu:92-117) and
+ * launchers `nvq.quant_cols_rht` (llm-1b/nvq.py:60-70), `fp4ops.quant_cols_rht` (llm-1b/fp4ops.py:41-49).
+ * Requires M % 16 == 0, C % 8 == 0, x 16-byte aligned; SWIZZLED also C % 128 == 0, M % 64 == 0.
+ */
+int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales, int scale_layout,
+                         const float* amax, float* gs_out, unsigned signs, int rounding, unsigned seed,
+                         void* stream);
+
+/*
+ * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,
+ * emitting W (q [N, K/2], s for [N, K/16]) and W^T (qt [K, N/2], st for [K, N/16]) with identical
+ * code values.  Either output pair may be null to skip it.
+ * Replaces kernel `quant_w2d` (llm-1b/nvq.cu:162-196 bf16; llm-1b/fp4k.cu:121-158 fp32) and
+ * launchers `nvq.quant_w2d` (llm-1b/nvq.py:73-87), `fp4ops.quant_w2d` (llm-1b/fp4ops.py:52-61).
+ * Requires N % 16 == 0, K % 16 == 0; SWIZZLED also N % 128 == 0, K % 128 == 0.
+ */
+int nvfp4_quant_w2d(const void* w, int w_dtype, int N, int K, void* q, void* s, void* qt, void* st,
+                    int scale_layout, const float* amax, float* gs_out, void* stream);
+
+/*
+ * Row-major scale bytes [R, C16] (row stride lds bytes) -> the swizzled layout.
+ * No reference kernel: it converts the llm-1b/fp4k.cu scale layout into the llm-1b/nvq.cu one
+ * (inverse of `nvq.unswizzle`, llm-1b/nvq.py:103-107).  Requires R % 128 == 0, C16 % 4 == 0.
+ */
+int nvfp4_swizzle_scales(const void* s_linear, long long lds, int R, int C16, void* s_swizzled, void* stream);
+
+/*
+ * Block-scaled FP4 GEMM  C[M,N] (+)= alpha * A[M,K] * B[N,K]^T  on tcgen05 tensor cores.
+ * Replaces kernel `gemm_fp4` (llm-1b/fp4k.cu:181-280) / launcher `fp4ops.gemm`
+ * (llm-1b/fp4ops.py:64-80) and the cuBLASLt call behind `nvq.mm` (llm-1b/nvq.py:90-96).
+ *   a, b      packed codes, row strides lda / ldb BYTES (multiples of 16), 16-byte aligned
+ *   sa, sb    scales in the SWIZZLED layout for [M, K/16] and [N, K/16], 16-byte aligned
+ *   c         bf16 or fp32 [M, N], row stride ldc ELEMENTS (multiple of 8), 16-byte aligned
+ *   pa, pb    device FP32 scalars used by alpha_mode (may be null for NVFP4_ALPHA_ONE)
+ *   accumulate  0: C = result; 1: C += result (fp32 only, atomic adds)
+ *   splitk    >= 1: the K range is cut into that many slices of whole 256-element tiles, each
+ *             added atomically into C; needs accumulate = 1 or C zeroed by the caller when > 1
+ *   status    optional device int; a CTA whose bounded pipeline wait expires writes a non-zero
+ *             code there and leaves the kernel without completing its tiles (never expected)
+ * Requires M % 128 == 0, N % 128 == 0, K % 64 == 0.
+ */
+int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, const void* sb, long long ldb,
+               void* c, int c_dtype, long long ldc, int M, int N, int K,
+               int alpha_mode, const float* pa, const float* pb, float ka, float kb,
+               int accumulate, int splitk, int* status, void* stream);
+
+/*
+ * Tuning hook: force the output-tile width of nvfp4_gemm (128 or 256 columns; 0 restores the built-in
+ * choice).  Process-wide; 256 is ignored for calls whose N is not a multiple of 256.  No reference
+ * counterpart (the reference kernel has one fixed 128x128 tile, llm-1b/fp4k.cu:164-167).
+ */
+int nvfp4_gemm_force_tile_n(int bn);
+
+/*
+ * Same product for operands whose scales are in the LINEAR layout (row strides ldsa / ldsb bytes):
+ * the scales are first rewritten into the swizzled layout inside `workspace`, then nvfp4_gemm runs.
+ * This is the `fp4ops.gemm` contract (llm-1b/fp4ops.py:64-80: strided d and s views allowed).
+ * workspace: device memory of at least nvfp4_gemm_linear_workspace_bytes(M, N, K) bytes, 16-byte
+ * aligned, owned by the caller and free for reuse once the stream has passed this call.
+ */
+size_t nvfp4_gemm_linear_workspace_bytes(int M, int N, int K);
+int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, long long ldsa,
+                      const void* b, const void* sb, long long ldb, long long ldsb,
+                      void* c, int c_dtype, long long ldc, int M, int N, int K,
+                      int alpha_mode, const float* pa, const float* pb, float ka, float kb,
+                      int accumulate, int splitk, void* workspace, size_t workspace_bytes,
+                      int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

@@ -1,0 +1,522 @@
+// Block-scaled FP4 GEMM for sm_100a:  C[M,N] (+)= alpha * A[M,K] * B[N,K]^T
+//   A, B   packed E2M1 (2 per byte), K-major; one UE4M3 scale per 16 values in the 128x4-tile
+//          swizzled layout (512-byte tiles, consecutive K tiles of one 128-row block contiguous).
+//
+// Persistent, warp-specialised kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer: per K tile (256 elements) one 128-byte-swizzled box load each for A and
+//               B plus plain bulk copies of the scale tiles (2 KB per 128 rows), all completing on
+//               the stage's `full` mbarrier
+//   warp 1      MMA issuer: copies the stage's scale tiles shared memory -> tensor memory
+//               (tcgen05.cp 32x128b.warpx4), issues four tcgen05.mma kind::mxf4nvf4 block16 (K = 64
+//               each) into the FP32 accumulator in tensor memory, releases the stage with
+//               tcgen05.commit; owns tensor-memory allocation
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one 32-lane quadrant per warp), alpha,
+//               cast and store (or FP32 atomic add for split-K / accumulate)
+// With BN = 128 two accumulators alternate so the epilogue of a tile overlaps the next tile's MMAs.
+// Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, reports a code through
+// `status`, lets copies in flight land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+
+constexpr int kBM = 128;            // rows of A per tile (UMMA M)
+constexpr int kBKBytes = 128;       // bytes of K per stage row = 256 FP4 values = one 128B swizzle row
+constexpr int kBK = 256;            // FP4 values of K per stage
+constexpr int kThreads = 192;
+constexpr u64 kWaitLimitNs = 1000000000ull;   // 1 s per wait, far above any legitimate wait
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kAccStages = BN == 128 ? 2 : 1;
+  static constexpr int kABytes = kBM * kBKBytes;           // 16 KB
+  static constexpr int kBBytes = BN * kBKBytes;            // 16 / 32 KB
+  static constexpr int kSFABytes = 2048;                   // 4 K-chunks x 512 B
+  static constexpr int kSFBBytes = 2048 * (BN / 128);
+  static constexpr int kStageBytes = kABytes + kBBytes + kSFABytes + kSFBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // tensor-memory columns: accumulators first, then scale factors of the stage being multiplied
+  static constexpr int kSfaCol = kAccStages * BN;
+  static constexpr int kSfbCol = kSfaCol + 16;
+  static constexpr int kTmemCols = 512;
+};
+
+struct GemmParams {
+  const unsigned char* sfa;
+  const unsigned char* sfb;
+  void* c;
+  const float* pa;
+  const float* pb;
+  int* status;
+  long long ldc;
+  float kscale;       // ka*kb/2688^2 for NVFP4_ALPHA_AMAX
+  int M, N, K;
+  int alpha_mode;
+  int c_fp32;
+  int atomic;         // 1: add into C with FP32 atomics
+  int splitk;         // number of K slices
+  int ktiles_per_split;
+};
+
+// ---------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(u32 bar, u32 count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(u32 bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(u32 bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ u32 mbar_try_wait(u32 bar, u32 parity) {
+  u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+__device__ __forceinline__ u64 globaltimer_ns() {
+  u64 t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one expired).
+__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const u64 t0 = globaltimer_ns();
+  for (u32 it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 127u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(u32 dst, const CUtensorMap* map, int x, int y, u32 bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(u32 dst, const void* src, u32 bytes, u32 bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(u32 smem_dst, u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(u32 taddr, u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(u32 bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(u32 taddr, u64 sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 sfa_tmem, u32 sfb_tmem,
+                                            u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(u32 taddr, u32 (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets in 16-byte
+// units, descriptor version 1 at bit 46, swizzle mode in bits 61..63 (0 none, 2 = 128 bytes).
+__device__ __forceinline__ u64 smem_desc(u32 saddr, u32 lbo_bytes, u32 sbo_bytes, u32 swizzle) {
+  return (u64)((saddr & 0x3FFFFu) >> 4) | ((u64)(lbo_bytes >> 4) << 16) | ((u64)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | ((u64)swizzle << 61);
+}
+
+// Instruction descriptor for kind::mxf4nvf4 with UE4M3 scales: A/B format E2M1 (code 1) at bits 7 and
+// 10, both operands K-major, N/8 at bit 17, scale format UE4M3 (0) at bit 23, M/16 at bit 24, K = 64.
+__host__ __device__ constexpr u32 make_idesc(int n) {
+  return (1u << 7) | (1u << 10) | ((u32)(n >> 3) << 17) | ((u32)(kBM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------- kernel
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the 128-byte swizzle atoms
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* bar_mem = smem + C::kStages * C::kStageBytes;
+  u64* full_bar = reinterpret_cast<u64*>(bar_mem);
+  u64* empty_bar = full_bar + C::kStages;
+  u64* acc_full = empty_bar + C::kStages;
+  u64* acc_empty = acc_full + 2;
+  u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = p.M / kBM, tiles_n = p.N / BN;
+  const int ktiles = (p.K + kBK - 1) / kBK;
+  const long long num_work = (long long)tiles_m * tiles_n * p.splitk;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full + a), 1); mbar_init(smem_u32(acc_empty + a), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const u32 tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      int stage = 0; u32 phase = 0;
+      const long long sf_row_bytes = (long long)(p.K >> 6) * 512;   // scale bytes of one 128-row block
+      bool ok = true;
+      for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int mt = (int)(w % tiles_m);
+        const long long rest = w / tiles_m;
+        const int nt = (int)(rest % tiles_n);
+        const int z = (int)(rest / tiles_n);
+        const int kt0 = z * p.ktiles_per_split;
+        const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+        for (int kt = kt0; kt < kt1; kt++) {
+          if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          unsigned char* st = smem + stage * C::kStageBytes;
+          const u32 bar = smem_u32(full_bar + stage);
+          const int kchunks = min(4, (p.K - kt * kBK) >> 6);
+          const u32 sf_bytes = (u32)kchunks * 512u;
+          mbar_arrive_expect_tx(bar, (u32)(C::kABytes + C::kBBytes) + sf_bytes * (1 + BN / 128));
+          tma_load_2d(smem_u32(st), &map_a, kt * kBKBytes, mt * kBM, bar);
+          tma_load_2d(smem_u32(st + C::kABytes), &map_b, kt * kBKBytes, nt * BN, bar);
+          bulk_load(smem_u32(st + C::kABytes + C::kBBytes), p.sfa + (long long)mt * sf_row_bytes + (long long)kt * 2048,
+                    sf_bytes, bar);
+#pragma unroll
+          for (int h = 0; h < BN / 128; h++)
+            bulk_load(smem_u32(st + C::kABytes + C::kBBytes + C::kSFABytes + h * 2048),
+                      p.sfb + (long long)(nt * (BN / 128) + h) * sf_row_bytes + (long long)kt * 2048, sf_bytes, bar);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && p.status) atomicExch(p.status, 1);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr u32 idesc = make_idesc(BN);
+      int stage = 0; u32 phase = 0;
+      int acc = 0; u32 acc_phase = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int z = (int)(w / ((long long)tiles_m * tiles_n));
+        const int kt0 = z * p.ktiles_per_split;
+        const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+        // the epilogue must have drained this accumulator
+        if (!mbar_wait(smem_u32(acc_empty + acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const u32 d_tmem = tmem_base + (u32)(acc * BN);
+        for (int kt = kt0; kt < kt1; kt++) {
+          if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          unsigned char* st = smem + stage * C::kStageBytes;
+          const u32 a_addr = smem_u32(st), b_addr = a_addr + C::kABytes;
+          const u32 sfa_addr = b_addr + C::kBBytes, sfb_addr = sfa_addr + C::kSFABytes;
+          const int kchunks = min(4, (p.K - kt * kBK) >> 6);
+          for (int j = 0; j < kchunks; j++) {
+            tc_cp_sf(tmem_base + C::kSfaCol + 4 * j, smem_desc(sfa_addr + 512 * j, 0, 128, 0));
+#pragma unroll
+            for (int h = 0; h < BN / 128; h++)
+              tc_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * j + 4 * h, smem_desc(sfb_addr + 2048 * h + 512 * j, 0, 128, 0));
+          }
+          for (int j = 0; j < kchunks; j++) {
+            // 64 FP4 values = 32 bytes further along K inside the 128-byte swizzle row
+            const u64 adesc = smem_desc(a_addr + 32 * j, 16, 1024, 2);
+            const u64 bdesc = smem_desc(b_addr + 32 * j, 16, 1024, 2);
+            tc_mma_nvf4(d_tmem, adesc, bdesc, idesc, tmem_base + C::kSfaCol + 4 * j, tmem_base + C::kSfbCol + (BN / 32) * j,
+                        (kt > kt0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(empty_bar + stage));     // frees the stage once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(acc_full + acc));          // accumulator complete
+        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok && p.status) atomicExch(p.status, 2);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;                         // tensor-memory lanes 32*quad .. +31
+    int acc = 0; u32 acc_phase = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int mt = (int)(w % tiles_m);
+      const int nt = (int)((w / tiles_m) % tiles_n);
+      // the decision must be warp-uniform: the tensor-memory loads below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(acc_full + acc), acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      float alpha = 1.f;
+      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
+      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
+      const long long row = (long long)mt * kBM + quad * 32 + lane;
+      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (u32)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        u32 r[32];
+        tc_ld32(t_row + c * 32, r);
+        tc_wait_ld();
+        if (c == BN / 32 - 1) {
+          // whole accumulator is in registers: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(acc_empty + acc));
+        }
+        const long long col = (long long)nt * BN + c * 32;
+        if (p.c_fp32) {
+          float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
+          if (p.atomic) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i),
+                           "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),
+                           "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
+                                                                __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            __nv_bfloat162 h;
+            h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h);
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h);
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h);
+            *reinterpret_cast<uint4*>(dst + i) = o;
+          }
+        }
+      }
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 3);
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // let bulk copies still in flight land before shared memory is released
+    const u64 t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// rows x kbytes byte matrix with row stride ld bytes; box = box_rows x 128 bytes, 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long kbytes, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld};
+  const cuuint32_t box[2] = {(cuuint32_t)kBKBytes, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced tile width (tuning and tests)
+
+struct DevInfo { int sms; bool attr128, attr256; };
+static DevInfo* dev_info() {
+  static DevInfo info[64];
+  static bool init[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!init[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return nullptr;
+    info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = false;
+    init[dev] = true;
+  }
+  return &info[dev];
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sms, bool& attr_done,
+                       cudaStream_t st) {
+  using C = Cfg<BN>;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gemm_nvf4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return NVFP4_ERR_CUDA;
+    attr_done = true;
+  }
+  const long long work = (long long)(p.M / kBM) * (p.N / BN) * p.splitk;
+  const unsigned grid = (unsigned)(work < sms ? work : sms);
+  gemm_nvf4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ma, mb, p);
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, const void* sb, long long ldb,
+                          void* c, int c_dtype, long long ldc, int M, int N, int K, int alpha_mode, const float* pa,
+                          const float* pb, float ka, float kb, int accumulate, int splitk, int* status, void* stream) {
+  if (!a || !sa || !b || !sb || !c) return NVFP4_ERR_NULL;
+  if (alpha_mode < NVFP4_ALPHA_ONE || alpha_mode > NVFP4_ALPHA_AMAX) return NVFP4_ERR_ENUM;
+  if (alpha_mode != NVFP4_ALPHA_ONE && (!pa || !pb)) return NVFP4_ERR_NULL;
+  if (c_dtype != NVFP4_DTYPE_BF16 && c_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
+  if (M < 0 || N < 0 || K < 0 || (M % 128) || (N % 128) || (K % 64) || splitk < 1) return NVFP4_ERR_SHAPE;
+  if (lda < K / 2 || ldb < K / 2 || ldc < N) return NVFP4_ERR_SHAPE;
+  if ((accumulate || splitk > 1) && c_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
+  if (!al16(a) || !al16(b) || !al16(sa) || !al16(sb) || !al16(c) || (lda & 15) || (ldb & 15) || (ldc & 7))
+    return NVFP4_ERR_ALIGN;
+  if (M == 0 || N == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    // empty contraction: C = 0 unless accumulating
+    if (!accumulate) {
+      const size_t es = c_dtype == NVFP4_DTYPE_FP32 ? 4 : 2;
+      if (cudaMemset2DAsync(c, (size_t)ldc * es, 0, (size_t)N * es, (size_t)M, st) != cudaSuccess) return NVFP4_ERR_CUDA;
+    }
+    return NVFP4_OK;
+  }
+  DevInfo* di = dev_info();
+  if (!di) return NVFP4_ERR_CUDA;
+
+  const int ktiles = (K + kBK - 1) / kBK;
+  if (splitk > ktiles) splitk = ktiles;
+  int per = (ktiles + splitk - 1) / splitk;
+  splitk = (ktiles + per - 1) / per;
+
+  // wide tiles halve the B traffic per FLOP but cannot overlap their epilogue; use them when the
+  // contraction is long enough to amortise it and N allows
+  bool wide = (N % 256 == 0) && ((long long)per * kBK >= 4096);
+  if (g_force_bn == 128) wide = false;
+  if (g_force_bn == 256 && N % 256 == 0) wide = true;
+  const int bn = wide ? 256 : 128;
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a, M, K / 2, lda, kBM) || !make_map(&mb, b, N, K / 2, ldb, bn)) return NVFP4_ERR_CUDA;
+
+  GemmParams p;
+  p.sfa = static_cast<const unsigned char*>(sa);
+  p.sfb = static_cast<const unsigned char*>(sb);
+  p.c = c; p.pa = pa; p.pb = pb; p.status = status; p.ldc = ldc;
+  p.kscale = ka * kb * (1.f / (kFp4E4m3 * kFp4E4m3));
+  p.M = M; p.N = N; p.K = K;
+  p.alpha_mode = alpha_mode;
+  p.c_fp32 = c_dtype == NVFP4_DTYPE_FP32;
+  p.atomic = (accumulate || splitk > 1) ? 1 : 0;
+  p.splitk = splitk;
+  p.ktiles_per_split = per;
+  if (wide) return launch_gemm<256>(ma, mb, p, di->sms, di->attr256, st);
+  return launch_gemm<128>(ma, mb, p, di->sms, di->attr128, st);
+}
+
+extern "C" size_t nvfp4_gemm_linear_workspace_bytes(int M, int N, int K) {
+  if (M < 0 || N < 0 || K < 0) return 0;
+  return ((size_t)M + (size_t)N) * (size_t)(K / 16);
+}
+
+extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, long long ldsa, const void* b, const void* sb,
+                                 long long ldb, long long ldsb, void* c, int c_dtype, long long ldc, int M, int N, int K,
+                                 int alpha_mode, const float* pa, const float* pb, float ka, float kb, int accumulate,
+                                 int splitk, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+  if (!sa || !sb) return NVFP4_ERR_NULL;
+  if (M < 0 || N < 0 || K < 0 || (M % 128) || (N % 128) || (K % 64)) return NVFP4_ERR_SHAPE;
+  if (!workspace || workspace_bytes < nvfp4_gemm_linear_workspace_bytes(M, N, K)) return NVFP4_ERR_WORKSPACE;
+  if (!al16(workspace)) return NVFP4_ERR_ALIGN;
+  unsigned char* wsa = static_cast<unsigned char*>(workspace);
+  unsigned char* wsb = wsa + (size_t)M * (size_t)(K / 16);      // M % 128 == 0 keeps this 16-byte aligned
+  int rc = nvfp4_swizzle_scales(sa, ldsa, M, K / 16, wsa, stream);
+  if (rc != NVFP4_OK) return rc;
+  rc = nvfp4_swizzle_scales(sb, ldsb, N, K / 16, wsb, stream);
+  if (rc != NVFP4_OK) return rc;
+  return nvfp4_gemm(a, wsa, lda, b, wsb, ldb, c, c_dtype, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, accumulate, splitk,
+                    status, stream);
+}
+
+extern "C" int nvfp4_gemm_force_tile_n(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return NVFP4_ERR_ENUM;
+  g_force_bn = bn;
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_version(void) { return 100; }
+
+extern "C" const char* nvfp4_error_string(int status) {
+  switch (status) {
+    case NVFP4_OK: return "ok";
+    case NVFP4_ERR_NULL: return "a required pointer is null";
+    case NVFP4_ERR_SHAPE: return "a size violates the divisibility rules of the entry point";
+    case NVFP4_ERR_ALIGN: return "a pointer or stride is not aligned as required";
+    case NVFP4_ERR_ENUM: return "unknown or unsupported layout / dtype / mode value";
+    case NVFP4_ERR_CUDA: return "a CUDA runtime or driver call failed";
+    case NVFP4_ERR_WORKSPACE: return "workspace missing or too small";
+    case NVFP4_ERR_TOO_LARGE: return "a size exceeds a documented maximum";
+    default: return "unknown status";
+  }
+}

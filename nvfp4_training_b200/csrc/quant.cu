@@ -1,0 +1,368 @@
+// NVFP4 quantizer kernels for sm_100a: per-tensor amax, 1x16 row quantizer, transposed
+// RHT16 quantizer, 16x16 weight quantizer (W and W^T), scale re-swizzle.  All HBM-bound:
+// 128-bit coalesced loads, register-resident blocks, warp shuffles for exchanges/reductions.
+#include "common.cuh"
+
+namespace nvfp4 {
+
+__device__ __forceinline__ void unpack8(const uint4& q, float* f) {
+  const u32 w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------ amax
+// max|x| via atomicMax on the float bit pattern (non-negative floats order like unsigned ints).
+__global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, long long n8, float* out) {
+  u32 m = 0u;  // running max of |x| as bf16 bit patterns in both halves of a word
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n8; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = ldg128(x + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      m = __vmaxu2(m, v[j].x & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].y & 0x7FFF7FFFu);
+      m = __vmaxu2(m, v[j].z & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].w & 0x7FFF7FFFu);
+    }
+  }
+  for (; i < n8; i += stride) {
+    uint4 v = ldg128(x + i);
+    m = __vmaxu2(m, v.x & 0x7FFF7FFFu); m = __vmaxu2(m, v.y & 0x7FFF7FFFu);
+    m = __vmaxu2(m, v.z & 0x7FFF7FFFu); m = __vmaxu2(m, v.w & 0x7FFF7FFFu);
+  }
+  u32 mm = max(m & 0xFFFFu, m >> 16);
+  // NaN patterns (> 0x7F80) count as +inf
+  mm = min(mm, 0x7F80u);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+  __shared__ u32 sm[8];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = mm;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    mm = threadIdx.x < (blockDim.x >> 5) ? sm[threadIdx.x] : 0u;
+#pragma unroll
+    for (int o = 4; o; o >>= 1) mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    if (threadIdx.x == 0 && mm) atomicMax(reinterpret_cast<unsigned*>(out), mm << 16);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ rows
+// One warp per (row, 512-column segment): lanes load 16-byte chunks l and l+32 (coalesced), lane
+// pairs swap halves so each lane owns one whole 16-block (even lanes: blocks 0..15 of the segment,
+// odd lanes: blocks 16..31), then quantize it from registers.
+template <int ROUNDING>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                          uint2* __restrict__ codes, unsigned char* __restrict__ scales,
+                                                          const float* __restrict__ amax, int R, int C, int linear,
+                                                          u32 seed, float* __restrict__ gs_out) {
+  const int lane = threadIdx.x & 31;
+  const int nchunk = C >> 3, nblk = C >> 4;
+  const int nseg = (nchunk + 63) >> 6;
+  const long long nitems = (long long)R * nseg;
+  const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
+  const float gs = tensor_scale(__ldg(amax), 1.f);
+  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = gs;
+  for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < nitems; item += wstride) {
+    const long long r = item / nseg;
+    const int seg = (int)(item - r * nseg);
+    const int c0 = seg * 64 + lane, c1 = c0 + 32;
+    const __nv_bfloat16* row = x + r * ldx;
+    uint4 A = make_uint4(0, 0, 0, 0), B = make_uint4(0, 0, 0, 0);
+    if (c0 < nchunk) A = ldg128(row + c0 * 8);
+    if (c1 < nchunk) B = ldg128(row + c1 * 8);
+    const bool odd = lane & 1;
+    uint4 snd = odd ? A : B, rcv;
+    rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, 1); rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, 1);
+    rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, 1); rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, 1);
+    const uint4 lo = odd ? rcv : A, hi = odd ? B : rcv;
+    const int blk = seg * 32 + (lane >> 1) + (odd ? 16 : 0);
+    if (blk < nblk) {
+      float v[16];
+      unpack8(lo, v); unpack8(hi, v + 8);
+      float bmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; i++) bmax = fmaxf(bmax, fabsf(v[i]));
+      const long long b = r * nblk + blk;
+      uint2 o; u32 sb;
+      quant_block16<ROUNDING>(v, bmax, gs, seed, (u32)b, (u32)(b * 16), o, sb);
+      codes[b] = o;
+      scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ cols + RHT16
+// CTA tile: 128 columns x 256 tokens.  A thread loads 16 tokens x 8 columns with 16 coalesced
+// 128-bit loads (half-warp = 256 contiguous bytes of one token row), so each 16-token column
+// block lives in its registers: sign flip, 4 butterfly stages, x0.25 and quantization need no
+// shared memory.  Outputs: 8 bytes of codes + 1 scale byte per (column, token block).
+template <int ROUNDING>
+__global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              unsigned char* __restrict__ codes,
+                                                              unsigned char* __restrict__ scales,
+                                                              const float* __restrict__ amax, int M, int C, int linear,
+                                                              u32 signs, u32 seed, float* __restrict__ gs_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cchunk = blockIdx.x * 16 + (lane & 15);            // 8-column chunk index
+  const int mb = blockIdx.y * 16 + warp * 2 + (lane >> 4);     // 16-token block index
+  const int nmb = M >> 4;
+  const float gs = tensor_scale(__ldg(amax), 4.f);
+  if (gs_out && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *gs_out = gs;
+  if (cchunk * 8 >= C || mb >= nmb) return;
+  uint4 raw[16];
+  const __nv_bfloat16* p = x + (long long)mb * 16 * C + cchunk * 8;
+#pragma unroll
+  for (int i = 0; i < 16; i++) raw[i] = ldg128(p + (long long)i * C);
+  // apply the sign vector on the packed bf16 words: token i is negated when bit i of signs is set
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    const u32 f = ((signs >> i) & 1u) ? 0x80008000u : 0u;
+    raw[i].x ^= f; raw[i].y ^= f; raw[i].z ^= f; raw[i].w ^= f;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const u32 w = (j >> 1) == 0 ? raw[i].x : (j >> 1) == 1 ? raw[i].y : (j >> 1) == 2 ? raw[i].z : raw[i].w;
+      v[i] = (j & 1) ? __uint_as_float(w & 0xFFFF0000u) : __uint_as_float(w << 16);
+    }
+#pragma unroll
+    for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+      for (int i = 0; i < 16; i++)
+        if (!(i & h)) { const float a = v[i], b = v[i + h]; v[i] = __fadd_rn(a, b); v[i + h] = __fsub_rn(a, b); }
+    float bmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) { v[i] = __fmul_rn(v[i], 0.25f); bmax = fmaxf(bmax, fabsf(v[i])); }
+    const long long c = (long long)cchunk * 8 + j;
+    const long long b = c * nmb + mb;
+    uint2 o; u32 sb;
+    quant_block16<ROUNDING>(v, bmax, gs, seed, (u32)b, (u32)(b * 16), o, sb);
+    *reinterpret_cast<uint2*>(codes + b * 8) = o;
+    scales[linear ? b : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ 16x16 weights
+// One warp per 16x16 block: lane = (row, 8-column half).  Block max by warp shuffles, codes for W
+// written as one word per lane, codes for W^T gathered with shuffles (lane = (k row, 8-row half)).
+template <typename T>
+__global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w, u32* __restrict__ q,
+                                                         unsigned char* __restrict__ s, u32* __restrict__ qt,
+                                                         unsigned char* __restrict__ st, const float* __restrict__ amax,
+                                                         int N, int K, int linear, float* __restrict__ gs_out) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nb = N >> 4, kb = K >> 4;
+  if (warp >= (long long)nb * kb) return;
+  const int bn = (int)(warp / kb), bk = (int)(warp - (long long)bn * kb);
+  const float gs = tensor_scale(__ldg(amax), 1.f);
+  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = gs;
+  const int r = lane >> 1, c0 = (lane & 1) * 8;
+  const T* src = w + (long long)(bn * 16 + r) * K + bk * 16 + c0;
+  float v[16];
+  if constexpr (sizeof(T) == 2) {
+    unpack8(ldg128(src), v);
+  } else {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  float bmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) bmax = fmaxf(bmax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+  // reuse the 16-wide block quantizer on 8 live values (upper half = copies, discarded)
+#pragma unroll
+  for (int i = 0; i < 8; i++) v[8 + i] = v[i];
+  uint2 o; u32 sb;
+  quant_block16<NVFP4_ROUND_NEAREST>(v, bmax, gs, 0u, 0u, 0u, o, sb);
+  const u32 word = o.x;
+  if (q) {
+    q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;
+    if (!(lane & 1)) s[linear ? (long long)(bn * 16 + r) * kb + bk : sw_off(bn * 16 + r, bk, kb >> 2)] = (unsigned char)sb;
+  }
+  // transposed block: this lane builds k-row kk = lane>>1, n values (lane&1)*8 .. +7
+  const int kk = lane >> 1;
+  u32 wt = 0u;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int row = c0 + i;
+    const u32 ww = __shfl_sync(0xffffffffu, word, 2 * row + (kk >> 3));
+    wt |= ((ww >> (4 * (kk & 7))) & 15u) << (4 * i);
+  }
+  if (qt) {
+    qt[((long long)(bk * 16 + kk) * N + bn * 16 + c0) >> 3] = wt;
+    if (!(lane & 1)) st[linear ? (long long)(bk * 16 + kk) * nb + bn : sw_off(bk * 16 + kk, bn, nb >> 2)] = (unsigned char)sb;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ scale re-swizzle
+__global__ void __launch_bounds__(256) swizzle_scales_kernel(const unsigned char* __restrict__ src, long long lds,
+                                                              int R, int C16, unsigned char* __restrict__ dst) {
+  const int ncb = C16 >> 2;
+  const long long total = (long long)R * ncb;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    // consecutive threads walk the destination so stores coalesce
+    const long long tile = i >> 7;           // (row block, column tile)
+    const int in = (int)(i & 127);           // (r%32)*4 + (r%128)/32
+    const long long rb = tile / ncb; const int cb = (int)(tile - rb * ncb);
+    const long long r = rb * 128 + (in & 3) * 32 + (in >> 2);
+    const unsigned char* p = src + r * lds + cb * 4;
+    const u32 v = (u32)p[0] | ((u32)p[1] << 8) | ((u32)p[2] << 16) | ((u32)p[3] << 24);
+    *reinterpret_cast<u32*>(dst + i * 4) = v;
+  }
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream) {
+  if (!out || (!x && n > 0)) return NVFP4_ERR_NULL;
+  if (n < 0 || (n & 7)) return NVFP4_ERR_SHAPE;
+  if (!aligned16(x)) return NVFP4_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(out, 0, sizeof(float), st) != cudaSuccess) return NVFP4_ERR_CUDA;
+  if (n == 0) return NVFP4_OK;
+  const long long n8 = n >> 3;
+  long long blocks = (n8 + 256 * 4 - 1) / (256 * 4);
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  amax_bf16_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint4*>(x), n8, out);
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, void* scales,
+                                int scale_layout, const float* amax, float* gs_out, int rounding, unsigned seed,
+                                void* stream) {
+  if (!x || !codes || !scales || !amax) return NVFP4_ERR_NULL;
+  if (scale_layout != NVFP4_SCALES_SWIZZLED && scale_layout != NVFP4_SCALES_LINEAR) return NVFP4_ERR_ENUM;
+  if (rounding < NVFP4_ROUND_NEAREST || rounding > NVFP4_ROUND_SR_HW) return NVFP4_ERR_ENUM;
+  if (R < 0 || C < 0 || (C & 15) || ldx < C) return NVFP4_ERR_SHAPE;
+  if (scale_layout == NVFP4_SCALES_SWIZZLED && ((R & 127) || (C & 63))) return NVFP4_ERR_SHAPE;
+  if (!aligned16(x) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes) & 7u)) return NVFP4_ERR_ALIGN;
+  if (R == 0 || C == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long nitems = (long long)R * (((C >> 3) + 63) >> 6);
+  long long blocks = (nitems + 7) / 8;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  const int linear = scale_layout == NVFP4_SCALES_LINEAR;
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  uint2* cp = static_cast<uint2*>(codes);
+  unsigned char* sp = static_cast<unsigned char*>(scales);
+  switch (rounding) {
+    case NVFP4_ROUND_NEAREST:
+      quant_rows_kernel<NVFP4_ROUND_NEAREST><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+    case NVFP4_ROUND_SR_DITHER:
+      quant_rows_kernel<NVFP4_ROUND_SR_DITHER><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+    case NVFP4_ROUND_SR_DITHER_K:
+      quant_rows_kernel<NVFP4_ROUND_SR_DITHER_K><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+    default:
+      quant_rows_kernel<NVFP4_ROUND_SR_HW><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+  }
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales, int scale_layout,
+                                    const float* amax, float* gs_out, unsigned signs, int rounding, unsigned seed,
+                                    void* stream) {
+  if (!x || !codes || !scales || !amax) return NVFP4_ERR_NULL;
+  if (scale_layout != NVFP4_SCALES_SWIZZLED && scale_layout != NVFP4_SCALES_LINEAR) return NVFP4_ERR_ENUM;
+  if (rounding < NVFP4_ROUND_NEAREST || rounding > NVFP4_ROUND_SR_HW) return NVFP4_ERR_ENUM;
+  if (M < 0 || C < 0 || (M & 15) || (C & 7)) return NVFP4_ERR_SHAPE;
+  if (scale_layout == NVFP4_SCALES_SWIZZLED && ((C & 127) || (M & 63))) return NVFP4_ERR_SHAPE;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7u)) return NVFP4_ERR_ALIGN;
+  if (M == 0 || C == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((unsigned)((C + 127) / 128), (unsigned)((M + 255) / 256));
+  if (grid.y > 65535u) return NVFP4_ERR_TOO_LARGE;
+  const int linear = scale_layout == NVFP4_SCALES_LINEAR;
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  unsigned char* cp = static_cast<unsigned char*>(codes);
+  unsigned char* sp = static_cast<unsigned char*>(scales);
+  signs &= 0xFFFFu;
+  switch (rounding) {
+    case NVFP4_ROUND_NEAREST:
+      quant_cols_rht_kernel<NVFP4_ROUND_NEAREST><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+    case NVFP4_ROUND_SR_DITHER:
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+    case NVFP4_ROUND_SR_DITHER_K:
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER_K><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+    default:
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_HW><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+  }
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_quant_w2d(const void* w, int w_dtype, int N, int K, void* q, void* s, void* qt, void* st_,
+                               int scale_layout, const float* amax, float* gs_out, void* stream) {
+  if (!w || !amax || (!q && !qt) || (q && !s) || (qt && !st_)) return NVFP4_ERR_NULL;
+  if (scale_layout != NVFP4_SCALES_SWIZZLED && scale_layout != NVFP4_SCALES_LINEAR) return NVFP4_ERR_ENUM;
+  if (w_dtype != NVFP4_DTYPE_BF16 && w_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
+  if (N < 0 || K < 0 || (N & 15) || (K & 15)) return NVFP4_ERR_SHAPE;
+  if (scale_layout == NVFP4_SCALES_SWIZZLED && ((N & 127) || (K & 127))) return NVFP4_ERR_SHAPE;
+  if (!aligned16(w) || (q && (reinterpret_cast<uintptr_t>(q) & 3u)) || (qt && (reinterpret_cast<uintptr_t>(qt) & 3u)))
+    return NVFP4_ERR_ALIGN;
+  if (N == 0 || K == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long nwarps = (long long)(N >> 4) * (K >> 4);
+  const long long blocks = (nwarps + 7) / 8;
+  if (blocks > 0x7FFFFFFFLL) return NVFP4_ERR_TOO_LARGE;
+  const int linear = scale_layout == NVFP4_SCALES_LINEAR;
+  if (w_dtype == NVFP4_DTYPE_BF16)
+    quant_w2d_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), static_cast<u32*>(q),
+        static_cast<unsigned char*>(s), static_cast<u32*>(qt), static_cast<unsigned char*>(st_), amax, N, K, linear, gs_out);
+  else
+    quant_w2d_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const float*>(w), static_cast<u32*>(q),
+        static_cast<unsigned char*>(s), static_cast<u32*>(qt), static_cast<unsigned char*>(st_), amax, N, K, linear, gs_out);
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_swizzle_scales(const void* s_linear, long long lds, int R, int C16, void* s_swizzled, void* stream) {
+  if (!s_linear || !s_swizzled) return NVFP4_ERR_NULL;
+  if (R < 0 || C16 < 0 || (R & 127) || (C16 & 3) || lds < C16) return NVFP4_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(s_swizzled) & 3u) return NVFP4_ERR_ALIGN;
+  if (R == 0 || C16 == 0) return NVFP4_OK;
+  const long long total = (long long)R * (C16 >> 2);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  swizzle_scales_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char*>(s_linear), lds, R, C16, static_cast<unsigned char*>(s_swizzled));
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}

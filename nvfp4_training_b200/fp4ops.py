@@ -1,0 +1,106 @@
+"""Drop-in for the reference's `fp4ops` module (llm-1b/fp4ops.py = small-model/fp4ops.py):
+quantizers with row-major `[R, C/16]` scales, FP32 weights, and `gemm` with bf16 output or FP32
+split-K accumulation, on the sm_100a C-ABI library.
+
+The tensor-core path consumes swizzled scales, so `gemm` first rewrites both operands' scales into
+a scratch buffer it allocates with torch (the C entry point takes it as `workspace`).
+"""
+import torch
+
+from . import _lib as L
+
+SMEM_GEMM = 6 * (128 * 128 + 128 * 128 + 2048 + 2048) + 1280   # informational, like llm-1b/fp4ops.py:8
+SR_MODE = L.ROUND_SR_DITHER_K
+
+
+class Q:
+    """Packed NVFP4 tensor: data [R, C/2] uint8, scales [R, C/16] uint8, amax (device scalar),
+    k (extra scale) (llm-1b/fp4ops.py:18-23)."""
+    __slots__ = ("d", "s", "amax", "k")
+
+    def __init__(self, d, s, amax, k=1.0):
+        self.d, self.s, self.amax, self.k = d, s, amax, k
+
+
+def amax_of(x):
+    return x.abs().amax().float().reshape(1)
+
+
+def quant_rows(x, sr=False, seed=0, amax=None):
+    """llm-1b/fp4ops.py:30-38."""
+    L.require_cuda(x)
+    R, C = x.shape
+    x = x.contiguous()
+    assert x.dtype == torch.bfloat16 and C % 16 == 0
+    a = amax_of(x) if amax is None else amax
+    d = torch.empty(R, C // 2, dtype=torch.uint8, device=x.device)
+    s = torch.empty(R, C // 16, dtype=torch.uint8, device=x.device)
+    L.check(L.load().nvfp4_quant_rows(L.ptr(x), C, R, C, L.ptr(d), L.ptr(s), L.SCALES_LINEAR, L.ptr(a),
+                                      None, SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()), "quant_rows")
+    return Q(d, s, a)
+
+
+def quant_cols_rht(x, signs, sr=False, seed=0, amax=None):
+    """x [M, C] -> quantized along M of x^T: data [C, M/2].  RHT applied along M (16-blocks)
+    (llm-1b/fp4ops.py:41-49)."""
+    L.require_cuda(x)
+    M, C = x.shape
+    x = x.contiguous()
+    assert x.dtype == torch.bfloat16 and M % 16 == 0 and C % 8 == 0
+    a = amax_of(x) if amax is None else amax
+    d = torch.empty(C, M // 2, dtype=torch.uint8, device=x.device)
+    s = torch.empty(C, M // 16, dtype=torch.uint8, device=x.device)
+    L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_LINEAR, L.ptr(a), None, signs & 0xFFFF,
+                                          SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()),
+            "quant_cols_rht")
+    return Q(d, s, a, 4.0)
+
+
+def quant_w2d(w):
+    """w fp32 [N, K] -> (Q, Q^T) (llm-1b/fp4ops.py:52-61)."""
+    L.require_cuda(w)
+    N, K = w.shape
+    assert w.dtype == torch.float32 and N % 16 == 0 and K % 16 == 0
+    a = amax_of(w)
+    q = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device)
+    s = torch.empty(N, K // 16, dtype=torch.uint8, device=w.device)
+    qt = torch.empty(K, N // 2, dtype=torch.uint8, device=w.device)
+    st = torch.empty(K, N // 16, dtype=torch.uint8, device=w.device)
+    L.check(L.load().nvfp4_quant_w2d(L.ptr(w.contiguous()), L.DTYPE_FP32, N, K, L.ptr(q), L.ptr(s), L.ptr(qt), L.ptr(st),
+                                     L.SCALES_LINEAR, L.ptr(a), None, L.stream()), "quant_w2d")
+    return Q(q, s, a), Q(qt, st, a)
+
+
+def gemm(a: Q, b: Q, out=None, splitk=1):
+    """a: [M,K] fp4, b: [N,K] fp4 -> [M,N].  splitk>1 or out given -> fp32 atomic accumulate into out
+    (llm-1b/fp4ops.py:64-80).  Row strides of d and s are honoured."""
+    L.require_cuda(a.d, b.d)
+    M, N, K = a.d.shape[0], b.d.shape[0], a.s.shape[1] * 16
+    assert M % 128 == 0 and N % 128 == 0 and K % 128 == 0, (M, N, K)
+    if splitk == 1 and out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.d.device)
+        acc, cdt = 0, L.DTYPE_BF16
+    else:
+        if out is None:
+            out = torch.zeros(M, N, dtype=torch.float32, device=a.d.device)
+        assert out.dtype == torch.float32 and out.stride(1) == 1
+        acc, cdt = 1, L.DTYPE_FP32
+    lib = L.load()
+    ws = torch.empty(lib.nvfp4_gemm_linear_workspace_bytes(M, N, K), dtype=torch.uint8, device=a.d.device)
+    L.check(lib.nvfp4_gemm_linear(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), a.s.stride(0), L.ptr(b.d), L.ptr(b.s),
+                                  b.d.stride(0), b.s.stride(0), L.ptr(out), cdt, out.stride(0), M, N, K, L.ALPHA_AMAX,
+                                  L.ptr(a.amax), L.ptr(b.amax), float(a.k), float(b.k), acc, splitk, L.ptr(ws),
+                                  ws.numel(), L.ptr(L.status_word(a.d.device)), L.stream()), "gemm")
+    return out
+
+
+# ---------- reference decode (for tests), llm-1b/fp4ops.py:83-92
+_E2M1 = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+
+
+def dequant(q: Q):
+    d = q.d
+    lo, hi = (d & 15).long(), (d >> 4).long()
+    v = torch.stack([_E2M1.to(d.device)[lo], _E2M1.to(d.device)[hi]], -1).reshape(d.shape[0], -1)
+    s = q.s.view(torch.float8_e4m3fn).float().repeat_interleave(16, 1)
+    return v * s * (q.amax * q.k / 2688.0)

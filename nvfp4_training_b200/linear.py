@@ -1,0 +1,100 @@
+"""Autograd NVFP4 linear layer: the recipe of `FP4LinearFn` / `Linear` in the reference
+(llm-1b/model.py:36-90) on the sm_100a kernels.
+
+  fprop : y  = Q_rn(x)  @ Q2d(W)^T
+  dgrad : dx = Q_sr(dy) @ Q2d(W)          (W^T operand: same 16x16-block values)
+  wgrad : dW = Q_sr(H dy)^T @ Q_rn(H x)   (16-point random Hadamard along tokens)
+
+Additions that do not change results: `LinCtx.wgrad_dtype` (the reference returns a bf16 weight
+gradient, llm-1b/nvq.py:90; FP32 is what a data-parallel all-reduce wants) and `WeightCache`, which
+quantizes a weight once per optimizer step instead of twice per microbatch -- the scheme of
+`FP4Weight.refresh` (small-model/fp4torch.py:71-84).
+"""
+import torch
+import torch.nn as nn
+
+from . import nvq
+
+
+class LinCtx:
+    """Global switches for the linear layers (llm-1b/model.py:36-39)."""
+    fp4 = True
+    seed = 0                       # changes every microbatch (stochastic rounding)
+    wgrad_dtype = torch.bfloat16   # reference default; torch.float32 for FP32 weight gradients
+
+
+_RHT_SIGNS = 0b1010011010110001    # llm-1b/model.py:42
+
+
+def sr_seed(lid):
+    """Per-layer, per-microbatch seed (llm-1b/model.py:59)."""
+    return (LinCtx.seed * 1000003 + lid * 7919) & 0xFFFFFFFF
+
+
+class WeightCache:
+    """Quantized W and W^T of one weight, refreshed once per optimizer step."""
+
+    def __init__(self, weight):
+        self.weight = weight
+        self.q = self.qt = None
+
+    @torch.no_grad()
+    def refresh(self):
+        self.q, self.qt = nvq.quant_w2d(self.weight.detach().to(torch.bfloat16))
+        return self
+
+
+class FP4LinearFn(torch.autograd.Function):
+    """x [T, K] bf16, w [N, K] bf16 -> y [T, N] bf16 (llm-1b/model.py:45-69)."""
+
+    @staticmethod
+    def forward(ctx, x, w, lid, cache=None):
+        ctx.save_for_backward(x, w)
+        ctx.lid, ctx.cache = lid, cache
+        qx = nvq.quant_rows(x)
+        qw = cache.q if cache is not None else nvq.quant_w2d(w, want=(True, False))[0]
+        return nvq.mm(qx, qw)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        gy = gy.contiguous()
+        seed = sr_seed(ctx.lid)
+        ag = nvq.amax(gy)
+        # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
+        qwt = ctx.cache.qt if ctx.cache is not None else nvq.quant_w2d(w, want=(False, True))[1]
+        qg = nvq.quant_rows(gy, sr=True, seed=seed, am=ag)
+        gx = nvq.mm(qg, qwt)
+        # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
+        qgt = nvq.quant_cols_rht(gy, _RHT_SIGNS, sr=True, seed=seed ^ 0x5bd1e995, am=ag)
+        qxt = nvq.quant_cols_rht(x, _RHT_SIGNS)
+        gw = nvq.mm(qgt, qxt, out_dtype=LinCtx.wgrad_dtype)
+        return gx, gw, None, None
+
+
+class Linear(nn.Module):
+    """Bias-free linear whose GEMMs run in NVFP4 when LinCtx.fp4, else BF16 (llm-1b/model.py:72-90)."""
+    _next_id = 0
+
+    def __init__(self, fin, fout, std, cache_weights=False):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(fout, fin))
+        nn.init.trunc_normal_(self.weight, std=std, a=-3 * std, b=3 * std)
+        self.lid = Linear._next_id
+        Linear._next_id += 1
+        self.cache = WeightCache(self.weight) if cache_weights else None
+
+    def refresh(self):
+        if self.cache is not None:
+            self.cache.refresh()
+
+    def forward(self, x):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        if LinCtx.fp4:
+            if self.cache is not None and self.cache.q is None:
+                self.cache.refresh()
+            y = FP4LinearFn.apply(x2, self.weight, self.lid, self.cache)
+        else:
+            y = x2 @ self.weight.t()
+        return y.view(*shp[:-1], -1)

@@ -1,0 +1,145 @@
+"""Drop-in for the reference's `nvq` module (llm-1b/nvq.py): NVFP4 quantizers with swizzled
+E4M3 scales and the block-scaled FP4 GEMM, same names, arguments, tensor layouts and assertions,
+running on the sm_100a C-ABI library instead of NVRTC kernels + cuBLASLt.
+
+Differences a caller can observe, all inside the stated tolerances:
+  * `gs` is `amax / 2688` by IEEE division (the order of small-model/model_ref.py:42), written by the
+    quantizer kernel itself, instead of `amax * (1/2688)` (llm-1b/nvq.py:43-44); at most one ulp apart.
+  * `mm` applies alpha = gsA*gsB in FP32 inside the GEMM epilogue before the output cast, instead of
+    rounding alpha to bf16 and multiplying a bf16 product (llm-1b/nvq.py:96).
+  * stochastic rounding defaults to the reference's mantissa-dither method and random stream;
+    `SR_MODE` switches to the hardware `cvt.rs` path.
+"""
+import torch
+
+from . import _lib as L
+
+# rounding used when a quantizer is called with sr=True
+SR_MODE = L.ROUND_SR_DITHER
+
+
+class Q:
+    """Packed NVFP4 matrix [R, C]: d [R, C/2] fp4x2, s swizzled e4m3 (flat), gs = per-tensor scale
+    (device, fp32).  Same container as llm-1b/nvq.py:24-29."""
+    __slots__ = ("d", "s", "gs")
+
+    def __init__(self, d, s, gs):
+        self.d, self.s, self.gs = d, s, gs
+
+
+def amax(x, out=None):
+    """max|x| of a contiguous bf16 tensor as a device fp32 [1] (llm-1b/nvq.py:32-40)."""
+    L.require_cuda(x, out)
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    n = x.numel()
+    assert n % 8 == 0 and x.is_contiguous() and x.dtype == torch.bfloat16
+    L.check(L.load().nvfp4_amax_bf16(L.ptr(x), n, L.ptr(out), L.stream()), "amax")
+    return out
+
+
+def _new_gs(am):
+    # filled by the quantizer kernel with gs = (k*amax)/2688, the role of `_gs` in llm-1b/nvq.py:43-44
+    return torch.empty(1, dtype=torch.float32, device=am.device)
+
+
+def quant_rows(x, sr=False, seed=0, am=None):
+    """x [R, C] bf16 (row-contiguous) -> Q quantized along C (llm-1b/nvq.py:47-57)."""
+    L.require_cuda(x)
+    R, C = x.shape
+    assert x.dtype == torch.bfloat16
+    assert x.stride(1) == 1 and C % 64 == 0 and R % 128 == 0, (R, C)
+    if am is None:
+        am = amax(x.contiguous())
+    d = torch.empty(R, C // 2, dtype=torch.uint8, device=x.device)
+    s = torch.empty(R * C // 16, dtype=torch.uint8, device=x.device)
+    gs = _new_gs(am)
+    L.check(L.load().nvfp4_quant_rows(L.ptr(x), x.stride(0), R, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am),
+                                      L.ptr(gs), SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()),
+            "quant_rows")
+    return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
+
+
+def quant_cols_rht(x, signs, sr=False, seed=0, am=None):
+    """x [M, C] -> Q of x^T [C, M] quantized along M, after a 16-pt RHT along M (llm-1b/nvq.py:60-70)."""
+    L.require_cuda(x)
+    M, C = x.shape
+    assert x.dtype == torch.bfloat16
+    x = x.contiguous()
+    assert M % 64 == 0 and C % 128 == 0, (M, C)
+    if am is None:
+        am = amax(x)
+    d = torch.empty(C, M // 2, dtype=torch.uint8, device=x.device)
+    s = torch.empty(C * M // 16, dtype=torch.uint8, device=x.device)
+    gs = _new_gs(am)
+    L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gs),
+                                          signs & 0xFFFF, SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF,
+                                          L.stream()), "quant_cols_rht")
+    return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
+
+
+def quant_w2d(w, am=None, want=(True, True)):
+    """w [N, K] bf16 -> (Q of w, Q of w^T), identical values (16x16 blocks) (llm-1b/nvq.py:73-87).
+    `want` lets a caller skip one of the two outputs (its slot is then None)."""
+    L.require_cuda(w)
+    N, K = w.shape
+    assert w.dtype == torch.bfloat16
+    w = w.contiguous()
+    assert N % 128 == 0 and K % 128 == 0, (N, K)
+    if am is None:
+        am = amax(w)
+    f4, f8 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+    q = s = qt = st = None
+    if want[0]:
+        q = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device)
+        s = torch.empty(N * K // 16, dtype=torch.uint8, device=w.device)
+    if want[1]:
+        qt = torch.empty(K, N // 2, dtype=torch.uint8, device=w.device)
+        st = torch.empty(K * N // 16, dtype=torch.uint8, device=w.device)
+    g = _new_gs(am)
+    L.check(L.load().nvfp4_quant_w2d(L.ptr(w), L.DTYPE_BF16, N, K, L.ptr(q), L.ptr(s), L.ptr(qt), L.ptr(st),
+                                     L.SCALES_SWIZZLED, L.ptr(am), L.ptr(g), L.stream()), "quant_w2d")
+    return (Q(q.view(f4), s.view(f8), g) if want[0] else None,
+            Q(qt.view(f4), st.view(f8), g) if want[1] else None)
+
+
+def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False):
+    """a [M,K], b [N,K] (both K-major) -> a @ b^T [M, N].  If scale=False returns (raw, alpha)
+    (llm-1b/nvq.py:90-96).  `out` / `accumulate` (fp32 only) are additions for in-place wgrad."""
+    M, N, K = a.d.shape[0], b.d.shape[0], a.d.shape[1] * 2
+    assert b.d.shape[1] * 2 == K, (a.d.shape, b.d.shape)
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    L.require_cuda(a.d, b.d)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.d.device)
+    else:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
+    L.check(L.load().nvfp4_gemm(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), L.ptr(b.d), L.ptr(b.s), b.d.stride(0),
+                                L.ptr(out), L.DTYPE_FP32 if out_dtype == torch.float32 else L.DTYPE_BF16,
+                                out.stride(0), M, N, K, L.ALPHA_GS if scale else L.ALPHA_ONE,
+                                L.ptr(a.gs) if scale else None, L.ptr(b.gs) if scale else None, 1.0, 1.0,
+                                int(accumulate), 1, L.ptr(L.status_word(a.d.device)), L.stream()), "mm")
+    if not scale:
+        return out, a.gs * b.gs
+    return out
+
+
+# ---------- reference decode (tests), llm-1b/nvq.py:99-117
+_E2M1 = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+
+
+def unswizzle(s, R, C16):
+    ncb = C16 // 4
+    t = s.view(torch.uint8).reshape(R // 128, ncb, 32, 4, 4)       # rb, cb, r%32, (r%128)/32, c%4
+    return t.permute(0, 3, 2, 1, 4).reshape(R, C16)                 # rb,(r/32),(r%32), cb, c%4
+
+
+def dequant(q: Q):
+    d = q.d.view(torch.uint8)
+    R, C = d.shape[0], d.shape[1] * 2
+    lo, hi = (d & 15).long(), (d >> 4).long()
+    tab = _E2M1.to(d.device)
+    v = torch.stack([tab[lo], tab[hi]], -1).reshape(R, C)
+    s = unswizzle(q.s, R, C // 16).view(torch.float8_e4m3fn).float().repeat_interleave(16, 1)
+    return v * s * q.gs

@@ -1,0 +1,75 @@
+"""CPU-side checks of the C-ABI boundary: the built library loads, exports every function that
+include/nvfp4_b200.h declares, and rejects malformed calls before touching the device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "nvfp4_b200.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from nvfp4_training_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_functions_are_exported_and_bound(lib):
+    from nvfp4_training_b200 import _lib
+    names = declared_functions()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_error_strings(lib):
+    assert lib.nvfp4_version() >= 100
+    for code in range(0, -8, -1):
+        assert lib.nvfp4_error_string(code)
+    assert lib.nvfp4_error_string(-99) == b"unknown status"
+
+
+def test_argument_validation_needs_no_device(lib):
+    # null pointers, bad shapes, bad enums: all rejected before any CUDA call
+    assert lib.nvfp4_amax_bf16(None, 8, None, None) == -1
+    assert lib.nvfp4_amax_bf16(ctypes.c_void_p(16), 12, ctypes.c_void_p(16), None) == -2
+    assert lib.nvfp4_quant_rows(None, 64, 128, 64, None, None, 0, None, None, 0, 0, None) == -1
+    p = ctypes.c_void_p(1 << 20)
+    assert lib.nvfp4_quant_rows(p, 64, 100, 64, p, p, 0, p, None, 0, 0, None) == -2
+    assert lib.nvfp4_quant_rows(p, 64, 128, 64, p, p, 0, p, None, 9, 0, None) == -4
+    assert lib.nvfp4_quant_cols_rht(p, 64, 100, p, p, 0, p, None, 0, 0, 0, None) == -2
+    assert lib.nvfp4_quant_w2d(p, 5, 128, 128, p, p, p, p, 0, p, None, None) == -4
+    assert lib.nvfp4_gemm(p, p, 64, p, p, 64, p, 1, 128, 128, 128, 100, 0, None, None, 1.0, 1.0, 0, 1, None, None) == -2
+    assert lib.nvfp4_gemm_linear(p, p, 64, 8, p, p, 64, 8, p, 1, 128, 128, 128, 128, 0, None, None, 1.0, 1.0, 0, 1,
+                                 None, 0, None, None) == -6
+    assert lib.nvfp4_gemm_linear_workspace_bytes(128, 256, 1024) == (128 + 256) * 64
+    assert lib.nvfp4_gemm_force_tile_n(64) == -4 and lib.nvfp4_gemm_force_tile_n(0) == 0
+
+
+def test_python_wrappers_refuse_cpu_tensors():
+    import torch
+    from nvfp4_training_b200 import _lib, fp4ops, nvq
+    x = torch.zeros(128, 64, dtype=torch.bfloat16)
+    with pytest.raises(_lib.Nvfp4Error):
+        nvq.quant_rows(x)
+    with pytest.raises(_lib.Nvfp4Error):
+        fp4ops.quant_rows(x, amax=torch.ones(1))
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from nvfp4_training_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", os.path.join(ROOT, "does_not_exist.so"))
+    with pytest.raises(_lib.Nvfp4Error):
+        _lib.load()

@@ -1,0 +1,51 @@
+"""GPU parity of the autograd NVFP4 linear layer (llm-1b/model.py:45-69 recipe) with the oracle's
+whole-layer restatement, on a shape small enough for the CPU to finish in seconds."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from tests.gpu_util import make_dy, make_w, make_x, rel_fro, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("cache", [False, True])
+def test_linear_fwd_bwd_matches_oracle(cache):
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.linear import FP4LinearFn, LinCtx, WeightCache, _RHT_SIGNS, sr_seed
+    T, K, N = 512, 256, 384
+    x, w, gy = make_x(1, T, K), make_w(2, N, K), make_dy(3, T, N)
+    LinCtx.seed, LinCtx.wgrad_dtype = 12, torch.float32
+    lid = 3
+    xd = to_dev(x).requires_grad_(True)
+    wd = to_dev(w).requires_grad_(True)
+    wc = WeightCache(wd).refresh() if cache else None
+    y = FP4LinearFn.apply(xd, wd, lid, wc)
+    y.backward(to_dev(gy))
+    seed = sr_seed(lid)
+    assert seed == (12 * 1000003 + 3 * 7919) & 0xFFFFFFFF
+    ry, rgx, rgw = O.linear_fwd_bwd(x, w, gy, _RHT_SIGNS, seed=seed, sr_mode=O.SR_DITHER_NVQ)
+    # same codes/scales on both sides, so only accumulation order and the bf16 output cast differ
+    assert rel_fro(y.float().cpu().numpy(), ry) <= 4e-3
+    assert rel_fro(xd.grad.float().cpu().numpy(), rgx) <= 4e-3
+    assert wd.grad.dtype == torch.float32 or wd.grad.dtype == torch.bfloat16
+    assert rel_fro(wd.grad.float().cpu().numpy(), rgw) <= 4e-3
+    # and the quantized layer tracks the exact one within FP4 noise
+    assert rel_fro(ry, x @ w.T) < 0.15
+    _lib.check_status()
+    LinCtx.wgrad_dtype = torch.bfloat16
+
+
+def test_linear_module_bf16_switch():
+    from nvfp4_training_b200.linear import Linear, LinCtx
+    torch.manual_seed(0)
+    lin = Linear(256, 384, std=0.02).cuda().bfloat16()
+    x = torch.randn(2, 64, 256, device="cuda", dtype=torch.bfloat16)
+    LinCtx.fp4 = True
+    y4 = lin(x)
+    LinCtx.fp4 = False
+    y16 = lin(x)
+    LinCtx.fp4 = True
+    assert y4.shape == (2, 64, 384)
+    assert ((y4.float() - y16.float()).norm() / y16.float().norm()).item() < 0.2

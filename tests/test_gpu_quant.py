@@ -1,0 +1,221 @@
+"""GPU parity of the quantizer kernels against the CPU oracle: codes, scale bytes and tensor scales
+bit-exact for round-to-nearest and for stochastic rounding given the same random bits."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from tests.gpu_util import bf16_round, make_dy, make_w, make_x, to_dev, u8
+
+pytestmark = pytest.mark.gpu
+
+ROW_CASES = ["normal_outliers", "weights_small", "student_t", "ties", "range", "zeros", "tiny", "negzero"]
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from nvfp4_training_b200 import _lib, fp4ops, nvq
+    _lib.load()
+    return nvq, fp4ops, _lib
+
+
+def check_nvq(q, codes, scales, gs, R, C):
+    assert np.array_equal(u8(q.d), codes)
+    assert np.array_equal(O.unswizzle_scales(u8(q.s), R, C // 16), scales)
+    assert q.gs.item() == float(gs)
+
+
+def test_amax(mods):
+    nvq, _, _ = mods
+    for n, seed in [(8, 0), (4096, 1), (128 * 2048, 2), (1 << 22, 3), ((1 << 22) + 8 * 77, 4)]:
+        rng = np.random.default_rng(seed)
+        x = bf16_round(rng.standard_normal(n).astype(np.float32) * 3)
+        x[rng.integers(n)] = -77.5
+        assert nvq.amax(to_dev(x)).item() == float(O.amax_f32(x))
+    assert nvq.amax(torch.zeros(64, dtype=torch.bfloat16, device="cuda")).item() == 0.0
+    out = torch.full((1,), 9.0, device="cuda")
+    nvq.amax(to_dev(np.full(16, 0.5, dtype=np.float32)), out=out)
+    assert out.item() == 0.5
+
+
+@pytest.mark.parametrize("name", ROW_CASES)
+def test_rows_rn_golden_inputs(mods, golden, name):
+    nvq, fp4ops, _ = mods
+    x = O.bf16_bits_to_f32(golden[f"rows_{name}_x"])
+    R, C = x.shape
+    codes, scales, gs = O.quant_rows(x)
+    q = nvq.quant_rows(to_dev(x))
+    check_nvq(q, codes, scales, gs, R, C)
+    # dequantized result equals the reference's torch fake-quant, bit for bit
+    assert np.array_equal(nvq.dequant(q).cpu().numpy(), golden[f"rows_{name}_dq"])
+    # linear-scale flavour
+    qf = fp4ops.quant_rows(to_dev(x))
+    assert np.array_equal(u8(qf.d), codes) and np.array_equal(u8(qf.s), scales)
+    assert np.array_equal(fp4ops.dequant(qf).cpu().numpy(), golden[f"rows_{name}_dq"])
+
+
+@pytest.mark.parametrize("R,C,seed", [(128, 64, 0), (256, 576, 1), (4096, 2048, 0), (384, 5632, 2)])
+def test_rows_rn_shapes(mods, R, C, seed):
+    nvq, _, _ = mods
+    x = make_x(seed, R, C)
+    codes, scales, gs = O.quant_rows(x)
+    check_nvq(nvq.quant_rows(to_dev(x)), codes, scales, gs, R, C)
+
+
+def test_rows_strided_and_shared_amax(mods):
+    nvq, _, _ = mods
+    x = make_dy(5, 256, 512)
+    big = to_dev(np.concatenate([x, x], axis=1))
+    view = big[:, 512:]                       # row stride 1024, offset 512
+    am = nvq.amax(to_dev(x))
+    am4 = am * 4
+    codes, scales, gs = O.quant_rows(x, amax=O.amax_f32(x) * np.float32(4))
+    check_nvq(nvq.quant_rows(view, am=am4), codes, scales, gs, 256, 512)
+
+
+@pytest.mark.parametrize("top", [48.0, 2688.0])
+def test_rows_fast_path_boundaries(mods, top):
+    """Values whose scaled magnitude sits exactly on, or one bf16 step around, every rounding
+    boundary of the E2M1 grid: the reciprocal fast path must fall back to the exact divisions."""
+    nvq, _, _ = mods
+    rng = np.random.default_rng(11)
+    bounds = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    x = np.zeros((128, 64), dtype=np.float32)
+    for r in range(128):
+        for b in range(4):
+            blk = rng.choice(bounds, 16) * rng.choice([-1.0, 1.0], 16)
+            blk[rng.integers(16)] = 6.0                      # block max -> scale exactly 2^k
+            x[r, b * 16:(b + 1) * 16] = blk * 2.0 ** rng.integers(-3, 4)
+    x[0, 0] = top          # tensor amax: 2688 makes gs = 1, so every scaled value is an exact tie
+    x = bf16_round(x)
+    codes, scales, gs = O.quant_rows(x)
+    check_nvq(nvq.quant_rows(to_dev(x)), codes, scales, gs, 128, 64)
+
+
+@pytest.mark.parametrize("mode_name", ["SR_DITHER_NVQ", "SR_DITHER_FP4K"])
+@pytest.mark.parametrize("seed", [0, 7, 0xDEADBEEF])
+def test_rows_sr_dither_bit_exact(mods, mode_name, seed):
+    nvq, fp4ops, L = mods
+    x = make_dy(3, 256, 320 if mode_name == "SR_DITHER_FP4K" else 384)
+    R, C = x.shape
+    codes, scales, gs = O.quant_rows(x, sr_mode=getattr(O, mode_name), seed=seed)
+    if mode_name == "SR_DITHER_NVQ":
+        assert nvq.SR_MODE == L.ROUND_SR_DITHER
+        check_nvq(nvq.quant_rows(to_dev(x), sr=True, seed=seed), codes, scales, gs, R, C)
+    else:
+        assert fp4ops.SR_MODE == L.ROUND_SR_DITHER_K
+        q = fp4ops.quant_rows(to_dev(x), sr=True, seed=seed)
+        assert np.array_equal(u8(q.d), codes) and np.array_equal(u8(q.s), scales)
+
+
+def test_rows_sr_unbiased_mean_of_64(mods):
+    """llm-1b/test_nvq.py:19-22 / small-model/test_fp4ops.py:12-16: the mean of 64 SR
+    quantizations is much closer to x than one round-to-nearest quantization.
+    Stated bound: rel-err(mean of 64) <= 1/4 rel-err(RN)."""
+    nvq, _, _ = mods
+    x = to_dev(make_dy(9, 512, 384))
+    xf = x.float()
+    acc = torch.zeros_like(xf)
+    for s in range(64):
+        acc += nvq.dequant(nvq.quant_rows(x, sr=True, seed=s))
+    e_sr = ((acc / 64 - xf).norm() / xf.norm()).item()
+    e_rn = ((nvq.dequant(nvq.quant_rows(x)) - xf).norm() / xf.norm()).item()
+    assert e_sr <= 0.25 * e_rn, (e_sr, e_rn)
+
+
+def test_w2d_bf16(mods, golden):
+    nvq, _, _ = mods
+    w = O.bf16_bits_to_f32(golden["w2d_bf16_w"])
+    wp = np.zeros((128, 256), dtype=np.float32)
+    wp[:, :192] = w                                            # swizzled layout wants K % 128 == 0
+    q, s, qt, st, gs = O.quant_w2d(wp)
+    a, b = nvq.quant_w2d(to_dev(wp))
+    check_nvq(a, q, s, gs, 128, 256)
+    check_nvq(b, qt, st, gs, 256, 128)
+    assert np.array_equal(nvq.dequant(a).cpu().numpy()[:, :192], golden["w2d_bf16_dq"])
+    assert (nvq.dequant(b) - nvq.dequant(a).t()).abs().max().item() == 0.0     # llm-1b/test_nvq.py:11
+    only_t = nvq.quant_w2d(to_dev(wp), want=(False, True))
+    assert only_t[0] is None and np.array_equal(u8(only_t[1].d), qt)
+
+
+@pytest.mark.parametrize("N,K,seed", [(2048, 2048, 0), (384, 1152, 1)])
+def test_w2d_shapes(mods, N, K, seed):
+    nvq, _, _ = mods
+    w = make_w(seed, N, K)
+    q, s, qt, st, gs = O.quant_w2d(w)
+    a, b = nvq.quant_w2d(to_dev(w))
+    check_nvq(a, q, s, gs, N, K)
+    check_nvq(b, qt, st, gs, K, N)
+
+
+def test_w2d_fp32_linear(mods, golden):
+    _, fp4ops, _ = mods
+    w = golden["w2d_f32_w"]
+    q, s, qt, st, gs = O.quant_w2d(w)
+    a, b = fp4ops.quant_w2d(torch.from_numpy(w).cuda())
+    assert np.array_equal(u8(a.d), q) and np.array_equal(u8(a.s), s)
+    assert np.array_equal(u8(b.d), qt) and np.array_equal(u8(b.s), st)
+    assert np.array_equal(fp4ops.dequant(a).cpu().numpy(), golden["w2d_f32_dq"])     # small-model/test_fp4ops.py:18-21
+    assert (fp4ops.dequant(b) - fp4ops.dequant(a).t()).abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("M,C,seed,kind", [(64, 128, 0, "int"), (256, 384, 1, "t"), (4096, 256, 2, "n"), (16384, 128, 3, "t")])
+def test_cols_rht_rn(mods, golden, M, C, seed, kind):
+    nvq, fp4ops, _ = mods
+    signs = 0b1010011010110001
+    if kind == "int":
+        x = O.bf16_bits_to_f32(golden["rht_int_x"])
+    elif kind == "t":
+        x = make_dy(seed, M, C)
+    else:
+        x = make_x(seed, M, C)
+    codes, scales, gs = O.quant_cols_rht(x, signs)
+    q = nvq.quant_cols_rht(to_dev(x), signs)
+    check_nvq(q, codes, scales, gs, C, M)
+    if kind == "int":
+        assert np.array_equal(nvq.dequant(q).cpu().numpy(), golden["rht_int_dq"])
+    qf = fp4ops.quant_cols_rht(to_dev(x), signs)
+    assert np.array_equal(u8(qf.d), codes) and np.array_equal(u8(qf.s), scales) and qf.k == 4.0
+
+
+@pytest.mark.parametrize("signs", [0, 0xFFFF, 0xA5C3])
+def test_cols_rht_sr_dither_bit_exact(mods, signs):
+    nvq, fp4ops, _ = mods
+    x = make_dy(4, 128, 256)
+    am = np.float32(O.amax_f32(x) * np.float32(1.5))
+    codes, scales, gs = O.quant_cols_rht(x, signs, amax=am, sr_mode=O.SR_DITHER_NVQ, seed=5)
+    amt = torch.tensor([float(am)], device="cuda")
+    check_nvq(nvq.quant_cols_rht(to_dev(x), signs, sr=True, seed=5, am=amt), codes, scales, gs, 256, 128)
+    codes, scales, gs = O.quant_cols_rht(x, signs, amax=am, sr_mode=O.SR_DITHER_FP4K, seed=5)
+    q = fp4ops.quant_cols_rht(to_dev(x), signs, sr=True, seed=5, amax=amt)
+    assert np.array_equal(u8(q.d), codes) and np.array_equal(u8(q.s), scales)
+
+
+def test_swizzle_scales_kernel(mods):
+    _, _, L = mods
+    rng = np.random.default_rng(0)
+    s = rng.integers(0, 256, (256, 40), dtype=np.uint8)
+    pad = torch.from_numpy(np.concatenate([s, s], 1)).cuda()
+    view = pad[:, 40:]
+    out = torch.empty(256 * 40, dtype=torch.uint8, device="cuda")
+    L.check(L.load().nvfp4_swizzle_scales(view.data_ptr(), view.stride(0), 256, 40, out.data_ptr(), L.stream()), "swz")
+    assert np.array_equal(out.cpu().numpy(), O.swizzle_scales(s))
+
+
+def test_rejects_bad_arguments(mods):
+    nvq, fp4ops, L = mods
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(AssertionError):
+        nvq.quant_rows(x[:100])                                  # R % 128 (llm-1b/nvq.py:50)
+    with pytest.raises(AssertionError):
+        nvq.quant_cols_rht(x, 0)                                 # C % 128 (llm-1b/nvq.py:64)
+    with pytest.raises(L.Nvfp4Error):
+        nvq.quant_rows(torch.zeros(128, 64, dtype=torch.bfloat16))   # CPU tensor: no fallback
+    d = torch.empty(128 * 32 + 1, dtype=torch.uint8, device="cuda")
+    s = torch.empty(128 * 4, dtype=torch.uint8, device="cuda")
+    am = torch.ones(1, device="cuda")
+    lib = L.load()
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr() + 1, s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -3
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 48, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -2
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr(), s.data_ptr(), 7, am.data_ptr(), None, 0, 0, L.stream()) == -4
+    assert lib.nvfp4_quant_rows(None, 64, 128, 64, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -1
