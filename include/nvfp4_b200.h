@@ -109,6 +109,15 @@ int nvfp4_quant_w2d(const void* w, int w_dtype, int N, int K, void* q, void* s, 
                     int scale_layout, const float* amax, float* gs_out, void* stream);
 
 /*
+ * The stochastic-rounding convert on its own, with caller-supplied random bits: group i turns
+ * y[4i..4i+3] (FP32, already divided by the scales) into 16 bits of E2M1 codes, y[4i] in the lowest
+ * nibble, using `cvt.rs.satfinite.e2m1x4.f32` with the random word rbits[i].  It exists so that the
+ * rounding function can be checked bit-for-bit against a CPU model on identical random bits.
+ * No reference counterpart (sm_120 has no cvt.rs: llm-1b/nvq.cu:31).  y 16-byte aligned.
+ */
+int nvfp4_e2m1x4_sr(const float* y, const unsigned* rbits, void* codes, long long n4, void* stream);
+
+/*
  * Row-major scale bytes [R, C16] (row stride lds bytes) -> the swizzled layout.
  * No reference kernel: it converts the llm-1b/fp4k.cu scale layout into the llm-1b/nvq.cu one
  * (inverse of `nvq.unswizzle`, llm-1b/nvq.py:103-107).  Requires R % 128 == 0, C16 % 4 == 0.

@@ -28,6 +28,7 @@ SIGNATURES = {
     "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp]),
     "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp]),
     "nvfp4_quant_w2d": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
+    "nvfp4_e2m1x4_sr": (_i, [_vp, _vp, _vp, _ll, _vp]),
     "nvfp4_swizzle_scales": (_i, [_vp, _ll, _i, _i, _vp, _vp]),
     "nvfp4_gemm": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _i, _vp, _vp]),
     "nvfp4_gemm_force_tile_n": (_i, [_i]),

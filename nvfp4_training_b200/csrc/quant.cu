@@ -227,6 +227,15 @@ __global__ void __launch_bounds__(256) swizzle_scales_kernel(const unsigned char
   }
 }
 
+// ------------------------------------------------------------------------------------------ raw SR convert
+__global__ void __launch_bounds__(256) e2m1x4_sr_kernel(const float4* __restrict__ y, const u32* __restrict__ rbits,
+                                                         unsigned short* __restrict__ out, long long n4) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 v = y[i];
+  out[i] = (unsigned short)e2m1x4_rs(v.x, v.y, v.z, v.w, rbits[i]);
+}
+
 static int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -363,6 +372,19 @@ extern "C" int nvfp4_swizzle_scales(const void* s_linear, long long lds, int R, 
   if (blocks > cap) blocks = cap;
   swizzle_scales_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned char*>(s_linear), lds, R, C16, static_cast<unsigned char*>(s_swizzled));
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_e2m1x4_sr(const float* y, const unsigned* rbits, void* codes, long long n4, void* stream) {
+  if (!y || !rbits || !codes) return NVFP4_ERR_NULL;
+  if (n4 < 0) return NVFP4_ERR_SHAPE;
+  if (!aligned16(y) || (reinterpret_cast<uintptr_t>(rbits) & 3u) || (reinterpret_cast<uintptr_t>(codes) & 1u)) return NVFP4_ERR_ALIGN;
+  if (n4 == 0) return NVFP4_OK;
+  const long long blocks = (n4 + 255) / 256;
+  if (blocks > 0x7FFFFFFFLL) return NVFP4_ERR_TOO_LARGE;
+  e2m1x4_sr_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(y), rbits, static_cast<unsigned short*>(codes), n4);
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;
 }
