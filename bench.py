@@ -1,0 +1,400 @@
+"""Benchmark of the NVFP4 linear-layer hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
+    python bench.py --impl reference --steps K --warmup W     (the reference's CPU torch path, host cores)
+
+Workload (both arms): every NVFP4 linear of the 1.0B architecture -- 20 blocks x {qkv, o, gate/up,
+down} + the 49,152-row LM head -- forward and backward (fprop, dgrad, wgrad with RHT16 and stochastic
+rounding), global batch 32 x 2048 tokens sharded by rows over N GPUs with replicated random-init
+weights, FP32 weight gradients all-reduced with NCCL.  A step re-quantizes all weights once, clears
+dW, runs the rank's microbatches and the all-reduce.  Metric: tokens/s of the whole job.
+
+Rank 0 prints ONE JSON line.  Extra keys: `roofline` (the GEMM, timed alone with CUDA events),
+`cpu_baseline` (the torch restatement of the reference on a bounded sample, N = 1 only), `e2e`
+(same step with the batch copied from pinned host memory and a result read back every step),
+`detail` (per-kernel-class numbers).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GLOBAL_TOKENS = 32 * 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        if sm:
+            busy = [s for s, p in zip(sm, power) if p > 0.5 * max(power)] or sm
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power))
+        return out
+
+
+# ------------------------------------------------------------------------------------------ reference arm (CPU)
+def cpu_reference_sample(tokens, threads):
+    """One bounded sample of the workload on the host: one block's four projections (weights
+    re-quantized, `tokens` rows forward + backward) with the torch restatement of the reference.
+    Returns (seconds for weight quantization, seconds for the token pass)."""
+    import torch
+    from oracle import torch_ref as T
+    from nvfp4_training_b200.stack import StackConfig
+    torch.set_num_threads(threads)
+    cfg = StackConfig()
+    g = torch.Generator().manual_seed(0)
+    t_w = t_tok = 0.0
+    for name, N, K, std in cfg.block_shapes():
+        w = (torch.randn(N, K, generator=g) * std).bfloat16()
+        x = torch.randn(tokens, K, generator=g).bfloat16()
+        gy = (torch.randn(tokens, N, generator=g) * 1e-3).bfloat16()
+        t0 = time.perf_counter()
+        wq = T.nvfp4_2d(w)
+        t1 = time.perf_counter()
+        T.linear_fwd_bwd(x, wq, gy, 0b1010011010110001, stochastic=True)
+        t2 = time.perf_counter()
+        t_w += t1 - t0
+        t_tok += t2 - t1
+    return t_w, t_tok
+
+
+def cpu_tokens_per_s(t_w, t_tok, tokens):
+    """Extrapolate the one-block sample to the full step: weights of all 20 blocks + head once,
+    65,536 tokens through all of them, scaled by parameter count and FLOPs."""
+    from nvfp4_training_b200.stack import StackConfig
+    cfg = StackConfig()
+    block_params = sum(n * k for _, n, k, _ in cfg.block_shapes())
+    scale = cfg.n_params() / block_params
+    step_s = t_w * scale + t_tok * scale * (GLOBAL_TOKENS / tokens)
+    return GLOBAL_TOKENS / step_s
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    tokens = 256
+    for _ in range(max(args.warmup, 0) and 1):
+        cpu_reference_sample(tokens, threads)
+    vals = []
+    t_all = time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        t_w, t_tok = cpu_reference_sample(tokens, threads)
+        vals.append(cpu_tokens_per_s(t_w, t_tok, tokens))
+    dt = (time.perf_counter() - t_all) / max(1, args.steps)
+    v = statistics.median(vals)
+    sample = (f"one block (qkv,o,gate/up,down) weight quant + {tokens} tokens fwd+bwd per step with the torch "
+              "restatement of small-model/model_ref.py, extrapolated to 20 blocks + LM head and 65,536 tokens "
+              "by parameter count")
+    print(json.dumps({
+        "impl": "reference", "metric": "tokens/s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": GLOBAL_TOKENS / v * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)+ue4m3 scales, fp32 math on CPU", "data": "synthetic",
+        "config": workload_config(args.gpus, None, None),
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+                         "sample_seconds": dt},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(n_gpus, microbatch, n_micro):
+    return {"workload": "NVFP4 linear fwd+bwd (fprop, dgrad, wgrad+RHT16, SR grads) of every linear of the 1.0B "
+                        "architecture: 20 x {qkv 2048->3072, o 2048->2048, gate/up 2048->11264, down 5632->2048} + "
+                        "LM head 2048->49152; weights re-quantized once per step; FP32 dW all-reduce",
+            "global_batch_tokens": GLOBAL_TOKENS, "seq_len": 2048, "sequences": 32,
+            "parallelism": f"dp{n_gpus} (token rows sharded, weights replicated)",
+            "microbatch_tokens": microbatch, "microbatches_per_rank": n_micro,
+            "l2": "per-step working set (2 GB bf16 weights, 1.1 GB packed weights, 4 GB dW, activations) >> 126 MB L2; "
+                  "isolated-kernel timings rotate operand sets larger than L2"}
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def time_events(fn, iters, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def isolated_kernels(cfg, T, peaks):
+    """Time the GEMM and the quantizers alone (CUDA events on the launch stream), rotating operand
+    sets so consecutive launches do not find their inputs in L2.  Returns the roofline object for
+    the GEMM and a detail dict."""
+    import torch
+    from nvfp4_training_b200 import nvq
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(7)
+    shapes = [(n, N, K) for n, N, K, _ in cfg.block_shapes()] + ([("head", cfg.vocab, cfg.d)] if cfg.lm_head else [])
+    counts = {n: cfg.layers for n, _, _ in shapes}
+    counts["head"] = 1
+    detail, tot_flops, tot_time = {}, 0.0, 0.0
+
+    def sets_for(nbytes):
+        return max(2, min(8, int(256e6 // max(nbytes, 1)) + 1))
+
+    for name, N, K in shapes:
+        for pas, (M_, N_, K_, fp32) in {"fprop": (T, N, K, False), "dgrad": (T, K, N, False), "wgrad": (N, K, T, True)}.items():
+            nset = sets_for((M_ + N_) * K_ * 0.5625 + M_ * N_ * (4 if fp32 else 2))
+            ops = []
+            for _ in range(nset):
+                a = nvq.quant_rows(torch.randn(M_, K_, generator=g, device=dev).bfloat16())
+                b = nvq.quant_rows(torch.randn(N_, K_, generator=g, device=dev).bfloat16())
+                out = torch.zeros(M_, N_, dtype=torch.float32 if fp32 else torch.bfloat16, device=dev)
+                ops.append((a, b, out))
+            it = [0]
+
+            def run():
+                a, b, out = ops[it[0] % nset]
+                it[0] += 1
+                nvq.mm(a, b, out_dtype=out.dtype, out=out, accumulate=fp32)
+            t = time_events(run, iters=max(10, 2 * nset))
+            fl = 2.0 * M_ * N_ * K_
+            detail[f"gemm_{name}_{pas}"] = {"M": M_, "N": N_, "K": K_, "us": t * 1e6, "tflops": fl / t / 1e12}
+            tot_flops += fl * counts[name]
+            tot_time += t * counts[name]
+            del ops
+    achieved = tot_flops / tot_time / 1e12
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    roof = {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
+            "traffic": None, "kernel": "gemm_nvf4_kernel (tcgen05.mma kind::mxf4nvf4 block16)",
+            "peak_basis": "4 x cuBLAS bf16 burst TFLOP/s (dense FP4 : bf16 = 4 : 1 on B200)",
+            "frac_of_nominal_9000": achieved / 9000.0,
+            "how": "all 15 GEMM shapes of the step timed alone with CUDA events, weighted by launches per step"}
+
+    # quantizers on the largest activation of a block: [T, 5632] X and [T, 11264] dY
+    x = [torch.randn(T, 5632, generator=g, device=dev).bfloat16() for _ in range(4)]
+    am = [nvq.amax(t) for t in x]
+    n = T * 5632
+    it = [0]
+
+    def q(fn):
+        def run():
+            i = it[0] % 4
+            it[0] += 1
+            fn(x[i], am[i])
+        return time_events(run, iters=20)
+    t = q(lambda t, a: nvq.amax(t))
+    detail["amax"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.0 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_rows(t, am=a))
+    detail["quant_rows_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_rows(t, sr=True, seed=1, am=a))
+    detail["quant_rows_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_cols_rht(t, 0xA6B1, am=a))
+    detail["quant_cols_rht_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_cols_rht(t, 0xA6B1, sr=True, seed=1, am=a))
+    detail["quant_cols_rht_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    w = [torch.randn(11264, 2048, generator=g, device=dev).bfloat16() for _ in range(4)]
+    it = [0]
+
+    def wq():
+        i = it[0] % 4
+        it[0] += 1
+        nvq.quant_w2d(w[i], am=am[0])
+    t = time_events(wq, iters=20)
+    detail["quant_w2d"] = {"elts": 11264 * 2048, "us": t * 1e6, "gbs": 11264 * 2048 * 3.125 / t / 1e9}
+    detail["hbm_peak_gbs"] = peaks["hbm_gbs"]
+    return roof, detail
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.stack import LinearStack, StackConfig, shard_plan
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}: launch with torch.distributed.run"
+    torch.cuda.set_device(local)
+    _lib.load()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peak_src = load_peaks()
+
+    cfg = StackConfig(layers=args.layers) if args.layers else StackConfig()
+    plan = shard_plan(world, rank, GLOBAL_TOKENS, args.microbatch)
+    mb, n_micro = plan["microbatch"], plan["n_micro"]
+    stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=rank, use_graphs=not args.no_graphs)
+    if not args.no_graphs:
+        stack.capture()
+    do_ar = world > 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        stack.step(n_micro, do_ar)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        stack.step(n_micro, do_ar)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    _lib.check_status()
+
+    # ---- end to end: the batch comes from pinned host memory every microbatch, a result goes back every step
+    host_x = torch.randn(mb, cfg.d).bfloat16().pin_memory()
+    host_out = torch.empty(1024, dtype=torch.float32).pin_memory()
+    last = stack.blocks[-1][-1]
+
+    def e2e_step():
+        stack.refresh_weights()
+        stack.zero_grads()
+        for m in range(n_micro):
+            stack.x_pool["qkv"].copy_(host_x, non_blocking=True)
+            stack.microbatch(last=(m == n_micro - 1), do_allreduce=do_ar)
+        if do_ar:
+            torch.cuda.current_stream().wait_stream(stack.comm_stream)
+        host_out.copy_(last.gw.view(-1)[:1024], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / e2e_steps
+
+    t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = t.tolist()
+
+    roof = detail = cpu = None
+    if rank == 0:
+        del stack
+        torch.cuda.empty_cache()
+        roof, detail = isolated_kernels(cfg, mb, peaks)
+        roof["peak_source"] = peak_src
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            cpu_reference_sample(64, threads)
+            t0 = time.perf_counter()
+            t_w, t_tok = cpu_reference_sample(256, threads)
+            cpu = {"value": cpu_tokens_per_s(t_w, t_tok, 256), "unit": "tokens/s", "cores": threads, "kind": "port",
+                   "sample": "one block's weight quant + 256 tokens fwd+bwd with the torch restatement of "
+                             "small-model/model_ref.py, extrapolated by parameter count to the full step",
+                   "sample_seconds": time.perf_counter() - t0}
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        val = GLOBAL_TOKENS / (ms * 1e-3)
+        flops = cfg.flops_per_token() * GLOBAL_TOKENS
+        line = {
+            "metric": "tokens/s", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp4 (e2m1, ue4m3 block scales, fp32 accumulate)", "data": "synthetic",
+            "config": workload_config(world, mb, n_micro),
+            "tflops_per_gpu": flops / (ms * 1e-3) / world / 1e12,
+            "frac_fp4_peak_per_gpu": flops / (ms * 1e-3) / world / 1e12 / (4.0 * peaks["bf16_tflops_sustained"]),
+            "frac_fp4_nominal_9000": flops / (ms * 1e-3) / world / 1e12 / 9000.0,
+            "e2e": {"value": GLOBAL_TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": n_micro * mb * cfg.d * 2, "d2h_bytes_per_step": 4096, "steps": e2e_steps},
+            "gpu_launches": args.steps * (n_micro * (cfg.layers * 4 + 1) * 9 + (cfg.layers * 4 + 1) * 2),
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "detail": detail,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--microbatch", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (not a valid bench number)")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

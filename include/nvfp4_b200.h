@@ -77,13 +77,16 @@ int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream);
  * codes [R, C/2] bytes, contiguous.  scales: R*C/16 bytes in `scale_layout`.
  * amax: device FP32 scalar, max|x| of the whole tensor (or a larger bound).
  * gs_out: optional device FP32 scalar that receives the tensor scale gs (`nvq._gs`, llm-1b/nvq.py:43-44).
+ * seed / seed_dev: stochastic-rounding seed; when seed_dev (a device word) is given it replaces
+ * `seed`, so a captured CUDA graph can be replayed with a fresh seed per microbatch
+ * (the reference changes `LinCtx.seed` on the host every microbatch, llm-1b/model.py:36-39,59).
  * Requires C % 16 == 0, ldx % 8 == 0, x 16-byte aligned; SWIZZLED also R % 128 == 0, C % 64 == 0.
  * Arithmetic: gs = max(amax/2688, 1e-30); bs = e4m3(min((max16|x|/gs)/6, 448));
  * code = round((x/gs)/bs) -- the operation order of small-model/model_ref.py:39-47, IEEE FP32.
  */
 int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, void* scales,
                      int scale_layout, const float* amax, float* gs_out, int rounding, unsigned seed,
-                     void* stream);
+                     const unsigned* seed_dev, void* stream);
 
 /*
  * Quantization of x^T along the token dim after a 16-point random Hadamard transform:
@@ -95,7 +98,7 @@ int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, vo
  */
 int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales, int scale_layout,
                          const float* amax, float* gs_out, unsigned signs, int rounding, unsigned seed,
-                         void* stream);
+                         const unsigned* seed_dev, void* stream);
 
 /*
  * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,

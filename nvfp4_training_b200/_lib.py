@@ -25,8 +25,8 @@ SIGNATURES = {
     "nvfp4_version": (_i, []),
     "nvfp4_error_string": (_c.c_char_p, [_i]),
     "nvfp4_amax_bf16": (_i, [_vp, _ll, _vp, _vp]),
-    "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp]),
-    "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp]),
+    "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp, _vp]),
+    "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp, _vp]),
     "nvfp4_quant_w2d": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
     "nvfp4_e2m1x4_sr": (_i, [_vp, _vp, _vp, _ll, _vp]),
     "nvfp4_swizzle_scales": (_i, [_vp, _ll, _i, _i, _vp, _vp]),
@@ -67,6 +67,14 @@ def check(rc, what):
 
 def ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def seed_args(seed):
+    """(host seed, device seed pointer): a CUDA int32/uint32 tensor selects the device-side seed."""
+    if isinstance(seed, torch.Tensor):
+        assert seed.is_cuda and seed.numel() >= 1 and seed.element_size() == 4
+        return 0, seed.data_ptr()
+    return seed & 0xFFFFFFFF, None
 
 
 def stream():

@@ -66,7 +66,9 @@ template <int ROUNDING>
 __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                           uint2* __restrict__ codes, unsigned char* __restrict__ scales,
                                                           const float* __restrict__ amax, int R, int C, int linear,
-                                                          u32 seed, float* __restrict__ gs_out) {
+                                                          u32 seed, const u32* __restrict__ seed_dev,
+                                                          float* __restrict__ gs_out) {
+  if (ROUNDING != NVFP4_ROUND_NEAREST && seed_dev) seed = __ldg(seed_dev);
   const int lane = threadIdx.x & 31;
   const int nchunk = C >> 3, nblk = C >> 4;
   const int nseg = (nchunk + 63) >> 6;
@@ -113,7 +115,9 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
                                                               unsigned char* __restrict__ codes,
                                                               unsigned char* __restrict__ scales,
                                                               const float* __restrict__ amax, int M, int C, int linear,
-                                                              u32 signs, u32 seed, float* __restrict__ gs_out) {
+                                                              u32 signs, u32 seed, const u32* __restrict__ seed_dev,
+                                                              float* __restrict__ gs_out) {
+  if (ROUNDING != NVFP4_ROUND_NEAREST && seed_dev) seed = __ldg(seed_dev);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cchunk = blockIdx.x * 16 + (lane & 15);            // 8-column chunk index
   const int mb = blockIdx.y * 16 + warp * 2 + (lane >> 4);     // 16-token block index
@@ -273,7 +277,7 @@ extern "C" int nvfp4_amax_bf16(const void* x, long long n, float* out, void* str
 
 extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, void* scales,
                                 int scale_layout, const float* amax, float* gs_out, int rounding, unsigned seed,
-                                void* stream) {
+                                const unsigned* seed_dev, void* stream) {
   if (!x || !codes || !scales || !amax) return NVFP4_ERR_NULL;
   if (scale_layout != NVFP4_SCALES_SWIZZLED && scale_layout != NVFP4_SCALES_LINEAR) return NVFP4_ERR_ENUM;
   if (rounding < NVFP4_ROUND_NEAREST || rounding > NVFP4_ROUND_SR_HW) return NVFP4_ERR_ENUM;
@@ -292,13 +296,13 @@ extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void
   unsigned char* sp = static_cast<unsigned char*>(scales);
   switch (rounding) {
     case NVFP4_ROUND_NEAREST:
-      quant_rows_kernel<NVFP4_ROUND_NEAREST><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+      quant_rows_kernel<NVFP4_ROUND_NEAREST><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
     case NVFP4_ROUND_SR_DITHER:
-      quant_rows_kernel<NVFP4_ROUND_SR_DITHER><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+      quant_rows_kernel<NVFP4_ROUND_SR_DITHER><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
     case NVFP4_ROUND_SR_DITHER_K:
-      quant_rows_kernel<NVFP4_ROUND_SR_DITHER_K><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+      quant_rows_kernel<NVFP4_ROUND_SR_DITHER_K><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
     default:
-      quant_rows_kernel<NVFP4_ROUND_SR_HW><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, gs_out); break;
+      quant_rows_kernel<NVFP4_ROUND_SR_HW><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
   }
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;
@@ -306,7 +310,7 @@ extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void
 
 extern "C" int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales, int scale_layout,
                                     const float* amax, float* gs_out, unsigned signs, int rounding, unsigned seed,
-                                    void* stream) {
+                                    const unsigned* seed_dev, void* stream) {
   if (!x || !codes || !scales || !amax) return NVFP4_ERR_NULL;
   if (scale_layout != NVFP4_SCALES_SWIZZLED && scale_layout != NVFP4_SCALES_LINEAR) return NVFP4_ERR_ENUM;
   if (rounding < NVFP4_ROUND_NEAREST || rounding > NVFP4_ROUND_SR_HW) return NVFP4_ERR_ENUM;
@@ -324,13 +328,13 @@ extern "C" int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, vo
   signs &= 0xFFFFu;
   switch (rounding) {
     case NVFP4_ROUND_NEAREST:
-      quant_cols_rht_kernel<NVFP4_ROUND_NEAREST><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+      quant_cols_rht_kernel<NVFP4_ROUND_NEAREST><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, seed_dev, gs_out); break;
     case NVFP4_ROUND_SR_DITHER:
-      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, seed_dev, gs_out); break;
     case NVFP4_ROUND_SR_DITHER_K:
-      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER_K><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_DITHER_K><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, seed_dev, gs_out); break;
     default:
-      quant_cols_rht_kernel<NVFP4_ROUND_SR_HW><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, gs_out); break;
+      quant_cols_rht_kernel<NVFP4_ROUND_SR_HW><<<grid, 256, 0, st>>>(xp, cp, sp, amax, M, C, linear, signs, seed, seed_dev, gs_out); break;
   }
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;

@@ -36,7 +36,7 @@ def quant_rows(x, sr=False, seed=0, amax=None):
     d = torch.empty(R, C // 2, dtype=torch.uint8, device=x.device)
     s = torch.empty(R, C // 16, dtype=torch.uint8, device=x.device)
     L.check(L.load().nvfp4_quant_rows(L.ptr(x), C, R, C, L.ptr(d), L.ptr(s), L.SCALES_LINEAR, L.ptr(a),
-                                      None, SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()), "quant_rows")
+                                      None, SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed), L.stream()), "quant_rows")
     return Q(d, s, a)
 
 
@@ -51,7 +51,7 @@ def quant_cols_rht(x, signs, sr=False, seed=0, amax=None):
     d = torch.empty(C, M // 2, dtype=torch.uint8, device=x.device)
     s = torch.empty(C, M // 16, dtype=torch.uint8, device=x.device)
     L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_LINEAR, L.ptr(a), None, signs & 0xFFFF,
-                                          SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()),
+                                          SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed), L.stream()),
             "quant_cols_rht")
     return Q(d, s, a, 4.0)
 

@@ -44,31 +44,49 @@ class WeightCache:
         return self
 
 
+def linear_fwd(x, qw):
+    """fprop of llm-1b/model.py:46-53 with W already quantized: returns (y bf16 [T, N], amax(x)).
+    amax(x) is handed back so the backward pass does not recompute it (same value)."""
+    am = nvq.amax(x.contiguous())
+    return nvq.mm(nvq.quant_rows(x, am=am), qw), am
+
+
+def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS):
+    """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
+    (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
+    gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
+    returned; otherwise a new tensor of `wgrad_dtype` is returned."""
+    gy = gy.contiguous()
+    ag = nvq.amax(gy)
+    # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
+    gx = nvq.mm(nvq.quant_rows(gy, sr=True, seed=seed, am=ag), qwt)
+    # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
+    qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag)
+    qxt = nvq.quant_cols_rht(x, signs, am=am_x)
+    if gw_out is not None:
+        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=True)
+    else:
+        gw = nvq.mm(qgt, qxt, out_dtype=wgrad_dtype)
+    return gx, gw
+
+
 class FP4LinearFn(torch.autograd.Function):
     """x [T, K] bf16, w [N, K] bf16 -> y [T, N] bf16 (llm-1b/model.py:45-69)."""
 
     @staticmethod
     def forward(ctx, x, w, lid, cache=None):
-        ctx.save_for_backward(x, w)
-        ctx.lid, ctx.cache = lid, cache
-        qx = nvq.quant_rows(x)
         qw = cache.q if cache is not None else nvq.quant_w2d(w, want=(True, False))[0]
-        return nvq.mm(qx, qw)
+        y, am = linear_fwd(x, qw)
+        ctx.save_for_backward(x, w, am)
+        ctx.lid, ctx.cache = lid, cache
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, w = ctx.saved_tensors
-        gy = gy.contiguous()
+        x, w, am = ctx.saved_tensors
         seed = sr_seed(ctx.lid)
-        ag = nvq.amax(gy)
-        # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
         qwt = ctx.cache.qt if ctx.cache is not None else nvq.quant_w2d(w, want=(False, True))[1]
-        qg = nvq.quant_rows(gy, sr=True, seed=seed, am=ag)
-        gx = nvq.mm(qg, qwt)
-        # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
-        qgt = nvq.quant_cols_rht(gy, _RHT_SIGNS, sr=True, seed=seed ^ 0x5bd1e995, am=ag)
-        qxt = nvq.quant_cols_rht(x, _RHT_SIGNS)
-        gw = nvq.mm(qgt, qxt, out_dtype=LinCtx.wgrad_dtype)
+        gx, gw = linear_bwd(x, am, gy, qwt, seed, seed ^ 0x5bd1e995, wgrad_dtype=LinCtx.wgrad_dtype)
         return gx, gw, None, None
 
 

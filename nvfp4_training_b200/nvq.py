@@ -55,7 +55,7 @@ def quant_rows(x, sr=False, seed=0, am=None):
     s = torch.empty(R * C // 16, dtype=torch.uint8, device=x.device)
     gs = _new_gs(am)
     L.check(L.load().nvfp4_quant_rows(L.ptr(x), x.stride(0), R, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am),
-                                      L.ptr(gs), SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF, L.stream()),
+                                      L.ptr(gs), SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed), L.stream()),
             "quant_rows")
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 
@@ -73,34 +73,45 @@ def quant_cols_rht(x, signs, sr=False, seed=0, am=None):
     s = torch.empty(C * M // 16, dtype=torch.uint8, device=x.device)
     gs = _new_gs(am)
     L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gs),
-                                          signs & 0xFFFF, SR_MODE if sr else L.ROUND_NEAREST, seed & 0xFFFFFFFF,
+                                          signs & 0xFFFF, SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed),
                                           L.stream()), "quant_cols_rht")
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 
 
-def quant_w2d(w, am=None, want=(True, True)):
+def quant_w2d(w, am=None, want=(True, True), out=None):
     """w [N, K] bf16 -> (Q of w, Q of w^T), identical values (16x16 blocks) (llm-1b/nvq.py:73-87).
-    `want` lets a caller skip one of the two outputs (its slot is then None)."""
+    `want` lets a caller skip one of the two outputs (its slot is then None); `out` = a pair
+    returned by an earlier call, overwritten in place (a per-step weight cache keeps its buffers)."""
     L.require_cuda(w)
     N, K = w.shape
     assert w.dtype == torch.bfloat16
     w = w.contiguous()
     assert N % 128 == 0 and K % 128 == 0, (N, K)
-    if am is None:
-        am = amax(w)
     f4, f8 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
-    q = s = qt = st = None
-    if want[0]:
-        q = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device)
-        s = torch.empty(N * K // 16, dtype=torch.uint8, device=w.device)
-    if want[1]:
-        qt = torch.empty(K, N // 2, dtype=torch.uint8, device=w.device)
-        st = torch.empty(K * N // 16, dtype=torch.uint8, device=w.device)
-    g = _new_gs(am)
+    if out is not None:
+        oq, oqt = out
+        want = (oq is not None, oqt is not None)
+        g = (oq or oqt).gs
+        if am is None:
+            am = amax(w)
+        q, s = (oq.d, oq.s) if oq is not None else (None, None)
+        qt, st = (oqt.d, oqt.s) if oqt is not None else (None, None)
+    else:
+        if am is None:
+            am = amax(w)
+        g = _new_gs(am)
+        q = s = qt = st = None
+        if want[0]:
+            q = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device).view(f4)
+            s = torch.empty(N * K // 16, dtype=torch.uint8, device=w.device).view(f8)
+        if want[1]:
+            qt = torch.empty(K, N // 2, dtype=torch.uint8, device=w.device).view(f4)
+            st = torch.empty(K * N // 16, dtype=torch.uint8, device=w.device).view(f8)
     L.check(L.load().nvfp4_quant_w2d(L.ptr(w), L.DTYPE_BF16, N, K, L.ptr(q), L.ptr(s), L.ptr(qt), L.ptr(st),
                                      L.SCALES_SWIZZLED, L.ptr(am), L.ptr(g), L.stream()), "quant_w2d")
-    return (Q(q.view(f4), s.view(f8), g) if want[0] else None,
-            Q(qt.view(f4), st.view(f8), g) if want[1] else None)
+    if out is not None:
+        return out
+    return (Q(q, s, g) if want[0] else None, Q(qt, st, g) if want[1] else None)
 
 
 def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False):

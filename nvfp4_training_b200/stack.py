@@ -1,0 +1,230 @@
+"""The NVFP4 linear layers of the 1B architecture as one data-parallel workload.
+
+Shapes follow the reference model (llm-1b/model.py:18-32 `Config`, :135-149 `Block`): per block
+qkv 2048->3072, o 2048->2048, gate/up 2048->11264, down 5632->2048, 20 blocks, plus the LM head
+2048->49152 run as an NVFP4 linear.  Everything between the linears (norms, attention, SwiGLU,
+loss) is outside this path: each projection reads its input and output-gradient from seeded
+synthetic pools of the right shape and distribution.
+
+One process per GPU.  Tokens are sharded by rows, weights replicated; fprop and dgrad need no
+communication.  The FP32 weight gradients are accumulated in place over the rank's microbatches and
+all-reduced (sum) once per step, block by block on a side stream as soon as the block's last
+backward has been enqueued, so NCCL overlaps the remaining backward GEMMs.
+
+Launch overhead: each block's four forwards, and its four backwards, are captured once into CUDA
+graphs that share one memory pool and are replayed per microbatch; stochastic-rounding seeds are
+read from device memory so every replay rounds with fresh bits.
+"""
+from dataclasses import dataclass
+
+import torch
+
+from . import nvq
+from .linear import _RHT_SIGNS, linear_bwd, linear_fwd
+
+
+@dataclass
+class StackConfig:
+    vocab: int = 49152
+    d: int = 2048
+    layers: int = 20
+    heads: int = 16
+    kv_heads: int = 4
+    ff: int = 5632
+    lm_head: bool = True
+
+    @property
+    def hd(self):
+        return self.d // self.heads
+
+    def block_shapes(self):
+        """(name, N out-features, K in-features, init std) of one block (llm-1b/model.py:139-149)."""
+        std, out_std = 0.02, 0.02 / (2 * self.layers) ** 0.5
+        return [("qkv", (self.heads + 2 * self.kv_heads) * self.hd, self.d, std),
+                ("o", self.d, self.heads * self.hd, out_std),
+                ("gu", 2 * self.ff, self.d, std),
+                ("down", self.d, self.ff, out_std)]
+
+    def flops_per_token(self):
+        per_block = sum(6 * n * k for _, n, k, _ in self.block_shapes())
+        return per_block * self.layers + (6 * self.vocab * self.d if self.lm_head else 0)
+
+    def n_params(self):
+        return sum(n * k for _, n, k, _ in self.block_shapes()) * self.layers + (self.vocab * self.d if self.lm_head else 0)
+
+
+def shard_plan(world, rank, global_tokens, microbatch, seq_len=2048):
+    """Row sharding of the global batch: whole sequences per rank, the rank's rows cut into equal
+    microbatches.  RHT16 blocks (16 rows) and 128-row tiles never straddle ranks or microbatches."""
+    n_seq = global_tokens // seq_len
+    if global_tokens % seq_len or n_seq % world:
+        raise ValueError(f"{global_tokens} tokens = {n_seq} sequences do not split over {world} ranks")
+    t_local = global_tokens // world
+    mb = min(microbatch, t_local)
+    if mb % 128 or t_local % mb:
+        raise ValueError(f"microbatch {mb} must be a multiple of 128 and divide the {t_local} local tokens")
+    return {"row0": rank * t_local, "rows": t_local, "microbatch": mb, "n_micro": t_local // mb}
+
+
+def allreduce_sum_(tensors, group=None):
+    """In-place FP32 sum of the weight gradients over the data-parallel group: the one exchange of
+    this path.  Works on any backend (NCCL on GPUs, gloo in the CPU tests)."""
+    for t in tensors:
+        assert t.dtype == torch.float32
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.SUM, group=group)
+    return tensors
+
+
+class _Proj:
+    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx")
+
+
+def student_t(shape, gen, device, df=3):
+    z = torch.randn(shape, generator=gen, device=device)
+    chi = torch.randn((df,) + tuple(shape), generator=gen, device=device).square_().sum(0)
+    return z / torch.sqrt(chi / df)
+
+
+class LinearStack:
+    def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None):
+        self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
+        self.use_graphs = use_graphs
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        self.blocks = []
+        lid = 0
+        names = cfg.block_shapes()
+        for b in range(cfg.layers):
+            projs = []
+            for name, N, K, std in names:
+                projs.append(self._make_proj(name, N, K, std, lid, gen))
+                lid += 1
+            self.blocks.append(projs)
+        if cfg.lm_head:
+            self.blocks.append([self._make_proj("head", cfg.vocab, cfg.d, 0.02, lid, gen)])
+            lid += 1
+        self.n_proj = lid
+        # synthetic pools: X ~ N(0,1) bf16, dY ~ Student-t(3) * 1e-3 bf16, one per projection kind
+        gen_in = torch.Generator(device=self.device).manual_seed(seed + 1000)
+        self.x_pool, self.gy_pool = {}, {}
+        for name, N, K, _ in names + ([("head", cfg.vocab, cfg.d, 0.02)] if cfg.lm_head else []):
+            self.x_pool[name] = torch.randn(self.T, K, generator=gen_in, device=self.device).bfloat16()
+            self.gy_pool[name] = (student_t((self.T, N), gen_in, self.device) * 1e-3).bfloat16()
+        # per-projection SR seeds in device memory: [n_proj, 2] = (seed, seed ^ 0x5bd1e995) (llm-1b/model.py:59,66)
+        self.seeds = torch.zeros(self.n_proj, 2, dtype=torch.int32, device=self.device)
+        self._lids = torch.arange(self.n_proj, dtype=torch.int64, device=self.device) * 7919
+        self.micro_count = 0
+        self._bump_seeds()
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        self.graphs_fwd = self.graphs_bwd = None
+        self.launches_per_micro = 0
+
+    def _make_proj(self, name, N, K, std, lid, gen):
+        p = _Proj()
+        p.name, p.N, p.K, p.lid = name, N, K, lid
+        w = torch.empty(N, K, device=self.device)
+        torch.nn.init.trunc_normal_(w, std=std, a=-3 * std, b=3 * std, generator=gen)
+        p.w = w.bfloat16()
+        p.gw = torch.zeros(N, K, dtype=torch.float32, device=self.device)
+        p.q = p.qt = p.am_x = p.y = p.gx = None
+        return p
+
+    # ------------------------------------------------------------------ per-step pieces
+    def _bump_seeds(self):
+        """seed = (LinCtx.seed * 1000003 + lid * 7919) & 0xFFFFFFFF, LinCtx.seed = microbatch counter."""
+        s = (self._lids + self.micro_count * 1000003) & 0xFFFFFFFF
+        both = torch.stack([s, s ^ 0x5BD1E995], 1)
+        self.seeds.copy_(torch.where(both >= 2 ** 31, both - 2 ** 32, both).to(torch.int32))
+        self.micro_count += 1
+
+    def refresh_weights(self):
+        """Quantize every weight once per optimizer step (the small-model/fp4torch.py:71-84 scheme)."""
+        for projs in self.blocks:
+            for p in projs:
+                if p.q is None:
+                    p.q, p.qt = nvq.quant_w2d(p.w)
+                else:
+                    nvq.quant_w2d(p.w, out=(p.q, p.qt))      # in place: captured graphs keep these buffers
+
+    def zero_grads(self):
+        for projs in self.blocks:
+            for p in projs:
+                p.gw.zero_()
+
+    def _fwd_block(self, projs, keep=False):
+        for p in projs:
+            y, p.am_x = linear_fwd(self.x_pool[p.name], p.q)
+            p.y = y if keep else None
+
+    def _bwd_block(self, projs, keep=False):
+        for p in reversed(projs):
+            sd = self.seeds[p.lid]
+            gx, _ = linear_bwd(self.x_pool[p.name], p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
+                               gw_out=p.gw, signs=_RHT_SIGNS)
+            p.gx = gx if keep else None
+
+    def capture(self):
+        """Capture each block's forward and backward into CUDA graphs sharing one memory pool."""
+        self.refresh_weights()
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):          # warm-up outside capture
+            for projs in self.blocks:
+                self._fwd_block(projs)
+            for projs in reversed(self.blocks):
+                self._bwd_block(projs)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        pool = torch.cuda.graph_pool_handle()
+        self.graphs_fwd, self.graphs_bwd = [], []
+        for projs in self.blocks:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                self._fwd_block(projs)
+            self.graphs_fwd.append(g)
+        for projs in reversed(self.blocks):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                self._bwd_block(projs)
+            self.graphs_bwd.append(g)
+        self.zero_grads()
+        torch.cuda.synchronize()
+
+    def kernels_per_microbatch(self):
+        """Kernels of this library launched per microbatch: fwd amax + quant_rows + gemm;
+        bwd amax + quant_rows + gemm + 2 quant_cols_rht + gemm."""
+        return self.n_proj * (3 + 6)
+
+    def microbatch(self, last, do_allreduce):
+        """One forward + backward over all projections.  On the rank's last microbatch each block's
+        weight gradients are all-reduced on the side stream right after its backward is enqueued."""
+        self._bump_seeds()
+        cur = torch.cuda.current_stream()
+        if self.use_graphs and self.graphs_fwd is not None:
+            for g in self.graphs_fwd:
+                g.replay()
+        else:
+            for projs in self.blocks:
+                self._fwd_block(projs)
+        works = []
+        for i, projs in enumerate(reversed(self.blocks)):
+            if self.use_graphs and self.graphs_bwd is not None:
+                self.graphs_bwd[i].replay()
+            else:
+                self._bwd_block(projs)
+            if last and do_allreduce:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ev)
+                    allreduce_sum_([p.gw for p in projs], self.group)
+        return works
+
+    def step(self, n_micro, do_allreduce):
+        """One optimizer step's worth of this path: re-quantize weights, clear dW, n_micro
+        microbatches, all-reduce.  Leaves the summed FP32 gradients in `p.gw`."""
+        self.refresh_weights()
+        self.zero_grads()
+        for m in range(n_micro):
+            self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce)
+        if do_allreduce:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)

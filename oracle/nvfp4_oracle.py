@@ -157,7 +157,7 @@ def sr_hw_code(y, r16):
     y = np.asarray(y, dtype=np.float32)
     r16 = np.asarray(r16, dtype=np.int64) & 0xFFFF
     nan = np.isnan(y)
-    a = np.where(nan, 6.0, np.abs(y).astype(np.float64))
+    a = np.minimum(np.where(nan, 6.0, np.abs(y).astype(np.float64)), 8.0)     # 8 stands for anything >= 6
     step = np.where(a < 2, 0.5, np.where(a < 4, 1.0, 2.0))
     lo = np.floor(a / step) * step
     f16 = np.floor((a - lo) / step * 65536.0).astype(np.int64)      # exact: a carries 24 bits

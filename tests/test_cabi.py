@@ -44,11 +44,11 @@ def test_argument_validation_needs_no_device(lib):
     # null pointers, bad shapes, bad enums: all rejected before any CUDA call
     assert lib.nvfp4_amax_bf16(None, 8, None, None) == -1
     assert lib.nvfp4_amax_bf16(ctypes.c_void_p(16), 12, ctypes.c_void_p(16), None) == -2
-    assert lib.nvfp4_quant_rows(None, 64, 128, 64, None, None, 0, None, None, 0, 0, None) == -1
+    assert lib.nvfp4_quant_rows(None, 64, 128, 64, None, None, 0, None, None, 0, 0, None, None) == -1
     p = ctypes.c_void_p(1 << 20)
-    assert lib.nvfp4_quant_rows(p, 64, 100, 64, p, p, 0, p, None, 0, 0, None) == -2
-    assert lib.nvfp4_quant_rows(p, 64, 128, 64, p, p, 0, p, None, 9, 0, None) == -4
-    assert lib.nvfp4_quant_cols_rht(p, 64, 100, p, p, 0, p, None, 0, 0, 0, None) == -2
+    assert lib.nvfp4_quant_rows(p, 64, 100, 64, p, p, 0, p, None, 0, 0, None, None) == -2
+    assert lib.nvfp4_quant_rows(p, 64, 128, 64, p, p, 0, p, None, 9, 0, None, None) == -4
+    assert lib.nvfp4_quant_cols_rht(p, 64, 100, p, p, 0, p, None, 0, 0, 0, None, None) == -2
     assert lib.nvfp4_quant_w2d(p, 5, 128, 128, p, p, p, p, 0, p, None, None) == -4
     assert lib.nvfp4_gemm(p, p, 64, p, p, 64, p, 1, 128, 128, 128, 100, 0, None, None, 1.0, 1.0, 0, 1, None, None) == -2
     assert lib.nvfp4_gemm_linear(p, p, 64, 8, p, p, 64, 8, p, 1, 128, 128, 128, 128, 0, None, None, 1.0, 1.0, 0, 1,

@@ -27,7 +27,7 @@ def test_linear_fwd_bwd_matches_oracle(cache):
     assert seed == (12 * 1000003 + 3 * 7919) & 0xFFFFFFFF
     ry, rgx, rgw = O.linear_fwd_bwd(x, w, gy, _RHT_SIGNS, seed=seed, sr_mode=O.SR_DITHER_NVQ)
     # same codes/scales on both sides, so only accumulation order and the bf16 output cast differ
-    assert rel_fro(y.float().cpu().numpy(), ry) <= 4e-3
+    assert rel_fro(y.detach().float().cpu().numpy(), ry) <= 4e-3
     assert rel_fro(xd.grad.float().cpu().numpy(), rgx) <= 4e-3
     assert wd.grad.dtype == torch.float32 or wd.grad.dtype == torch.bfloat16
     assert rel_fro(wd.grad.float().cpu().numpy(), rgw) <= 4e-3

@@ -191,6 +191,20 @@ def test_cols_rht_sr_dither_bit_exact(mods, signs):
     assert np.array_equal(u8(q.d), codes) and np.array_equal(u8(q.s), scales)
 
 
+def test_device_side_seed(mods):
+    """A seed read from device memory gives the same bits as the same seed passed by value."""
+    nvq, _, _ = mods
+    x = to_dev(make_dy(6, 128, 128))
+    sd = torch.tensor([77], dtype=torch.int32, device="cuda")
+    a, b = nvq.quant_rows(x, sr=True, seed=77), nvq.quant_rows(x, sr=True, seed=sd)
+    assert torch.equal(a.d.view(torch.uint8), b.d.view(torch.uint8))
+    a, b = nvq.quant_cols_rht(x, 3, sr=True, seed=77), nvq.quant_cols_rht(x, 3, sr=True, seed=sd)
+    assert torch.equal(a.d.view(torch.uint8), b.d.view(torch.uint8))
+    sd.fill_(78)
+    c = nvq.quant_cols_rht(x, 3, sr=True, seed=sd)
+    assert not torch.equal(a.d.view(torch.uint8), c.d.view(torch.uint8))
+
+
 def test_swizzle_scales_kernel(mods):
     _, _, L = mods
     rng = np.random.default_rng(0)
@@ -215,7 +229,7 @@ def test_rejects_bad_arguments(mods):
     s = torch.empty(128 * 4, dtype=torch.uint8, device="cuda")
     am = torch.ones(1, device="cuda")
     lib = L.load()
-    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr() + 1, s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -3
-    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 48, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -2
-    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr(), s.data_ptr(), 7, am.data_ptr(), None, 0, 0, L.stream()) == -4
-    assert lib.nvfp4_quant_rows(None, 64, 128, 64, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, L.stream()) == -1
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr() + 1, s.data_ptr(), 0, am.data_ptr(), None, 0, 0, None, L.stream()) == -3
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 48, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, None, L.stream()) == -2
+    assert lib.nvfp4_quant_rows(x.data_ptr(), 64, 128, 64, d.data_ptr(), s.data_ptr(), 7, am.data_ptr(), None, 0, 0, None, L.stream()) == -4
+    assert lib.nvfp4_quant_rows(None, 64, 128, 64, d.data_ptr(), s.data_ptr(), 0, am.data_ptr(), None, 0, 0, None, L.stream()) == -1
