@@ -2,7 +2,7 @@
 //   A, B   packed E2M1 (2 per byte), K-major; one UE4M3 scale per 16 values in the 128x4-tile
 //          swizzled layout (512-byte tiles, consecutive K tiles of one 128-row block contiguous).
 //
-// Persistent, warp-specialised kernel, one CTA per SM, 192 threads:
+// Persistent, warp-specialised kernel, one CTA per SM, 320 threads:
 //   warp 0      TMA producer: per K tile (256 elements) one 128-byte-swizzled box load each for A and
 //               B plus plain bulk copies of the scale tiles (2 KB per 128 rows), all completing on
 //               the stage's `full` mbarrier
@@ -10,9 +10,13 @@
 //               (tcgen05.cp 32x128b.warpx4), issues four tcgen05.mma kind::mxf4nvf4 block16 (K = 64
 //               each) into the FP32 accumulator in tensor memory, releases the stage with
 //               tcgen05.commit; owns tensor-memory allocation
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one 32-lane quadrant per warp), alpha,
-//               cast and store (or FP32 atomic add for split-K / accumulate)
-// With BN = 128 two accumulators alternate so the epilogue of a tile overlaps the next tile's MMAs.
+//   warps 2..9  epilogue: each warp drains half the columns of its 32-lane quadrant with tcgen05.ld
+//               into registers, hands the accumulator back at once, then applies alpha, casts and
+//               stores (or FP32 vector atomic adds for split-K / accumulate)
+// With BN = 128 two accumulators alternate; with BN = 256 the single accumulator is free again as
+// soon as it has been read, so the next tile's MMAs overlap the conversion and the stores.
+// The issuing threads keep their per-K-tile instruction count minimal (descriptor low words are
+// advanced by adds, high words are constants): a single thread feeds the whole tensor core.
 // Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, reports a code through
 // `status`, lets copies in flight land, frees its tensor memory and returns.
 #include <cuda.h>
@@ -24,7 +28,8 @@ namespace nvfp4 {
 constexpr int kBM = 128;            // rows of A per tile (UMMA M)
 constexpr int kBKBytes = 128;       // bytes of K per stage row = 256 FP4 values = one 128B swizzle row
 constexpr int kBK = 256;            // FP4 values of K per stage
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;         // two warps per 32-lane quadrant of tensor memory
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr u64 kWaitLimitNs = 1000000000ull;   // 1 s per wait, far above any legitimate wait
 
 template <int BN>
@@ -40,6 +45,7 @@ struct Cfg {
   // tensor-memory columns: accumulators first, then scale factors of the stage being multiplied
   static constexpr int kSfaCol = kAccStages * BN;
   static constexpr int kSfbCol = kSfaCol + 16;
+  static constexpr int kSfBufCols = 16 + 16 * (BN / 128);   // columns of one scale buffer; two alternate per K tile
   static constexpr int kTmemCols = 512;
 };
 
@@ -58,6 +64,9 @@ struct GemmParams {
   int atomic;         // 1: add into C with FP32 atomics
   int splitk;         // number of K slices
   int ktiles_per_split;
+#ifdef NVFP4_GEMM_DEBUG
+  int dbg;            // development switches: 1 no stores, 2 no scale copies, 4 no MMAs, 8 no operand loads
+#endif
 };
 
 // ---------------------------------------------------------------------------------------- PTX wrappers
@@ -161,6 +170,18 @@ __host__ __device__ constexpr u32 make_idesc(int n) {
 }
 
 // ---------------------------------------------------------------------------------------- kernel
+__device__ __forceinline__ u64 pack64(u32 lo, u32 hi) {
+  u64 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// high words of the shared-memory descriptors (constant for the whole kernel):
+//   operand tiles: stride offset 1024 B (8 rows x 128 B), version 1, 128-byte swizzle
+//   scale tiles:   stride offset 128 B (8 rows x 16 B), version 1, no swizzle
+constexpr u32 kDescHiAB = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr u32 kDescHiSF = (128u >> 4) | (1u << 14);
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
@@ -179,11 +200,13 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = p.M / kBM, tiles_n = p.N / BN;
   const int ktiles = (p.K + kBK - 1) / kBK;
-  const long long num_work = (long long)tiles_m * tiles_n * p.splitk;
+  const int num_work = tiles_m * tiles_n * p.splitk;
+  const u32 smem_base = smem_u32(smem);
+  const u32 full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; s++) { mbar_init(smem_u32(full_bar + s), 1); mbar_init(smem_u32(empty_bar + s), 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full + a), 1); mbar_init(smem_u32(acc_empty + a), 4); }
+    for (int s = 0; s < C::kStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(smem_u32(acc_full + a), 1); mbar_init(smem_u32(acc_empty + a), kEpiWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -203,31 +226,40 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       int stage = 0; u32 phase = 0;
+      u32 st_addr = smem_base;
       const long long sf_row_bytes = (long long)(p.K >> 6) * 512;   // scale bytes of one 128-row block
       bool ok = true;
-      for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int mt = (int)(w % tiles_m);
-        const long long rest = w / tiles_m;
-        const int nt = (int)(rest % tiles_n);
-        const int z = (int)(rest / tiles_n);
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int mt = w % tiles_m;
+        const int rest = w / tiles_m;
+        const int nt = rest % tiles_n;
+        const int z = rest / tiles_n;
         const int kt0 = z * p.ktiles_per_split;
         const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+        const unsigned char* sfa = p.sfa + (long long)mt * sf_row_bytes + (long long)kt0 * 2048;
+        const unsigned char* sfb = p.sfb + (long long)(nt * (BN / 128)) * sf_row_bytes + (long long)kt0 * 2048;
+        const int ya = mt * kBM, yb = nt * BN;
+        int x = kt0 * kBKBytes;
         for (int kt = kt0; kt < kt1; kt++) {
-          if (!mbar_wait(smem_u32(empty_bar + stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          unsigned char* st = smem + stage * C::kStageBytes;
-          const u32 bar = smem_u32(full_bar + stage);
-          const int kchunks = min(4, (p.K - kt * kBK) >> 6);
-          const u32 sf_bytes = (u32)kchunks * 512u;
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+          const u32 bar = full0 + 8 * stage;
+          const int krem = p.K - kt * kBK;
+          const u32 sf_bytes = krem >= kBK ? 2048u : (u32)(krem >> 6) * 512u;
+#ifdef NVFP4_GEMM_DEBUG
+          if (p.dbg & 8) mbar_arrive_expect_tx(bar, sf_bytes * (1 + BN / 128)); else
+#endif
+          {
           mbar_arrive_expect_tx(bar, (u32)(C::kABytes + C::kBBytes) + sf_bytes * (1 + BN / 128));
-          tma_load_2d(smem_u32(st), &map_a, kt * kBKBytes, mt * kBM, bar);
-          tma_load_2d(smem_u32(st + C::kABytes), &map_b, kt * kBKBytes, nt * BN, bar);
-          bulk_load(smem_u32(st + C::kABytes + C::kBBytes), p.sfa + (long long)mt * sf_row_bytes + (long long)kt * 2048,
-                    sf_bytes, bar);
+          tma_load_2d(st_addr, &map_a, x, ya, bar);
+          tma_load_2d(st_addr + C::kABytes, &map_b, x, yb, bar);
+          }
+          bulk_load(st_addr + C::kABytes + C::kBBytes, sfa, sf_bytes, bar);
 #pragma unroll
           for (int h = 0; h < BN / 128; h++)
-            bulk_load(smem_u32(st + C::kABytes + C::kBBytes + C::kSFABytes + h * 2048),
-                      p.sfb + (long long)(nt * (BN / 128) + h) * sf_row_bytes + (long long)kt * 2048, sf_bytes, bar);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+            bulk_load(st_addr + C::kABytes + C::kBBytes + C::kSFABytes + h * 2048, sfb + h * sf_row_bytes, sf_bytes, bar);
+          x += kBKBytes; sfa += 2048; sfb += 2048;
+          st_addr += C::kStageBytes;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
         }
       }
       if (!ok && p.status) atomicExch(p.status, 1);
@@ -236,39 +268,73 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr u32 idesc = make_idesc(BN);
+      u32 sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+      u32 sf_flip = C::kSfBufCols;
       int stage = 0; u32 phase = 0;
+      // low descriptor words of the current stage: operand tiles carry leading offset 16 B (bit 16)
+      const u32 a_lo0 = (smem_base >> 4) | (1u << 16);
+      u32 a_lo = a_lo0;
       int acc = 0; u32 acc_phase = 0;
       bool ok = true;
-      for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int z = (int)(w / ((long long)tiles_m * tiles_n));
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int z = w / (tiles_m * tiles_n);
         const int kt0 = z * p.ktiles_per_split;
         const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
         // the epilogue must have drained this accumulator
         if (!mbar_wait(smem_u32(acc_empty + acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const u32 d_tmem = tmem_base + (u32)(acc * BN);
+        u32 accum = 0u;
         for (int kt = kt0; kt < kt1; kt++) {
-          if (!mbar_wait(smem_u32(full_bar + stage), phase, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          unsigned char* st = smem + stage * C::kStageBytes;
-          const u32 a_addr = smem_u32(st), b_addr = a_addr + C::kABytes;
-          const u32 sfa_addr = b_addr + C::kBBytes, sfb_addr = sfa_addr + C::kSFABytes;
-          const int kchunks = min(4, (p.K - kt * kBK) >> 6);
-          for (int j = 0; j < kchunks; j++) {
-            tc_cp_sf(tmem_base + C::kSfaCol + 4 * j, smem_desc(sfa_addr + 512 * j, 0, 128, 0));
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          const u32 b_lo = a_lo + (C::kABytes >> 4);
+          const u32 sfa_lo = (a_lo & 0xFFFFu) + ((C::kABytes + C::kBBytes) >> 4);
+          const u32 sfb_lo = sfa_lo + (C::kSFABytes >> 4);
+          const int krem = p.K - kt * kBK;
+          if (krem >= kBK) {
+            // scale tiles of the four K chunks: shared memory -> tensor memory
+#ifdef NVFP4_GEMM_DEBUG
+            if (!((p.dbg & 2) && accum))
+#endif
 #pragma unroll
-            for (int h = 0; h < BN / 128; h++)
-              tc_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * j + 4 * h, smem_desc(sfb_addr + 2048 * h + 512 * j, 0, 128, 0));
+            for (int j = 0; j < 4; j++) {
+              tc_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
+#pragma unroll
+              for (int h = 0; h < BN / 128; h++)
+                tc_cp_sf(sfb_t + (BN / 32) * j + 4 * h, pack64(sfb_lo + 128 * h + 32 * j, kDescHiSF));
+            }
+            // four MMAs, each 64 FP4 values = 32 bytes further along K inside the 128-byte swizzle row
+#ifdef NVFP4_GEMM_DEBUG
+            if (!((p.dbg & 4) && accum))
+#endif
+            tc_mma_nvf4(d_tmem, pack64(a_lo, kDescHiAB), pack64(b_lo, kDescHiAB), idesc, sfa_t, sfb_t, accum);
+#ifdef NVFP4_GEMM_DEBUG
+            if (!(p.dbg & 4))
+#endif
+#pragma unroll
+            for (int j = 1; j < 4; j++)
+              tc_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                          sfb_t + (BN / 32) * j, 1u);
+          } else {
+            const int kchunks = krem >> 6;
+            for (int j = 0; j < kchunks; j++) {
+              tc_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
+#pragma unroll
+              for (int h = 0; h < BN / 128; h++)
+                tc_cp_sf(sfb_t + (BN / 32) * j + 4 * h, pack64(sfb_lo + 128 * h + 32 * j, kDescHiSF));
+            }
+            for (int j = 0; j < kchunks; j++)
+              tc_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                          sfb_t + (BN / 32) * j, (j > 0) ? 1u : accum);
           }
-          for (int j = 0; j < kchunks; j++) {
-            // 64 FP4 values = 32 bytes further along K inside the 128-byte swizzle row
-            const u64 adesc = smem_desc(a_addr + 32 * j, 16, 1024, 2);
-            const u64 bdesc = smem_desc(b_addr + 32 * j, 16, 1024, 2);
-            tc_mma_nvf4(d_tmem, adesc, bdesc, idesc, tmem_base + C::kSfaCol + 4 * j, tmem_base + C::kSfbCol + (BN / 32) * j,
-                        (kt > kt0 || j > 0) ? 1u : 0u);
-          }
-          tc_commit(smem_u32(empty_bar + stage));     // frees the stage once these MMAs have read it
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          accum = 1u;
+#ifdef NVFP4_GEMM_DEBUG
+          if (!(p.dbg & 16))
+#endif
+          { sfa_t += sf_flip; sfb_t += sf_flip; sf_flip = 0u - sf_flip; }   // other scale buffer for the next K tile
+          tc_commit(empty0 + 8 * stage);              // frees the stage once these MMAs have read it
+          a_lo += C::kStageBytes >> 4;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
         }
         if (!ok) break;
         tc_commit(smem_u32(acc_full + acc));          // accumulator complete
@@ -277,62 +343,65 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (!ok && p.status) atomicExch(p.status, 2);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Each warp drains kEpiCols columns of its 32-lane quadrant into registers in one go and hands
+    // the accumulator back before converting and storing, so the tensor core restarts early.
+    constexpr int kEpiCols = BN / 2;
     const int quad = warp & 3;                         // tensor-memory lanes 32*quad .. +31
+    const int half = (warp - 2) >> 2;                  // which half of the tile's columns
     int acc = 0; u32 acc_phase = 0;
     bool ok = true;
-    for (long long w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-      const int mt = (int)(w % tiles_m);
-      const int nt = (int)((w / tiles_m) % tiles_n);
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int mt = w % tiles_m;
+      const int nt = (w / tiles_m) % tiles_n;
       // the decision must be warp-uniform: the tensor-memory loads below are warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(acc_full + acc), acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after();
+      u32 r[kEpiCols];
+      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (u32)(acc * BN + half * kEpiCols);
+#pragma unroll
+      for (int c = 0; c < kEpiCols / 32; c++) tc_ld32(t_row + c * 32, *reinterpret_cast<u32(*)[32]>(&r[c * 32]));
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(acc_empty + acc));
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
+
       float alpha = 1.f;
       if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
       const long long row = (long long)mt * kBM + quad * 32 + lane;
-      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (u32)(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        u32 r[32];
-        tc_ld32(t_row + c * 32, r);
-        tc_wait_ld();
-        if (c == BN / 32 - 1) {
-          // whole accumulator is in registers: hand it back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(acc_empty + acc));
-        }
-        const long long col = (long long)nt * BN + c * 32;
-        if (p.c_fp32) {
-          float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
-          if (p.atomic) {
+      const long long col = (long long)nt * BN + half * kEpiCols;
+#ifdef NVFP4_GEMM_DEBUG
+      if (p.dbg & 1) { if (r[0] == 0x12345678u && r[kEpiCols - 1] == 0x9abcdef0u) *static_cast<u32*>(p.c) = r[5]; } else
+#endif
+      if (p.c_fp32) {
+        float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
+        if (p.atomic) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i),
-                           "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),
-                           "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
-                                                                __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
-          }
+          for (int i = 0; i < kEpiCols; i += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i),
+                         "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),
+                         "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");
         } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 o;
-            __nv_bfloat162 h;
-            h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h);
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h);
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h);
-            *reinterpret_cast<uint4*>(dst + i) = o;
-          }
+          for (int i = 0; i < kEpiCols; i += 4)
+            *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha,
+                                                              __uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha);
+        }
+      } else {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+#pragma unroll
+        for (int i = 0; i < kEpiCols; i += 8) {
+          uint4 o;
+          __nv_bfloat162 h;
+          h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);
+          h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h);
+          h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h);
+          h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h);
+          *reinterpret_cast<uint4*>(dst + i) = o;
         }
       }
-      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
     }
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 3);
   }
@@ -382,6 +451,10 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+#ifdef NVFP4_GEMM_DEBUG
+static int g_debug = 0;
+extern "C" int nvfp4_gemm_debug(int flags) { g_debug = flags; return 0; }
+#endif
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced tile width (tuning and tests)
 
 struct DevInfo { int sms; bool attr128, attr256; };
@@ -451,9 +524,9 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   int per = (ktiles + splitk - 1) / splitk;
   splitk = (ktiles + per - 1) / per;
 
-  // wide tiles halve the B traffic per FLOP but cannot overlap their epilogue; use them when the
-  // contraction is long enough to amortise it and N allows
-  bool wide = (N % 256 == 0) && ((long long)per * kBK >= 4096);
+  // 256-wide tiles move fewer operand bytes per FLOP and need fewer issue slots; fall back to 128
+  // when N demands it or when wide tiles would leave SMs without work
+  bool wide = (N % 256 == 0) && ((long long)(M / kBM) * (N / 256) * splitk >= di->sms || (long long)(M / kBM) * (N / 128) * splitk <= di->sms);
   if (g_force_bn == 128) wide = false;
   if (g_force_bn == 256 && N % 256 == 0) wide = true;
   const int bn = wide ? 256 : 128;
@@ -472,6 +545,9 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   p.atomic = (accumulate || splitk > 1) ? 1 : 0;
   p.splitk = splitk;
   p.ktiles_per_split = per;
+#ifdef NVFP4_GEMM_DEBUG
+  p.dbg = g_debug;
+#endif
   if (wide) return launch_gemm<256>(ma, mb, p, di->sms, di->attr256, st);
   return launch_gemm<128>(ma, mb, p, di->sms, di->attr128, st);
 }
