@@ -170,6 +170,13 @@ __host__ __device__ constexpr u32 make_idesc(int n) {
 }
 
 // ---------------------------------------------------------------------------------------- kernel
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  u32 pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0u;
+}
+
 __device__ __forceinline__ u64 pack64(u32 lo, u32 hi) {
   u64 d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
@@ -220,31 +227,36 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const u32 tmem_base = *tmem_slot;
 
+  // The two issuing warps run their loops with all 32 lanes converged, so that loop state,
+  // addresses and descriptors stay warp-uniform (the asynchronous-copy and tensor-core instructions
+  // take uniform operands); only the instruction issue itself is predicated on one elected lane.
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-      int stage = 0; u32 phase = 0;
-      u32 st_addr = smem_base;
-      const long long sf_row_bytes = (long long)(p.K >> 6) * 512;   // scale bytes of one 128-row block
-      bool ok = true;
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int mt = w % tiles_m;
-        const int rest = w / tiles_m;
-        const int nt = rest % tiles_n;
-        const int z = rest / tiles_n;
-        const int kt0 = z * p.ktiles_per_split;
-        const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
-        const unsigned char* sfa = p.sfa + (long long)mt * sf_row_bytes + (long long)kt0 * 2048;
-        const unsigned char* sfb = p.sfb + (long long)(nt * (BN / 128)) * sf_row_bytes + (long long)kt0 * 2048;
-        const int ya = mt * kBM, yb = nt * BN;
-        int x = kt0 * kBKBytes;
-        for (int kt = kt0; kt < kt1; kt++) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
-          const u32 bar = full0 + 8 * stage;
-          const int krem = p.K - kt * kBK;
-          const u32 sf_bytes = krem >= kBK ? 2048u : (u32)(krem >> 6) * 512u;
+    }
+    int stage = 0; u32 phase = 0;
+    u32 st_addr = smem_base;
+    const long long sf_row_bytes = (long long)(p.K >> 6) * 512;   // scale bytes of one 128-row block
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int mt = w % tiles_m;
+      const int rest = w / tiles_m;
+      const int nt = rest % tiles_n;
+      const int z = rest / tiles_n;
+      const int kt0 = z * p.ktiles_per_split;
+      const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+      const unsigned char* sfa = p.sfa + (long long)mt * sf_row_bytes + (long long)kt0 * 2048;
+      const unsigned char* sfb = p.sfb + (long long)(nt * (BN / 128)) * sf_row_bytes + (long long)kt0 * 2048;
+      const int ya = mt * kBM, yb = nt * BN;
+      int x = kt0 * kBKBytes;
+      for (int kt = kt0; kt < kt1; kt++) {
+        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag))) { ok = false; break; }
+        const u32 bar = full0 + 8 * stage;
+        const int krem = p.K - kt * kBK;
+        const u32 sf_bytes = krem >= kBK ? 2048u : (u32)(krem >> 6) * 512u;
+        if (elect_one()) {
 #ifdef NVFP4_GEMM_DEBUG
           if (p.dbg & 8) mbar_arrive_expect_tx(bar, sf_bytes * (1 + BN / 128)); else
 #endif
@@ -257,40 +269,40 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int h = 0; h < BN / 128; h++)
             bulk_load(st_addr + C::kABytes + C::kBBytes + C::kSFABytes + h * 2048, sfb + h * sf_row_bytes, sf_bytes, bar);
-          x += kBKBytes; sfa += 2048; sfb += 2048;
-          st_addr += C::kStageBytes;
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
         }
+        x += kBKBytes; sfa += 2048; sfb += 2048;
+        st_addr += C::kStageBytes;
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
       }
-      if (!ok && p.status) atomicExch(p.status, 1);
     }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr u32 idesc = make_idesc(BN);
-      u32 sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
-      u32 sf_flip = C::kSfBufCols;
-      int stage = 0; u32 phase = 0;
-      // low descriptor words of the current stage: operand tiles carry leading offset 16 B (bit 16)
-      const u32 a_lo0 = (smem_base >> 4) | (1u << 16);
-      u32 a_lo = a_lo0;
-      int acc = 0; u32 acc_phase = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int z = w / (tiles_m * tiles_n);
-        const int kt0 = z * p.ktiles_per_split;
-        const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
-        // the epilogue must have drained this accumulator
-        if (!mbar_wait(smem_u32(acc_empty + acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const u32 d_tmem = tmem_base + (u32)(acc * BN);
-        u32 accum = 0u;
-        for (int kt = kt0; kt < kt1; kt++) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
-          const u32 b_lo = a_lo + (C::kABytes >> 4);
-          const u32 sfa_lo = (a_lo & 0xFFFFu) + ((C::kABytes + C::kBBytes) >> 4);
-          const u32 sfb_lo = sfa_lo + (C::kSFABytes >> 4);
-          const int krem = p.K - kt * kBK;
+    constexpr u32 idesc = make_idesc(BN);
+    u32 sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+    u32 sf_flip = C::kSfBufCols;
+    int stage = 0; u32 phase = 0;
+    // low descriptor words of the current stage: operand tiles carry leading offset 16 B (bit 16)
+    const u32 a_lo0 = (smem_base >> 4) | (1u << 16);
+    u32 a_lo = a_lo0;
+    int acc = 0; u32 acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int z = w / (tiles_m * tiles_n);
+      const int kt0 = z * p.ktiles_per_split;
+      const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+      // the epilogue must have drained this accumulator
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(acc_empty + acc), acc_phase ^ 1u, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      const u32 d_tmem = tmem_base + (u32)(acc * BN);
+      u32 accum = 0u;
+      for (int kt = kt0; kt < kt1; kt++) {
+        if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag))) { ok = false; break; }
+        const u32 b_lo = a_lo + (C::kABytes >> 4);
+        const u32 sfa_lo = (a_lo & 0xFFFFu) + ((C::kABytes + C::kBBytes) >> 4);
+        const u32 sfb_lo = sfa_lo + (C::kSFABytes >> 4);
+        const int krem = p.K - kt * kBK;
+        if (elect_one()) {
           if (krem >= kBK) {
             // scale tiles of the four K chunks: shared memory -> tensor memory
 #ifdef NVFP4_GEMM_DEBUG
@@ -327,21 +339,18 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               tc_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
                           sfb_t + (BN / 32) * j, (j > 0) ? 1u : accum);
           }
-          accum = 1u;
-#ifdef NVFP4_GEMM_DEBUG
-          if (!(p.dbg & 16))
-#endif
-          { sfa_t += sf_flip; sfb_t += sf_flip; sf_flip = 0u - sf_flip; }   // other scale buffer for the next K tile
           tc_commit(empty0 + 8 * stage);              // frees the stage once these MMAs have read it
-          a_lo += C::kStageBytes >> 4;
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
         }
-        if (!ok) break;
-        tc_commit(smem_u32(acc_full + acc));          // accumulator complete
-        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
+        accum = 1u;
+        sfa_t += sf_flip; sfb_t += sf_flip; sf_flip = 0u - sf_flip;   // other scale buffer for the next K tile
+        a_lo += C::kStageBytes >> 4;
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
       }
-      if (!ok && p.status) atomicExch(p.status, 2);
+      if (!ok) break;
+      if (elect_one()) tc_commit(smem_u32(acc_full + acc));          // accumulator complete
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
     }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 2);
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     // Each warp drains kEpiCols columns of its 32-lane quadrant into registers in one go and hands
