@@ -49,6 +49,19 @@ __device__ __forceinline__ u32 e2m1x2_rn(float lo, float hi) {
   return r;
 }
 
+// eight f32 -> one 32-bit word of E2M1 codes (v[0] in the lowest nibble), round to nearest even
+__device__ __forceinline__ u32 e2m1x8_rn(const float* v) {
+  u32 r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r) : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return r;
+}
+
 // four f32 -> 16 bits of E2M1 codes with hardware stochastic rounding; v0 lands in the lowest nibble
 // and consumes byte 0 of rbits, v3 the highest nibble and byte 3.
 __device__ __forceinline__ u32 e2m1x4_rs(float v0, float v1, float v2, float v3, u32 rbits) {
@@ -74,23 +87,58 @@ __device__ __forceinline__ long long sw_off(long long r, int c, int ncb) {
   return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
 }
 
-__device__ __forceinline__ float tensor_scale(float amax, float k) {
-  return fmaxf(__fdiv_rn(amax * k, kFp4E4m3), kTiny);
+// Per-tensor constants of a quantizer launch.
+struct TensorScale {
+  float gs;      // max(k*amax/2688, 1e-30): the FP32 tensor scale
+  float r6;      // 1/(6*gs), biased up by 2^-20: fast path of the block-scale argument
+  float inv_gs;  // 2688/(k*amax), 0 for an all-zero tensor: the reference kernels' scale (llm-1b/nvq.cu:101)
+  const float* lut;   // shared memory, 128 entries: per scale byte, the multiplier that turns v into y
+};
+
+// Fill the per-CTA table: for round to nearest  lut[sb] = (1/(gs*bs))*(1+2^-20)  (biased fast path),
+// for stochastic rounding  lut[sb] = inv_gs/bs  (the exact multiplier).  Ends with a block barrier.
+template <int ROUNDING>
+__device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, float* lut) {
+  TensorScale t;
+  const float am = amax * k;
+  t.gs = fmaxf(__fdiv_rn(am, kFp4E4m3), kTiny);
+  t.r6 = __fmul_rn(__frcp_rn(__fmul_rn(t.gs, 6.0f)), 1.00000095367431640625f);
+  t.inv_gs = am > 0.f ? __fdiv_rn(kFp4E4m3, am) : 0.f;
+  t.lut = lut;
+  if (threadIdx.x < 128) {
+    const float bsf = e4m3_dec(threadIdx.x);
+    float m = 0.f;
+    if (threadIdx.x >= 1 && threadIdx.x <= 126)
+      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? __fmul_rn(__frcp_rn(__fmul_rn(t.gs, bsf)), 1.00000095367431640625f)
+                                            : __fdiv_rn(t.inv_gs, bsf);
+    lut[threadIdx.x] = m;
+  }
+  __syncthreads();
+  return t;
 }
+
+// The exact (slow) forms live in functions that are never inlined: a call cannot be turned into
+// straight-line speculated code, so the IEEE divisions really run only on the rare slow path.
+static __device__ __noinline__ float exact_scale_arg(float bmax, float gs) { return __fdiv_rn(__fdiv_rn(bmax, gs), 6.0f); }
+static __device__ __noinline__ float exact_scaled(float v, float gs, float bsf) { return __fdiv_rn(__fdiv_rn(v, gs), bsf); }
 
 // Quantize one block of 16 values that share a scale.
 //   v      the 16 values (x, or the Hadamard-transformed x)
 //   bmax   max |v| over everything that shares the scale (16 values, or a 16x16 weight block)
-//   gs     tensor scale
-// Defines  bs = e4m3(min((bmax/gs)/6, 448)),  y = (v/gs)/bs  in IEEE FP32 -- the operation order of
-// the reference's torch path -- and rounds y.  For round-to-nearest a fast path multiplies by a
-// reciprocal biased upward by 2^-20: the product then lies in (y, y*(1+1.5*2^-20)], so it rounds
-// like y unless it sits within 32 ulp above a rounding boundary (all boundaries have 21 zero low
-// mantissa bits); only then are the two divisions done.
+// Block scale, all modes:  bs = e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
+// Round to nearest:  y = (v/gs)/bs, the torch path's operation order.  Both the scale argument and y
+//   are first formed with a reciprocal biased upward by 2^-20: the product then lies in
+//   (exact, exact*(1+1.5*2^-20)], so it rounds like the exact value unless it sits within 32 ulp above
+//   a rounding boundary (E4M3 boundaries have 19 zero low mantissa bits, E2M1 boundaries 21); only
+//   then are the divisions done.
+// Stochastic rounding:  y = v * (inv_gs / bs), the reference kernels' form (llm-1b/nvq.cu:50,54) in
+//   IEEE arithmetic; the torch path draws torch.rand and so defines no bit-level result.
 template <int ROUNDING>
-__device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, float gs, u32 seed,
+__device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, const TensorScale& ts, u32 seed,
                                               u32 blk_idx, u32 elt_idx, uint2& codes, u32& sbyte) {
-  u32 sb = e4m3_enc(__fdiv_rn(__fdiv_rn(bmax, gs), 6.0f));
+  float sarg = __fmul_rn(bmax, ts.r6);
+  if (sarg < 0.03125f || (__float_as_uint(sarg) & 0x7FFE0u) == 0u) sarg = exact_scale_arg(bmax, ts.gs);
+  const u32 sb = e4m3_enc(sarg);
   sbyte = sb;
   u32 w[2] = {0u, 0u};
   if (sb == 0u) {
@@ -100,10 +148,9 @@ __device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, 
     codes = make_uint2(w[0], w[1]);
     return;
   }
-  const float bsf = e4m3_dec(sb);
+  const float kf = ts.lut[sb];
   float y[16];
   if (ROUNDING == NVFP4_ROUND_NEAREST) {
-    const float kf = __fmul_rn(__frcp_rn(__fmul_rn(gs, bsf)), 1.00000095367431640625f);
     u32 nearest = 0xFFFFFFFFu;
 #pragma unroll
     for (int i = 0; i < 16; i++) {
@@ -111,14 +158,16 @@ __device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, 
       nearest = min(nearest, __float_as_uint(y[i]) & 0x1FFFE0u);
     }
     if (nearest == 0u) {
+      const float bsf = e4m3_dec(sb);
 #pragma unroll
-      for (int i = 0; i < 16; i++) y[i] = __fdiv_rn(__fdiv_rn(v[i], gs), bsf);
+      for (int i = 0; i < 16; i++)
+        if ((__float_as_uint(y[i]) & 0x1FFFE0u) == 0u) y[i] = exact_scaled(v[i], ts.gs, bsf);
     }
-#pragma unroll
-    for (int i = 0; i < 16; i += 2) w[i >> 3] |= e2m1x2_rn(y[i], y[i + 1]) << ((i & 7) * 4);
+    w[0] = e2m1x8_rn(y);
+    w[1] = e2m1x8_rn(y + 8);
   } else {
 #pragma unroll
-    for (int i = 0; i < 16; i++) y[i] = __fdiv_rn(__fdiv_rn(v[i], gs), bsf);
+    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(v[i], kf);
     if (ROUNDING == NVFP4_ROUND_SR_HW) {
       const u32 hb = hash32(seed ^ hash32(blk_idx));
 #pragma unroll
@@ -132,10 +181,11 @@ __device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, 
       for (int i = 0; i < 16; i += 2) {
         const u32 h = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(hb + (u32)i)
                                                           : hash32(seed ^ (elt_idx + (u32)i) * 0x9E3779B9u);
-        const float a = sr_dither(y[i], h);
-        const float b = sr_dither(y[i + 1], (h >> 10) | (h << 22));
-        w[i >> 3] |= e2m1x2_rn(a, b) << ((i & 7) * 4);
+        y[i] = sr_dither(y[i], h);
+        y[i + 1] = sr_dither(y[i + 1], (h >> 10) | (h << 22));
       }
+      w[0] = e2m1x8_rn(y);
+      w[1] = e2m1x8_rn(y + 8);
     }
   }
   codes = make_uint2(w[0], w[1]);

@@ -72,19 +72,22 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   const int lane = threadIdx.x & 31;
   const int nchunk = C >> 3, nblk = C >> 4;
   const int nseg = (nchunk + 63) >> 6;
-  const long long nitems = (long long)R * nseg;
-  const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
-  const float gs = tensor_scale(__ldg(amax), 1.f);
-  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = gs;
-  for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < nitems; item += wstride) {
-    const long long r = item / nseg;
-    const int seg = (int)(item - r * nseg);
+  __shared__ float lut[128];
+  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 1.f, lut);
+  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = ts.gs;
+  // walk (row, segment) pairs with a fixed warp stride, without a division per item
+  const unsigned nwarps = gridDim.x * (blockDim.x >> 5);
+  const unsigned w0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int dr = (int)(nwarps / (unsigned)nseg), ds = (int)(nwarps % (unsigned)nseg);
+  int r = (int)(w0 / (unsigned)nseg), seg = (int)(w0 % (unsigned)nseg);
+  const bool odd = lane & 1;
+  for (; r < R; r += dr, seg += ds) {
+    if (seg >= nseg) { seg -= nseg; if (++r >= R) break; }
     const int c0 = seg * 64 + lane, c1 = c0 + 32;
-    const __nv_bfloat16* row = x + r * ldx;
+    const __nv_bfloat16* row = x + (long long)r * ldx;
     uint4 A = make_uint4(0, 0, 0, 0), B = make_uint4(0, 0, 0, 0);
     if (c0 < nchunk) A = ldg128(row + c0 * 8);
     if (c1 < nchunk) B = ldg128(row + c1 * 8);
-    const bool odd = lane & 1;
     uint4 snd = odd ? A : B, rcv;
     rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, 1); rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, 1);
     rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, 1); rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, 1);
@@ -96,9 +99,9 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
       float bmax = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; i++) bmax = fmaxf(bmax, fabsf(v[i]));
-      const long long b = r * nblk + blk;
+      const long long b = (long long)r * nblk + blk;
       uint2 o; u32 sb;
-      quant_block16<ROUNDING>(v, bmax, gs, seed, (u32)b, (u32)(b * 16), o, sb);
+      quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
       codes[b] = o;
       scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
     }
@@ -122,8 +125,9 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
   const int cchunk = blockIdx.x * 16 + (lane & 15);            // 8-column chunk index
   const int mb = blockIdx.y * 16 + warp * 2 + (lane >> 4);     // 16-token block index
   const int nmb = M >> 4;
-  const float gs = tensor_scale(__ldg(amax), 4.f);
-  if (gs_out && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *gs_out = gs;
+  __shared__ float lut[128];
+  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 4.f, lut);
+  if (gs_out && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *gs_out = ts.gs;
   if (cchunk * 8 >= C || mb >= nmb) return;
   uint4 raw[16];
   const __nv_bfloat16* p = x + (long long)mb * 16 * C + cchunk * 8;
@@ -154,7 +158,7 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
     const long long c = (long long)cchunk * 8 + j;
     const long long b = c * nmb + mb;
     uint2 o; u32 sb;
-    quant_block16<ROUNDING>(v, bmax, gs, seed, (u32)b, (u32)(b * 16), o, sb);
+    quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
     *reinterpret_cast<uint2*>(codes + b * 8) = o;
     scales[linear ? b : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb;
   }
@@ -171,10 +175,11 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nb = N >> 4, kb = K >> 4;
+  __shared__ float lut[128];
+  const TensorScale ts = make_tensor_scale<NVFP4_ROUND_NEAREST>(__ldg(amax), 1.f, lut);
+  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = ts.gs;
   if (warp >= (long long)nb * kb) return;
   const int bn = (int)(warp / kb), bk = (int)(warp - (long long)bn * kb);
-  const float gs = tensor_scale(__ldg(amax), 1.f);
-  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = gs;
   const int r = lane >> 1, c0 = (lane & 1) * 8;
   const T* src = w + (long long)(bn * 16 + r) * K + bk * 16 + c0;
   float v[16];
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
 #pragma unroll
   for (int i = 0; i < 8; i++) v[8 + i] = v[i];
   uint2 o; u32 sb;
-  quant_block16<NVFP4_ROUND_NEAREST>(v, bmax, gs, 0u, 0u, 0u, o, sb);
+  quant_block16<NVFP4_ROUND_NEAREST>(v, bmax, ts, 0u, 0u, 0u, o, sb);
   const u32 word = o.x;
   if (q) {
     q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;

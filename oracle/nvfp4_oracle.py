@@ -16,9 +16,11 @@ Conventions shared with the CUDA library
   * codes: E2M1, two per byte, low nibble = lower index (llm-1b/nvq.cu:2)
   * block scale: one unsigned E4M3 byte per 16 values along the contraction dim
   * tensor scale: gs = amax / 2688 (2688 = 6 * 448), FP32, division (small-model/model_ref.py:42)
-  * `y = (x / gs) / max(bs, 1e-30)` -- the division order of model_ref.nvfp4_1d
+  * round to nearest: `y = (x / gs) / max(bs, 1e-30)` -- the division order of model_ref.nvfp4_1d
     (small-model/model_ref.py:43-46); the reference kernels use the algebraically equal
-    `x * (2688/amax / bs)` (llm-1b/nvq.cu:47-54), which is not bit-identical in general.
+    `x * (2688/amax / bs)` (llm-1b/nvq.cu:47-54), which is not bit-identical in general
+  * stochastic rounding: `y = x * ((2688/amax) / bs)`, that kernel form in IEEE FP32, because the
+    torch path rounds with `torch.rand` and defines no bits; block scales are the same as for RN
   * a block whose scale byte is 0 stores code 0 with the sign of x (llm-1b/nvq.cu:50: k = 0);
     model_ref dequantizes such a block to 0 as well, so dequantized values always agree.
 """
@@ -280,13 +282,29 @@ def global_scale(amax, k=1.0):
     return np.maximum(np.float32(am / FP4_E4M3), TINY).astype(np.float32)
 
 
-def _quant_blocks(xb, sr_mode, rnd):
-    """xb: [..., 16] float32 already divided by gs, one scale per leading index.
-    Returns (codes [...,16] uint8, scale bytes [...])."""
+def inv_global_scale(amax, k=1.0):
+    """2688 / (k*amax), 0 for an all-zero tensor: the scale of the reference kernels
+    (llm-1b/nvq.cu:100-101, :137-138)."""
+    am = np.float32(amax) * np.float32(k)
+    return np.float32(FP4_E4M3 / am) if am > 0 else np.float32(0)
+
+
+def _quant_blocks(v, gs, inv_gs, sr_mode, rnd):
+    """v: [..., 16] float32 values sharing one scale per leading index.
+    Block scale (all modes): e4m3(((max|v|)/gs)/6), the torch path (model_ref.py:43-44).
+    Round to nearest: y = (v/gs)/bs (model_ref.py:45).  Stochastic: y = v * (inv_gs/bs), the
+    reference kernels' multiply form (llm-1b/nvq.cu:50,54) in IEEE FP32 -- model_ref draws
+    torch.rand for SR and so fixes no bits.  Returns (codes [...,16] uint8, scale bytes [...])."""
+    xb = (v / gs).astype(np.float32)
     bmax = np.max(np.abs(xb), axis=-1)
     sbyte = e4m3_encode((bmax / FP4_MAX).astype(np.float32))
     bs = e4m3_decode(sbyte)
-    y = (xb / np.maximum(bs, TINY)[..., None]).astype(np.float32)
+    if sr_mode == SR_NONE:
+        y = (xb / np.maximum(bs, TINY)[..., None]).astype(np.float32)
+    else:
+        with np.errstate(divide="ignore", invalid="ignore"):
+            k = np.where(bs > 0, np.float32(inv_gs) / bs, np.float32(0)).astype(np.float32)
+        y = (v * k[..., None]).astype(np.float32)
     return _round_blocks(xb, y, sbyte, sr_mode, rnd), sbyte
 
 
@@ -326,10 +344,9 @@ def quant_rows(x, amax=None, sr_mode=SR_NONE, seed=0):
     assert C % 16 == 0
     am = amax_f32(x) if amax is None else np.float32(amax)
     gs = global_scale(am)
-    xb = (x.reshape(R, C // 16, 16) / gs).astype(np.float32)
     blk = np.arange(R * (C // 16), dtype=np.uint64).reshape(R, C // 16)
     rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
-    codes, sbyte = _quant_blocks(xb, sr_mode, rnd)
+    codes, sbyte = _quant_blocks(x.reshape(R, C // 16, 16), gs, inv_global_scale(am), sr_mode, rnd)
     return pack_codes(codes.reshape(R, C)), sbyte, gs
 
 
@@ -364,10 +381,9 @@ def quant_cols_rht(x, signs, amax=None, sr_mode=SR_NONE, seed=0):
     am = amax_f32(x) if amax is None else np.float32(amax)
     gs = global_scale(am, 4.0)
     t = rht16_cols(x, signs)
-    xb = (t / gs).astype(np.float32)
     blk = np.arange(C * (M // 16), dtype=np.uint64).reshape(C, M // 16)
     rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
-    codes, sbyte = _quant_blocks(xb, sr_mode, rnd)
+    codes, sbyte = _quant_blocks(t, gs, inv_global_scale(am, 4.0), sr_mode, rnd)
     return pack_codes(codes.reshape(C, M)), sbyte, gs
 
 
