@@ -81,13 +81,22 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   const int dr = (int)(nwarps / (unsigned)nseg), ds = (int)(nwarps % (unsigned)nseg);
   int r = (int)(w0 / (unsigned)nseg), seg = (int)(w0 % (unsigned)nseg);
   const bool odd = lane & 1;
-  for (; r < R; r += dr, seg += ds) {
-    if (seg >= nseg) { seg -= nseg; if (++r >= R) break; }
-    const int c0 = seg * 64 + lane, c1 = c0 + 32;
+  uint4 A = make_uint4(0, 0, 0, 0), B = make_uint4(0, 0, 0, 0);
+  if (r < R) {
     const __nv_bfloat16* row = x + (long long)r * ldx;
-    uint4 A = make_uint4(0, 0, 0, 0), B = make_uint4(0, 0, 0, 0);
-    if (c0 < nchunk) A = ldg128(row + c0 * 8);
-    if (c1 < nchunk) B = ldg128(row + c1 * 8);
+    if (seg * 64 + lane < nchunk) A = ldg128(row + (seg * 64 + lane) * 8);
+    if (seg * 64 + lane + 32 < nchunk) B = ldg128(row + (seg * 64 + lane + 32) * 8);
+  }
+  while (r < R) {
+    // next item of this warp: its loads are issued before the current item is processed
+    int rn = r + dr, sn = seg + ds;
+    if (sn >= nseg) { sn -= nseg; rn++; }
+    uint4 An = make_uint4(0, 0, 0, 0), Bn = make_uint4(0, 0, 0, 0);
+    if (rn < R) {
+      const __nv_bfloat16* row = x + (long long)rn * ldx;
+      if (sn * 64 + lane < nchunk) An = ldg128(row + (sn * 64 + lane) * 8);
+      if (sn * 64 + lane + 32 < nchunk) Bn = ldg128(row + (sn * 64 + lane + 32) * 8);
+    }
     uint4 snd = odd ? A : B, rcv;
     rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, 1); rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, 1);
     rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, 1); rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, 1);
@@ -105,6 +114,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
       codes[b] = o;
       scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
     }
+    r = rn; seg = sn; A = An; B = Bn;
   }
 }
 
@@ -139,28 +149,33 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
     const u32 f = ((signs >> i) & 1u) ? 0x80008000u : 0u;
     raw[i].x ^= f; raw[i].y ^= f; raw[i].z ^= f; raw[i].w ^= f;
   }
+  // four rounds of two columns: the packed words are rotated so that the loop body (two block
+  // quantizations) exists once in the instruction stream
+#pragma unroll 1
+  for (int jw = 0; jw < 4; jw++) {
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-      const u32 w = (j >> 1) == 0 ? raw[i].x : (j >> 1) == 1 ? raw[i].y : (j >> 1) == 2 ? raw[i].z : raw[i].w;
-      v[i] = (j & 1) ? __uint_as_float(w & 0xFFFF0000u) : __uint_as_float(w << 16);
-    }
-#pragma unroll
-    for (int h = 1; h < 16; h <<= 1)
+    for (int hf = 0; hf < 2; hf++) {
+      float v[16];
 #pragma unroll
       for (int i = 0; i < 16; i++)
-        if (!(i & h)) { const float a = v[i], b = v[i + h]; v[i] = __fadd_rn(a, b); v[i + h] = __fsub_rn(a, b); }
-    float bmax = 0.f;
+        v[i] = hf ? __uint_as_float(raw[i].x & 0xFFFF0000u) : __uint_as_float(raw[i].x << 16);
 #pragma unroll
-    for (int i = 0; i < 16; i++) { v[i] = __fmul_rn(v[i], 0.25f); bmax = fmaxf(bmax, fabsf(v[i])); }
-    const long long c = (long long)cchunk * 8 + j;
-    const long long b = c * nmb + mb;
-    uint2 o; u32 sb;
-    quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
-    *reinterpret_cast<uint2*>(codes + b * 8) = o;
-    scales[linear ? b : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb;
+      for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+          if (!(i & h)) { const float a = v[i], b = v[i + h]; v[i] = __fadd_rn(a, b); v[i + h] = __fsub_rn(a, b); }
+      float bmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; i++) { v[i] = __fmul_rn(v[i], 0.25f); bmax = fmaxf(bmax, fabsf(v[i])); }
+      const long long c = (long long)cchunk * 8 + jw * 2 + hf;
+      const long long b = c * nmb + mb;
+      uint2 o; u32 sb;
+      quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
+      *reinterpret_cast<uint2*>(codes + b * 8) = o;
+      scales[linear ? b : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) { raw[i].x = raw[i].y; raw[i].y = raw[i].z; raw[i].z = raw[i].w; }
   }
 }
 
