@@ -169,6 +169,28 @@ int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, long long ld
                       int accumulate, int splitk, void* workspace, size_t workspace_bytes,
                       int* status, void* stream);
 
+/*
+ * nvfp4_gemm_linear without a workspace argument, for callers that cannot obtain device memory at
+ * call time (no counterpart in the reference, whose launcher always allocates with torch:
+ * llm-1b/fp4ops.py:67-72).  The re-swizzled scales go into a fixed array inside the library, so the
+ * call allocates nothing -- no cudaMalloc/cudaFree, no allocating library routine.
+ *   limit    (M + N) * K / 16 <= nvfp4_gemm_linear_noalloc_max_scratch() (8 MiB); larger problems are
+ *            rejected with NVFP4_ERR_TOO_LARGE before anything is launched
+ *   cost     every GPU on which the library is loaded holds those 8 MiB until the process exits
+ *   first call on a device: looks up the array's device address (cudaGetSymbolAddress) with that
+ *            device current; make this first call outside any stream capture
+ *   sharing  all calls on a device use the same array, which keeps the previous call's bytes (each
+ *            call overwrites what it reads, nothing has to start at zero); two calls whose kernels
+ *            can overlap on the GPU -- different streams without ordering -- race on it
+ * Everything else (arguments, results, status codes) is exactly nvfp4_gemm_linear.
+ */
+size_t nvfp4_gemm_linear_noalloc_max_scratch(void);
+int nvfp4_gemm_linear_noalloc(const void* a, const void* sa, long long lda, long long ldsa,
+                              const void* b, const void* sb, long long ldb, long long ldsb,
+                              void* c, int c_dtype, long long ldc, int M, int N, int K,
+                              int alpha_mode, const float* pa, const float* pb, float ka, float kb,
+                              int accumulate, int splitk, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

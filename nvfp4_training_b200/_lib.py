@@ -35,6 +35,9 @@ SIGNATURES = {
     "nvfp4_gemm_linear_workspace_bytes": (_sz, [_i, _i, _i]),
     "nvfp4_gemm_linear": (_i, [_vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f,
                                _i, _i, _vp, _sz, _vp, _vp]),
+    "nvfp4_gemm_linear_noalloc_max_scratch": (_sz, []),
+    "nvfp4_gemm_linear_noalloc": (_i, [_vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f,
+                                       _i, _i, _vp, _vp]),
 }
 
 _lib = None
