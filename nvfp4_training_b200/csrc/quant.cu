@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
 // pairs swap halves so each lane owns one whole 16-block (even lanes: blocks 0..15 of the segment,
 // odd lanes: blocks 16..31), then quantize it from registers.
 template <int ROUNDING>
-__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+__global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                           uint2* __restrict__ codes, unsigned char* __restrict__ scales,
                                                           const float* __restrict__ amax, int R, int C, int linear,
                                                           u32 seed, const u32* __restrict__ seed_dev,

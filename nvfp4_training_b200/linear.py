@@ -51,17 +51,19 @@ def linear_fwd(x, qw):
     return nvq.mm(nvq.quant_rows(x, am=am), qw), am
 
 
-def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS):
+def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
+               sr_mode=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
-    returned; otherwise a new tensor of `wgrad_dtype` is returned."""
+    returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
+    rounding (default: the module default of `nvq`)."""
     gy = gy.contiguous()
     ag = nvq.amax(gy)
     # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
-    gx = nvq.mm(nvq.quant_rows(gy, sr=True, seed=seed, am=ag), qwt)
+    gx = nvq.mm(nvq.quant_rows(gy, sr=True, seed=seed, am=ag, sr_mode=sr_mode), qwt)
     # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
-    qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag)
+    qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag, sr_mode=sr_mode)
     qxt = nvq.quant_cols_rht(x, signs, am=am_x)
     if gw_out is not None:
         gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=True)

@@ -14,7 +14,8 @@ import torch
 
 from . import _lib as L
 
-# rounding used when a quantizer is called with sr=True
+# rounding used when a quantizer is called with sr=True (a per-call `sr_mode` overrides it):
+# ROUND_SR_DITHER = the reference's rounding and random stream, ROUND_SR_HW = hardware cvt.rs
 SR_MODE = L.ROUND_SR_DITHER
 
 
@@ -43,7 +44,7 @@ def _new_gs(am):
     return torch.empty(1, dtype=torch.float32, device=am.device)
 
 
-def quant_rows(x, sr=False, seed=0, am=None):
+def quant_rows(x, sr=False, seed=0, am=None, sr_mode=None):
     """x [R, C] bf16 (row-contiguous) -> Q quantized along C (llm-1b/nvq.py:47-57)."""
     L.require_cuda(x)
     R, C = x.shape
@@ -55,12 +56,12 @@ def quant_rows(x, sr=False, seed=0, am=None):
     s = torch.empty(R * C // 16, dtype=torch.uint8, device=x.device)
     gs = _new_gs(am)
     L.check(L.load().nvfp4_quant_rows(L.ptr(x), x.stride(0), R, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am),
-                                      L.ptr(gs), SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed), L.stream()),
+                                      L.ptr(gs), (sr_mode or SR_MODE) if sr else L.ROUND_NEAREST, *L.seed_args(seed), L.stream()),
             "quant_rows")
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 
 
-def quant_cols_rht(x, signs, sr=False, seed=0, am=None):
+def quant_cols_rht(x, signs, sr=False, seed=0, am=None, sr_mode=None):
     """x [M, C] -> Q of x^T [C, M] quantized along M, after a 16-pt RHT along M (llm-1b/nvq.py:60-70)."""
     L.require_cuda(x)
     M, C = x.shape
@@ -73,7 +74,7 @@ def quant_cols_rht(x, signs, sr=False, seed=0, am=None):
     s = torch.empty(C * M // 16, dtype=torch.uint8, device=x.device)
     gs = _new_gs(am)
     L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gs),
-                                          signs & 0xFFFF, SR_MODE if sr else L.ROUND_NEAREST, *L.seed_args(seed),
+                                          signs & 0xFFFF, (sr_mode or SR_MODE) if sr else L.ROUND_NEAREST, *L.seed_args(seed),
                                           L.stream()), "quant_cols_rht")
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 

@@ -59,6 +59,12 @@ def main():
                               ("quant_cols_rht_sr", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, am=am), 2.5625)):
             us = timed(fn, a.iters)
             out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
+        nvq.SR_MODE = _lib.ROUND_SR_HW
+        for name, fn in (("quant_rows_sr_hw", lambda: nvq.quant_rows(x, sr=True, seed=1, am=am)),
+                         ("quant_cols_rht_sr_hw", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, am=am))):
+            us = timed(fn, a.iters)
+            out[name] = {"us": us, "gbs": n * 2.5625 / us / 1e3}
+        nvq.SR_MODE = _lib.ROUND_SR_DITHER
         w = torch.randn(a.N, a.K, generator=g, device="cuda").bfloat16()
         us = timed(lambda: nvq.quant_w2d(w), a.iters)
         out["amax+quant_w2d"] = {"us": us, "gbs": a.N * a.K * 5.125 / us / 1e3}

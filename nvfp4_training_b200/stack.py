@@ -19,7 +19,7 @@ from dataclasses import dataclass
 
 import torch
 
-from . import nvq
+from . import _lib, nvq
 from .linear import _RHT_SIGNS, linear_bwd, linear_fwd
 
 
@@ -86,8 +86,10 @@ def student_t(shape, gen, device, df=3):
 
 
 class LinearStack:
-    def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None):
+    def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
+                 sr_mode=_lib.ROUND_SR_HW):
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
+        self.sr_mode = sr_mode       # gradients: hardware cvt.rs stochastic rounding, counter-based random words
         self.use_graphs = use_graphs
         gen = torch.Generator(device=self.device).manual_seed(seed)
         self.blocks = []
@@ -159,7 +161,7 @@ class LinearStack:
         for p in reversed(projs):
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(self.x_pool[p.name], p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
-                               gw_out=p.gw, signs=_RHT_SIGNS)
+                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode)
             p.gx = gx if keep else None
 
     def capture(self):
