@@ -148,8 +148,9 @@ int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, cons
                int accumulate, int splitk, int* status, void* stream);
 
 /*
- * Tuning hook: force the output-tile width of nvfp4_gemm (128 or 256 columns; 0 restores the built-in
- * choice).  Process-wide; 256 is ignored for calls whose N is not a multiple of 256.  No reference
+ * Tuning hook: force the kernel variant of nvfp4_gemm: 128 or 256 = one-CTA tiles of that many columns,
+ * 512 = the CTA-pair kernel (256x256 tiles over an SM pair, needs M and N multiples of 256), 0 restores the
+ * built-in choice.  Process-wide; a variant the shape does not allow is ignored.  No reference
  * counterpart (the reference kernel has one fixed 128x128 tile, llm-1b/fp4k.cu:164-167).
  */
 int nvfp4_gemm_force_tile_n(int bn);

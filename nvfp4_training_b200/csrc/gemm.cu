@@ -430,6 +430,346 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ======================================================================================== CTA-pair kernel
+// Two CTAs of one cluster (an SM pair) share every 256x256 output tile: tcgen05.mma.cta_group::2 with
+// M = 256 reads A rows 0..127 and B rows 0..127 from the leader CTA's shared memory and rows 128..255
+// from its peer's, and leaves each CTA the accumulator of its own 128 rows in its own tensor memory.
+// Each CTA therefore loads only half of B per K tile (38 KB a stage instead of 54 KB), which is what
+// the operand pipeline -- bound by bytes in flight against the ~1 us load latency -- needs, and the
+// shared memory saved holds a fifth stage plus a staging buffer for coalesced output stores.
+//   both CTAs   warp 0 loads its A rows, its half of B, its A scales and all B scales with
+//               cp.async.bulk.tensor (cta_group::2 form: the bytes are counted on the LEADER's `full`
+//               barrier; no multicast), after waiting on its own `empty` barrier
+//   leader      warp 1 copies scales to tensor memory (both CTAs at once), issues the MMAs and commits
+//               to the `empty` / `acc_full` barriers of both CTAs (one commit per CTA)
+//   both CTAs   warps 2..9 drain their accumulator, arrive on the leader's `acc_empty` barrier, then
+//               convert and store through a per-warp 4 KB staging area so that every global store
+//               instruction writes whole 128-byte (FP32) or 64-byte (bf16) row segments
+namespace pair {
+constexpr int kStages = 5;
+constexpr int kABytes = 16384, kBBytes = 16384, kSFABytes = 2048, kSFBBytes = 4096;
+constexpr int kStageBytes = kABytes + kBBytes + kSFABytes + kSFBBytes;      // 38912 = 38 * 1024
+constexpr int kStagingBytes = kEpiWarps * 4096;
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+constexpr u32 kTxBytes = 2u * kStageBytes;                                  // both CTAs' loads of one stage
+constexpr int kBN = 256;
+constexpr int kSfaCol = 256, kSfbCol = 272, kSfBufCols = 48, kTmemCols = 512;
+}  // namespace pair
+
+__device__ __forceinline__ u32 cluster_ctarank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ u32 map_to_cta(u32 saddr, u32 rank) {
+  u32 r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(u32 cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(u32 dst, const CUtensorMap* map, int x, int y, u32 bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(u32 dst, const CUtensorMap* map, int x, int y, int z, u32 bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem2_alloc(u32 smem_dst, u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem2_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem2_dealloc(u32 taddr, u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc2_commit(u32 cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc2_cp_sf(u32 taddr, u64 sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc2_mma_nvf4(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 sfa_tmem, u32 sfb_tmem,
+                                             u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// instruction descriptor of the pair MMA: M = 256 (16 at bit 24), N = 256
+__host__ __device__ constexpr u32 make_idesc_pair() {
+  return (1u << 7) | (1u << 10) | ((u32)(256 >> 3) << 17) | ((u32)(256 >> 4) << 24);
+}
+
+struct PairParams {
+  void* c;
+  const float* pa;
+  const float* pb;
+  int* status;
+  long long ldc;
+  float kscale;
+  int M, N, K;
+  int alpha_mode;
+  int c_fp32;
+  int atomic;
+  int splitk;
+  int ktiles_per_split;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                      const PairParams p) {
+  using namespace pair;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* staging = smem + kStages * kStageBytes;
+  unsigned char* bar_mem = staging + kStagingBytes;
+  u64* full_bar = reinterpret_cast<u64*>(bar_mem);
+  u64* empty_bar = full_bar + kStages;
+  u64* acc_full = empty_bar + kStages;
+  u64* acc_empty = acc_full + 1;
+  u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const u32 rank = cluster_ctarank();                 // 0 = leader (issues the MMAs), 1 = peer
+  const int tiles_m = p.M / 256, tiles_n = p.N / kBN;
+  const int ktiles = (p.K + kBK - 1) / kBK;
+  const int num_work = tiles_m * tiles_n * p.splitk;
+  const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+  const u32 smem_base = smem_u32(smem);
+  const u32 full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+  const u32 accf = smem_u32(acc_full), acce = smem_u32(acc_empty);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(accf, 1);
+    mbar_init(acce, 2 * kEpiWarps);                   // the epilogue warps of both CTAs
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem2_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem2_relinquish();
+  }
+  tc_fence_before();
+  cluster_sync_all();                                 // barriers of both CTAs exist before anyone signals them
+  tc_fence_after();
+  const u32 tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
+    }
+    const u32 leader_full0 = map_to_cta(full0, 0);    // the leader's `full` barriers in cluster address space
+    int stage = 0; u32 phase = 0;
+    u32 st_addr = smem_base;
+    bool ok = true;
+    for (int w = cid; w < num_work && ok; w += ncl) {
+      const int mt = w % tiles_m;
+      const int rest = w / tiles_m;
+      const int nt = rest % tiles_n;
+      const int z = rest / tiles_n;
+      const int kt0 = z * p.ktiles_per_split;
+      const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+      const int ya = mt * 256 + (int)rank * 128, yb = nt * kBN + (int)rank * 128;
+      const int za = mt * 2 + (int)rank, zb = nt * 2;
+      for (int kt = kt0; kt < kt1; kt++) {
+        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag))) { ok = false; break; }
+        if (elect_one()) {
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, kTxBytes);
+          const u32 bar = leader_full0 + 8 * stage;
+          tma2_load_2d(st_addr, &map_a, kt * kBKBytes, ya, bar);
+          tma2_load_2d(st_addr + kABytes, &map_b, kt * kBKBytes, yb, bar);
+          tma2_load_3d(st_addr + kABytes + kBBytes, &map_sfa, 0, kt * 4, za, bar);
+          tma2_load_3d(st_addr + kABytes + kBBytes + kSFABytes, &map_sfb, 0, kt * 4, zb, bar);
+        }
+        st_addr += kStageBytes;
+        if (++stage == kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
+      }
+    }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0) {
+      constexpr u32 idesc = make_idesc_pair();
+      u32 sfa_t = tmem_base + kSfaCol, sfb_t = tmem_base + kSfbCol;
+      u32 sf_flip = kSfBufCols;
+      const u32 empty_peer0 = map_to_cta(empty0, 1), accf_peer = map_to_cta(accf, 1);
+      int stage = 0; u32 phase = 0;
+      const u32 a_lo0 = (smem_base >> 4) | (1u << 16);
+      u32 a_lo = a_lo0;
+      u32 acc_phase = 0;
+      bool ok = true;
+      for (int w = cid; w < num_work && ok; w += ncl) {
+        const int z = w / (tiles_m * tiles_n);
+        const int kt0 = z * p.ktiles_per_split;
+        const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
+        // both CTAs' epilogues must have drained the accumulator
+        if (!__all_sync(0xffffffffu, mbar_wait(acce, acc_phase ^ 1u, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        u32 accum = 0u;
+        for (int kt = kt0; kt < kt1; kt++) {
+          if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag))) { ok = false; break; }
+          const u32 b_lo = a_lo + (kABytes >> 4);
+          const u32 sfa_lo = (a_lo & 0xFFFFu) + ((kABytes + kBBytes) >> 4);
+          const u32 sfb_lo = sfa_lo + (kSFABytes >> 4);
+          const int krem = p.K - kt * kBK;
+          const int kchunks = krem >= kBK ? 4 : (krem >> 6);
+          if (elect_one()) {
+            if (kchunks == 4) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                tc2_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
+                tc2_cp_sf(sfb_t + 8 * j, pack64(sfb_lo + 32 * j, kDescHiSF));
+                tc2_cp_sf(sfb_t + 8 * j + 4, pack64(sfb_lo + 128 + 32 * j, kDescHiSF));
+              }
+              tc2_mma_nvf4(tmem_base, pack64(a_lo, kDescHiAB), pack64(b_lo, kDescHiAB), idesc, sfa_t, sfb_t, accum);
+#pragma unroll
+              for (int j = 1; j < 4; j++)
+                tc2_mma_nvf4(tmem_base, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                             sfb_t + 8 * j, 1u);
+            } else {
+              for (int j = 0; j < kchunks; j++) {
+                tc2_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
+                tc2_cp_sf(sfb_t + 8 * j, pack64(sfb_lo + 32 * j, kDescHiSF));
+                tc2_cp_sf(sfb_t + 8 * j + 4, pack64(sfb_lo + 128 + 32 * j, kDescHiSF));
+              }
+              for (int j = 0; j < kchunks; j++)
+                tc2_mma_nvf4(tmem_base, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                             sfb_t + 8 * j, (j > 0) ? 1u : accum);
+            }
+            // free the stage in both CTAs once these MMAs have read it
+            tc2_commit(empty0 + 8 * stage);
+            tc2_commit(empty_peer0 + 8 * stage);
+          }
+          accum = 1u;
+          sfa_t += sf_flip; sfb_t += sf_flip; sf_flip = 0u - sf_flip;
+          a_lo += kStageBytes >> 4;
+          if (++stage == kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
+        }
+        if (!ok) break;
+        if (elect_one()) { tc2_commit(accf); tc2_commit(accf_peer); }     // accumulators complete in both CTAs
+        acc_phase ^= 1u;
+      }
+      if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const u32 sw = smem_u32(staging) + (u32)(warp - 2) * 4096u;       // this warp's staging area
+    const u32 acce_leader = map_to_cta(acce, 0);
+    u32 acc_phase = 0;
+    bool ok = true;
+    for (int w = cid; w < num_work && ok; w += ncl) {
+      const int mt = w % tiles_m;
+      const int nt = (w / tiles_m) % tiles_n;
+      if (!__all_sync(0xffffffffu, mbar_wait(accf, acc_phase, abort_flag))) { ok = false; break; }
+      acc_phase ^= 1u;
+      tc_fence_after();
+      u32 r[128];
+      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (u32)(half * 128);
+#pragma unroll
+      for (int c = 0; c < 4; c++) tc_ld32(t_row + c * 32, *reinterpret_cast<u32(*)[32]>(&r[c * 32]));
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acce_leader);
+
+      float alpha = 1.f;
+      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
+      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
+      const long long row0 = (long long)mt * 256 + rank * 128 + quad * 32;      // first row of this warp
+      const long long col0 = (long long)nt * kBN + half * 128;
+      const u32 wr = sw + (u32)lane * 128u;                     // staging row of this lane (write phase)
+      const int rr = lane >> 3, ru = lane & 7;                  // read phase: row within a group of 4, 16-byte unit
+      if (p.c_fp32) {
+        float* cbase = static_cast<float*>(p.c) + row0 * p.ldc + col0;
+#define NVFP4_PAIR_F32_ROUND(C)                                                                                           \
+        {                                                                                                                  \
+          _Pragma("unroll") for (int u = 0; u < 8; u++) {                                                                  \
+            const int i = (C) * 32 + u * 4;                                                                                \
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (u32)((u ^ (lane & 7)) << 4)),            \
+                         "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),                      \
+                         "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");      \
+          }                                                                                                                \
+          __syncwarp();                                                                                                    \
+          _Pragma("unroll") for (int it = 0; it < 8; it++) {                                                               \
+            const int row = it * 4 + rr;                                                                                   \
+            float4 v;                                                                                                      \
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)           \
+                         : "r"(sw + (u32)row * 128u + (u32)((ru ^ (row & 7)) << 4)) : "memory");                         \
+            float* dst = cbase + (long long)row * p.ldc + (C) * 32 + ru * 4;                                               \
+            if (p.atomic)                                                                                                  \
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),      \
+                           "f"(v.w) : "memory");                                                                          \
+            else                                                                                                           \
+              *reinterpret_cast<float4*>(dst) = v;                                                                         \
+          }                                                                                                                \
+          __syncwarp();                                                                                                    \
+        }
+        NVFP4_PAIR_F32_ROUND(0) NVFP4_PAIR_F32_ROUND(1) NVFP4_PAIR_F32_ROUND(2) NVFP4_PAIR_F32_ROUND(3)
+#undef NVFP4_PAIR_F32_ROUND
+      } else {
+        __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0;
+#define NVFP4_PAIR_BF16_ROUND(C)                                                                                          \
+        {                                                                                                                  \
+          _Pragma("unroll") for (int u = 0; u < 8; u++) {                                                                  \
+            const int i = (C) * 64 + u * 8;                                                                                \
+            uint4 o;                                                                                                       \
+            __nv_bfloat162 h;                                                                                              \
+            h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);     \
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h); \
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h); \
+            h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h); \
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (u32)((u ^ (lane & 7)) << 4)), "r"(o.x),    \
+                         "r"(o.y), "r"(o.z), "r"(o.w) : "memory");                                                        \
+          }                                                                                                                \
+          __syncwarp();                                                                                                    \
+          _Pragma("unroll") for (int it = 0; it < 8; it++) {                                                               \
+            const int row = it * 4 + rr;                                                                                   \
+            uint4 v;                                                                                                       \
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)           \
+                         : "r"(sw + (u32)row * 128u + (u32)((ru ^ (row & 7)) << 4)) : "memory");                         \
+            *reinterpret_cast<uint4*>(cbase + (long long)row * p.ldc + (C) * 64 + ru * 8) = v;                             \
+          }                                                                                                                \
+          __syncwarp();                                                                                                    \
+        }
+        NVFP4_PAIR_BF16_ROUND(0) NVFP4_PAIR_BF16_ROUND(1)
+#undef NVFP4_PAIR_BF16_ROUND
+      }
+    }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) {
+    const u64 t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();                                 // neither CTA frees tensor memory or exits while the other still works
+  if (warp == 1) {
+    tc_fence_after();
+    tmem2_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -464,9 +804,23 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 static int g_debug = 0;
 extern "C" int nvfp4_gemm_debug(int flags) { g_debug = flags; return 0; }
 #endif
-static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced tile width (tuning and tests)
+static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
 
-struct DevInfo { int sms; bool attr128, attr256; };
+// Swizzled scale bytes of an [R, K/16] operand seen as a 3-D tensor of 32-bit words:
+// {128 words of one 512-byte tile, K/64 tiles along K, R/128 row blocks}; box = 4 tiles x `rb_box` row blocks.
+static bool make_sf_map(CUtensorMap* map, const void* base, long long rows, long long K, int rb_box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {128, (cuuint64_t)(K / 64), (cuuint64_t)(rows / 128)};
+  const cuuint64_t strides[2] = {512, (cuuint64_t)(K / 64) * 512};
+  const cuuint32_t box[3] = {128, 4, (cuuint32_t)rb_box};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct DevInfo { int sms; bool attr128, attr256, attr_pair; };
 static DevInfo* dev_info() {
   static DevInfo info[64];
   static bool init[64] = {false};
@@ -475,7 +829,7 @@ static DevInfo* dev_info() {
   if (!init[dev]) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return nullptr;
-    info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = false;
+    info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = info[dev].attr_pair = false;
     init[dev] = true;
   }
   return &info[dev];
@@ -540,6 +894,35 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   if (g_force_bn == 256 && N % 256 == 0) wide = true;
   const int bn = wide ? 256 : 128;
 
+  // CTA-pair kernel (256x256 tiles over an SM pair): the fast path whenever the shape allows it
+  bool use_pair = (M % 256 == 0) && (N % 256 == 0) && g_force_bn != 128 && g_force_bn != 256;
+  if (g_force_bn == 0 && (long long)(M / 256) * (N / 256) * splitk < di->sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
+  if (use_pair) {
+    CUtensorMap ma, mb, msa, msb;
+    if (!make_map(&ma, a, M, K / 2, lda, 128) || !make_map(&mb, b, N, K / 2, ldb, 128) ||
+        !make_sf_map(&msa, sa, M, K, 1) || !make_sf_map(&msb, sb, N, K, 2))
+      return NVFP4_ERR_CUDA;
+    PairParams pp;
+    pp.c = c; pp.pa = pa; pp.pb = pb; pp.status = status; pp.ldc = ldc;
+    pp.kscale = ka * kb * (1.f / (kFp4E4m3 * kFp4E4m3));
+    pp.M = M; pp.N = N; pp.K = K;
+    pp.alpha_mode = alpha_mode;
+    pp.c_fp32 = c_dtype == NVFP4_DTYPE_FP32;
+    pp.atomic = (accumulate || splitk > 1) ? 1 : 0;
+    pp.splitk = splitk;
+    pp.ktiles_per_split = per;
+    if (!di->attr_pair) {
+      if (cudaFuncSetAttribute(gemm_nvf4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes) != cudaSuccess)
+        return NVFP4_ERR_CUDA;
+      di->attr_pair = true;
+    }
+    const long long work = (long long)(M / 256) * (N / 256) * splitk;
+    const long long clusters = work < di->sms / 2 ? work : di->sms / 2;
+    gemm_nvf4_pair_kernel<<<(unsigned)(2 * clusters), kThreads, pair::kSmemBytes, st>>>(ma, mb, msa, msb, pp);
+    NVFP4_LAUNCH_CHECK();
+    return NVFP4_OK;
+  }
+
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, M, K / 2, lda, kBM) || !make_map(&mb, b, N, K / 2, ldb, bn)) return NVFP4_ERR_CUDA;
 
@@ -585,7 +968,7 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
 }
 
 extern "C" int nvfp4_gemm_force_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256) return NVFP4_ERR_ENUM;
+  if (bn != 0 && bn != 128 && bn != 256 && bn != 512) return NVFP4_ERR_ENUM;
   g_force_bn = bn;
   return NVFP4_OK;
 }
