@@ -149,8 +149,8 @@ int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, cons
 
 /*
  * Tuning hook: force the kernel variant of nvfp4_gemm: 128 or 256 = one-CTA tiles of that many columns,
- * 512 = the CTA-pair kernel (256x256 tiles over an SM pair, needs M and N multiples of 256), 0 restores the
- * built-in choice.  Process-wide; a variant the shape does not allow is ignored.  No reference
+ * 512 / 448 / 384 = the CTA-pair kernel with 256x256 / 256x192 / 256x128 tiles over an SM pair (needs M a
+ * multiple of 256; 512 also N), 0 restores the built-in choice.  Process-wide; a variant the shape does not allow is ignored.  No reference
  * counterpart (the reference kernel has one fixed 128x128 tile, llm-1b/fp4k.cu:164-167).
  */
 int nvfp4_gemm_force_tile_n(int bn);

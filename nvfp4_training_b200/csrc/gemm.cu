@@ -154,6 +154,13 @@ __device__ __forceinline__ void tc_ld32(u32 taddr, u32 (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(u32 taddr, u32 (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets in 16-byte
@@ -445,16 +452,34 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //   both CTAs   warps 2..9 drain their accumulator, arrive on the leader's `acc_empty` barrier, then
 //               convert and store through a per-warp 4 KB staging area so that every global store
 //               instruction writes whole 128-byte (FP32) or 64-byte (bf16) row segments
-namespace pair {
-constexpr int kStages = 5;
-constexpr int kABytes = 16384, kBBytes = 16384, kSFABytes = 2048, kSFBBytes = 4096;
-constexpr int kStageBytes = kABytes + kBBytes + kSFABytes + kSFBBytes;      // 38912 = 38 * 1024
-constexpr int kStagingBytes = kEpiWarps * 4096;
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
-constexpr u32 kTxBytes = 2u * kStageBytes;                                  // both CTAs' loads of one stage
-constexpr int kBN = 256;
-constexpr int kSfaCol = 256, kSfbCol = 272, kSfBufCols = 48, kTmemCols = 512;
-}  // namespace pair
+template <int BN>
+struct PairCfg {
+  // BN = 256: one 256x256 tile per CTA pair, two accumulators that overlap in 48 tensor-memory columns
+  // BN = 192: 256x192 tiles, two disjoint accumulators (the next tile's MMAs never wait for the
+  //           previous tile's epilogue); N need not be a multiple of 192 (loads beyond N read zeros,
+  //           stores are clipped)
+  // BN = 128: 256x128 tiles, two disjoint accumulators, more stages; most operand bytes per FLOP
+  static constexpr int kStages = BN == 256 ? 5 : BN == 192 ? 6 : 7;
+  static constexpr int kSfbBlocks = BN == 128 ? 1 : 2;     // 128-row scale blocks of B fetched per K tile
+  static constexpr int kABytes = 16384;                    // 128 rows x 128 B
+  static constexpr int kBBytes = (BN / 2) * 128;           // this CTA's half of the B tile
+  static constexpr int kSFABytes = 2048;
+  static constexpr int kSFBBytes = kSfbBlocks * 2048;      // all B scales, in both CTAs
+  static constexpr int kStageBytes = kABytes + kBBytes + kSFABytes + kSFBBytes;   // multiple of 1024
+  static constexpr int kStageRowBytes = BN == 256 ? 128 : 64;                     // staging row of one lane
+  static constexpr int kStagingBytes = kEpiWarps * 32 * kStageRowBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+  static constexpr u32 kTxBytes = 2u * kStageBytes;        // both CTAs' loads of one stage
+  // Tensor-memory columns.  BN = 256: accumulators at columns 0 and 208 overlap in columns 208..255,
+  // which the epilogue drains first and hands back at once; scales behind them at 464 (A: 16 columns,
+  // B: 32).  BN = 192 / 128: accumulators at 0 and BN, scales at 2*BN.
+  static constexpr int kAccOff1 = BN == 256 ? 208 : BN;
+  static constexpr int kSfaCol = BN == 256 ? 464 : 2 * BN;
+  static constexpr int kSfbCol = kSfaCol + 16;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEpiCols = BN / 2;                  // columns each epilogue warp drains
+};
+
 
 __device__ __forceinline__ u32 cluster_ctarank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ u32 map_to_cta(u32 saddr, u32 rank) {
@@ -503,9 +528,9 @@ __device__ __forceinline__ void tc2_mma_nvf4(u32 d_tmem, u64 adesc, u64 bdesc, u
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
-// instruction descriptor of the pair MMA: M = 256 (16 at bit 24), N = 256
-__host__ __device__ constexpr u32 make_idesc_pair() {
-  return (1u << 7) | (1u << 10) | ((u32)(256 >> 3) << 17) | ((u32)(256 >> 4) << 24);
+// instruction descriptor of the pair MMA: M = 256 (16 at bit 24), N = n
+__host__ __device__ constexpr u32 make_idesc_pair(int n) {
+  return (1u << 7) | (1u << 10) | ((u32)(n >> 3) << 17) | ((u32)(256 >> 4) << 24);
 }
 
 struct PairParams {
@@ -521,44 +546,131 @@ struct PairParams {
   int atomic;
   int splitk;
   int ktiles_per_split;
+#ifdef NVFP4_GEMM_DEBUG
+  int dbg;
+  unsigned long long* prof;   // [16] clock64 sums of cluster 0 / leader: see NVFP4_PROF uses
+#endif
 };
 
+// Convert, scale and store the NCOLS accumulator values each lane holds for its row (32 rows per warp,
+// starting at `cbase`), through this warp's staging area so that global stores are coalesced: a round
+// writes one ROWB-byte row per lane into shared memory (16-byte units XOR-swizzled against bank
+// conflicts), then the warp reads it back with consecutive lanes along a row and stores row segments.
+template <int NCOLS, int ROWB>
+__device__ __forceinline__ void staged_store(const u32 (&r)[NCOLS], float alpha, u32 sw, int lane, void* cbase, long long ldc,
+                                             bool fp32, bool atomic, int valid_cols) {
+  constexpr int U = ROWB / 16;            // 16-byte units per staging row
+  constexpr int RPI = 32 / U;             // rows covered by one read instruction
+  const u32 wswz = ROWB == 128 ? (u32)(lane & 7) : (u32)((lane >> 1) & 3);
+  const u32 wr = sw + (u32)lane * ROWB;
+  const int rrow = lane / U, ru = lane % U;
+  if (fp32) {
+    constexpr int CPR = ROWB / 4;         // columns per round
+    float* cb = static_cast<float*>(cbase);
+#pragma unroll
+    for (int c = 0; c < NCOLS / CPR; c++) {
+      if (c * CPR >= valid_cols) break;               // columns beyond N (multiples of 32): nothing to store
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int i = c * CPR + u * 4;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (((u32)u ^ wswz) << 4)),
+                     "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),
+                     "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");
+      }
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < U; it++) {
+        const int row = it * RPI + rrow;
+        const u32 rswz = ROWB == 128 ? (u32)(row & 7) : (u32)((row >> 1) & 3);
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "r"(sw + (u32)row * ROWB + (((u32)ru ^ rswz) << 4)) : "memory");
+        float* dst = cb + (long long)row * ldc + c * CPR + ru * 4;
+        if (atomic)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+        else
+          *reinterpret_cast<float4*>(dst) = v;
+      }
+      __syncwarp();
+    }
+  } else {
+    constexpr int CPR = ROWB / 2;
+    __nv_bfloat16* cb = static_cast<__nv_bfloat16*>(cbase);
+#pragma unroll
+    for (int c = 0; c < NCOLS / CPR; c++) {
+      if (c * CPR >= valid_cols) break;
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int i = c * CPR + u * 8;
+        uint4 o;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (((u32)u ^ wswz) << 4)), "r"(o.x), "r"(o.y),
+                     "r"(o.z), "r"(o.w) : "memory");
+      }
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < U; it++) {
+        const int row = it * RPI + rrow;
+        const u32 rswz = ROWB == 128 ? (u32)(row & 7) : (u32)((row >> 1) & 3);
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "r"(sw + (u32)row * ROWB + (((u32)ru ^ rswz) << 4)) : "memory");
+        *reinterpret_cast<uint4*>(cb + (long long)row * ldc + c * CPR + ru * 8) = v;
+      }
+      __syncwarp();
+    }
+  }
+}
+
+#ifdef NVFP4_GEMM_DEBUG
+#define NVFP4_PROF_T0() long long _t0 = clock64()
+#define NVFP4_PROF_ADD(slot) { long long _t1 = clock64(); prof_acc[slot] += (unsigned long long)(_t1 - _t0); _t0 = _t1; }
+#else
+#define NVFP4_PROF_T0()
+#define NVFP4_PROF_ADD(slot)
+#endif
+
+template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                       const PairParams p) {
-  using namespace pair;
+  using C = PairCfg<BN>;
+  constexpr int kStages = C::kStages;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* staging = smem + kStages * kStageBytes;
-  unsigned char* bar_mem = staging + kStagingBytes;
+  unsigned char* staging = smem + kStages * C::kStageBytes;
+  unsigned char* bar_mem = staging + C::kStagingBytes;
   u64* full_bar = reinterpret_cast<u64*>(bar_mem);
   u64* empty_bar = full_bar + kStages;
-  u64* acc_full = empty_bar + kStages;
-  u64* acc_empty = acc_full + 1;
-  u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 1);
+  u64* acc_full = empty_bar + kStages;                // [2]
+  u64* acc_empty = acc_full + 2;                      // [2]
+  u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const u32 rank = cluster_ctarank();                 // 0 = leader (issues the MMAs), 1 = peer
-  const int tiles_m = p.M / 256, tiles_n = p.N / kBN;
+  const int tiles_m = p.M / 256, tiles_n = (p.N + BN - 1) / BN;
   const int ktiles = (p.K + kBK - 1) / kBK;
   const int num_work = tiles_m * tiles_n * p.splitk;
   const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
   const u32 smem_base = smem_u32(smem);
   const u32 full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
-  const u32 accf = smem_u32(acc_full), acce = smem_u32(acc_empty);
+  const u32 accf0 = smem_u32(acc_full), acce0 = smem_u32(acc_empty);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(accf, 1);
-    mbar_init(acce, 2 * kEpiWarps);                   // the epilogue warps of both CTAs
+    for (int a = 0; a < 2; a++) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 2 * kEpiWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem2_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem2_alloc(smem_u32(tmem_slot), C::kTmemCols);
     tmem2_relinquish();
   }
   tc_fence_before();
@@ -578,6 +690,10 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int stage = 0; u32 phase = 0;
     u32 st_addr = smem_base;
     bool ok = true;
+#ifdef NVFP4_GEMM_DEBUG
+    unsigned long long prof_acc[4] = {0, 0, 0, 0};
+#endif
+    NVFP4_PROF_T0();
     for (int w = cid; w < num_work && ok; w += ncl) {
       const int mt = w % tiles_m;
       const int rest = w / tiles_m;
@@ -585,174 +701,197 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int z = rest / tiles_n;
       const int kt0 = z * p.ktiles_per_split;
       const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
-      const int ya = mt * 256 + (int)rank * 128, yb = nt * kBN + (int)rank * 128;
-      const int za = mt * 2 + (int)rank, zb = nt * 2;
+      const int ya = mt * 256 + (int)rank * 128, yb = nt * BN + (int)rank * (BN / 2);
+      const int za = mt * 2 + (int)rank, zb = (nt * BN) >> 7;
       for (int kt = kt0; kt < kt1; kt++) {
         if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag))) { ok = false; break; }
+        NVFP4_PROF_ADD(0);        // producer: waiting for a free stage
         if (elect_one()) {
-          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, kTxBytes);
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, C::kTxBytes);
           const u32 bar = leader_full0 + 8 * stage;
           tma2_load_2d(st_addr, &map_a, kt * kBKBytes, ya, bar);
-          tma2_load_2d(st_addr + kABytes, &map_b, kt * kBKBytes, yb, bar);
-          tma2_load_3d(st_addr + kABytes + kBBytes, &map_sfa, 0, kt * 4, za, bar);
-          tma2_load_3d(st_addr + kABytes + kBBytes + kSFABytes, &map_sfb, 0, kt * 4, zb, bar);
+          tma2_load_2d(st_addr + C::kABytes, &map_b, kt * kBKBytes, yb, bar);
+          tma2_load_3d(st_addr + C::kABytes + C::kBBytes, &map_sfa, 0, kt * 4, za, bar);
+          tma2_load_3d(st_addr + C::kABytes + C::kBBytes + C::kSFABytes, &map_sfb, 0, kt * 4, zb, bar);
         }
-        st_addr += kStageBytes;
+        st_addr += C::kStageBytes;
         if (++stage == kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
+        NVFP4_PROF_ADD(1);        // producer: issuing
       }
     }
+#ifdef NVFP4_GEMM_DEBUG
+    if (p.prof && blockIdx.x == 0 && lane == 0) { p.prof[0] = prof_acc[0]; p.prof[1] = prof_acc[1]; }
+#endif
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0) {
-      constexpr u32 idesc = make_idesc_pair();
-      u32 sfa_t = tmem_base + kSfaCol, sfb_t = tmem_base + kSfbCol;
-      u32 sf_flip = kSfBufCols;
-      const u32 empty_peer0 = map_to_cta(empty0, 1), accf_peer = map_to_cta(accf, 1);
+      constexpr u32 idesc = make_idesc_pair(BN);
+      const u32 sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+      const u32 empty_peer0 = map_to_cta(empty0, 1), accf_peer0 = map_to_cta(accf0, 1);
       int stage = 0; u32 phase = 0;
       const u32 a_lo0 = (smem_base >> 4) | (1u << 16);
       u32 a_lo = a_lo0;
-      u32 acc_phase = 0;
+      u32 tile = 0;                                   // tiles done by this cluster
       bool ok = true;
-      for (int w = cid; w < num_work && ok; w += ncl) {
+#ifdef NVFP4_GEMM_DEBUG
+      unsigned long long prof_acc[4] = {0, 0, 0, 0};
+#endif
+      NVFP4_PROF_T0();
+      for (int w = cid; w < num_work && ok; w += ncl, tile++) {
         const int z = w / (tiles_m * tiles_n);
+        const int nt = (w / tiles_m) % tiles_n;
         const int kt0 = z * p.ktiles_per_split;
         const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
-        // both CTAs' epilogues must have drained the accumulator
-        if (!__all_sync(0xffffffffu, mbar_wait(acce, acc_phase ^ 1u, abort_flag))) { ok = false; break; }
+        const u32 acc = tile & 1u;
+        // a 192-wide tile starts 0 or 64 rows into its first 128-row scale block: 0 or 2 columns in
+        const u32 sfb_m = sfb_t + (BN == 192 ? (u32)(((nt * BN) & 127) >> 5) : 0u);
+        // BN = 256: wait until the previous tile's epilogues (both CTAs) have handed back the 48 columns
+        // the two accumulators share.  BN = 128: wait until this accumulator's previous tile (two tiles
+        // ago) has been drained.
+        {
+          const u32 bar = BN == 256 ? acce0 : acce0 + 8 * acc;
+          const u32 par = BN == 256 ? ((tile & 1u) ^ 1u) : (((tile >> 1) & 1u) ^ 1u);
+          if (!__all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag))) { ok = false; break; }
+        }
+        NVFP4_PROF_ADD(0);        // MMA: waiting for the accumulator
         tc_fence_after();
+        const u32 d_tmem = tmem_base + (acc ? C::kAccOff1 : 0);
         u32 accum = 0u;
         for (int kt = kt0; kt < kt1; kt++) {
           if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag))) { ok = false; break; }
-          const u32 b_lo = a_lo + (kABytes >> 4);
-          const u32 sfa_lo = (a_lo & 0xFFFFu) + ((kABytes + kBBytes) >> 4);
-          const u32 sfb_lo = sfa_lo + (kSFABytes >> 4);
+          NVFP4_PROF_ADD(1);      // MMA: waiting for operands
+          const u32 b_lo = a_lo + (C::kABytes >> 4);
+          const u32 sfa_lo = (a_lo & 0xFFFFu) + ((C::kABytes + C::kBBytes) >> 4);
+          const u32 sfb_lo = sfa_lo + (C::kSFABytes >> 4);
           const int krem = p.K - kt * kBK;
           const int kchunks = krem >= kBK ? 4 : (krem >> 6);
           if (elect_one()) {
+#ifdef NVFP4_GEMM_DEBUG
+            if ((p.dbg & 4) && accum) { tc2_commit(empty0 + 8 * stage); tc2_commit(empty_peer0 + 8 * stage); } else
+#endif
+            {
             if (kchunks == 4) {
 #pragma unroll
               for (int j = 0; j < 4; j++) {
                 tc2_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
-                tc2_cp_sf(sfb_t + 8 * j, pack64(sfb_lo + 32 * j, kDescHiSF));
-                tc2_cp_sf(sfb_t + 8 * j + 4, pack64(sfb_lo + 128 + 32 * j, kDescHiSF));
+#pragma unroll
+                for (int h = 0; h < C::kSfbBlocks; h++)
+                  tc2_cp_sf(sfb_t + (4 * C::kSfbBlocks) * j + 4 * h, pack64(sfb_lo + 128 * h + 32 * j, kDescHiSF));
               }
-              tc2_mma_nvf4(tmem_base, pack64(a_lo, kDescHiAB), pack64(b_lo, kDescHiAB), idesc, sfa_t, sfb_t, accum);
+              tc2_mma_nvf4(d_tmem, pack64(a_lo, kDescHiAB), pack64(b_lo, kDescHiAB), idesc, sfa_t, sfb_m, accum);
 #pragma unroll
               for (int j = 1; j < 4; j++)
-                tc2_mma_nvf4(tmem_base, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
-                             sfb_t + 8 * j, 1u);
+                tc2_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                             sfb_m + (4 * C::kSfbBlocks) * j, 1u);
             } else {
               for (int j = 0; j < kchunks; j++) {
                 tc2_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
-                tc2_cp_sf(sfb_t + 8 * j, pack64(sfb_lo + 32 * j, kDescHiSF));
-                tc2_cp_sf(sfb_t + 8 * j + 4, pack64(sfb_lo + 128 + 32 * j, kDescHiSF));
+#pragma unroll
+                for (int h = 0; h < C::kSfbBlocks; h++)
+                  tc2_cp_sf(sfb_t + (4 * C::kSfbBlocks) * j + 4 * h, pack64(sfb_lo + 128 * h + 32 * j, kDescHiSF));
               }
               for (int j = 0; j < kchunks; j++)
-                tc2_mma_nvf4(tmem_base, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
-                             sfb_t + 8 * j, (j > 0) ? 1u : accum);
+                tc2_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
+                             sfb_m + (4 * C::kSfbBlocks) * j, (j > 0) ? 1u : accum);
             }
             // free the stage in both CTAs once these MMAs have read it
             tc2_commit(empty0 + 8 * stage);
             tc2_commit(empty_peer0 + 8 * stage);
+            }
           }
           accum = 1u;
-          sfa_t += sf_flip; sfb_t += sf_flip; sf_flip = 0u - sf_flip;
-          a_lo += kStageBytes >> 4;
+          a_lo += C::kStageBytes >> 4;
           if (++stage == kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
+          NVFP4_PROF_ADD(2);      // MMA: issuing
         }
         if (!ok) break;
-        if (elect_one()) { tc2_commit(accf); tc2_commit(accf_peer); }     // accumulators complete in both CTAs
-        acc_phase ^= 1u;
+        // accumulator complete: tell the epilogues of both CTAs
+        const u32 fb = BN == 256 ? 0u : 8u * acc;
+        if (elect_one()) { tc2_commit(accf0 + fb); tc2_commit(accf_peer0 + fb); }
       }
+#ifdef NVFP4_GEMM_DEBUG
+      if (p.prof && blockIdx.x == 0 && lane == 0) { p.prof[2] = prof_acc[0]; p.prof[3] = prof_acc[1]; p.prof[4] = prof_acc[2]; }
+#endif
       if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    constexpr int NC = C::kEpiCols;
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
-    const u32 sw = smem_u32(staging) + (u32)(warp - 2) * 4096u;       // this warp's staging area
-    const u32 acce_leader = map_to_cta(acce, 0);
-    u32 acc_phase = 0;
+    const u32 sw = smem_u32(staging) + (u32)(warp - 2) * (32u * C::kStageRowBytes);   // this warp's staging area
+    const u32 acce_leader0 = map_to_cta(acce0, 0);
+    u32 tile = 0;
     bool ok = true;
-    for (int w = cid; w < num_work && ok; w += ncl) {
+#ifdef NVFP4_GEMM_DEBUG
+    unsigned long long prof_acc[4] = {0, 0, 0, 0};
+#endif
+    NVFP4_PROF_T0();
+    for (int w = cid; w < num_work && ok; w += ncl, tile++) {
       const int mt = w % tiles_m;
       const int nt = (w / tiles_m) % tiles_n;
-      if (!__all_sync(0xffffffffu, mbar_wait(accf, acc_phase, abort_flag))) { ok = false; break; }
-      acc_phase ^= 1u;
+      const u32 acc = tile & 1u;
+      {
+        const u32 bar = BN == 256 ? accf0 : accf0 + 8 * acc;
+        const u32 par = BN == 256 ? (tile & 1u) : ((tile >> 1) & 1u);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag))) { ok = false; break; }
+      }
+      NVFP4_PROF_ADD(0);          // epilogue: waiting for a finished accumulator
       tc_fence_after();
-      u32 r[128];
-      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (u32)(half * 128);
-#pragma unroll
-      for (int c = 0; c < 4; c++) tc_ld32(t_row + c * 32, *reinterpret_cast<u32(*)[32]>(&r[c * 32]));
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acce_leader);
+      u32 r[NC];
+      const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (acc ? (u32)C::kAccOff1 : 0u) + (u32)(half * NC);
+      const u32 rel_bar = BN == 256 ? acce_leader0 : acce_leader0 + 8 * acc;
+#define NVFP4_LD32(I) tc_ld32(t_row + (I), *reinterpret_cast<u32(*)[32]>(&r[(I)]))
+#define NVFP4_LD16(I) tc_ld16(t_row + (I), *reinterpret_cast<u32(*)[16]>(&r[(I)]))
+#define NVFP4_RELEASE_ACC() { tc_wait_ld(); tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive_cluster(rel_bar); }
+      if constexpr (BN == 256) {
+        if (acc && half == 0) {
+          // this warp's first 48 columns are the shared ones: read them, hand them back, read the rest
+          NVFP4_LD32(0); NVFP4_LD16(32);
+          NVFP4_RELEASE_ACC();
+          NVFP4_LD16(48); NVFP4_LD32(64); NVFP4_LD32(96);
+          tc_wait_ld();
+        } else if (!acc && half == 1) {
+          // this warp's last 48 columns are the shared ones
+          NVFP4_LD16(80); NVFP4_LD32(96);
+          NVFP4_RELEASE_ACC();
+          NVFP4_LD32(0); NVFP4_LD32(32); NVFP4_LD16(64);
+          tc_wait_ld();
+        } else {
+          // none of this warp's columns is shared with the other accumulator
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(rel_bar);
+          NVFP4_LD32(0); NVFP4_LD32(32); NVFP4_LD32(64); NVFP4_LD32(96);
+          tc_wait_ld();
+        }
+      } else {
+        NVFP4_LD32(0); NVFP4_LD32(32);
+        if constexpr (NC == 96) NVFP4_LD32(64);
+        NVFP4_RELEASE_ACC();
+      }
+#undef NVFP4_LD32
+#undef NVFP4_LD16
+#undef NVFP4_RELEASE_ACC
+      NVFP4_PROF_ADD(1);          // epilogue: draining tensor memory
 
+#ifdef NVFP4_GEMM_DEBUG
+      if (p.dbg & 1) { if (r[0] == 0x12345678u && r[NC - 1] == 0x9abcdef0u) *static_cast<u32*>(p.c) = r[5]; continue; }
+#endif
       float alpha = 1.f;
       if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
       const long long row0 = (long long)mt * 256 + rank * 128 + quad * 32;      // first row of this warp
-      const long long col0 = (long long)nt * kBN + half * 128;
-      const u32 wr = sw + (u32)lane * 128u;                     // staging row of this lane (write phase)
-      const int rr = lane >> 3, ru = lane & 7;                  // read phase: row within a group of 4, 16-byte unit
-      if (p.c_fp32) {
-        float* cbase = static_cast<float*>(p.c) + row0 * p.ldc + col0;
-#define NVFP4_PAIR_F32_ROUND(C)                                                                                           \
-        {                                                                                                                  \
-          _Pragma("unroll") for (int u = 0; u < 8; u++) {                                                                  \
-            const int i = (C) * 32 + u * 4;                                                                                \
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (u32)((u ^ (lane & 7)) << 4)),            \
-                         "f"(__uint_as_float(r[i]) * alpha), "f"(__uint_as_float(r[i + 1]) * alpha),                      \
-                         "f"(__uint_as_float(r[i + 2]) * alpha), "f"(__uint_as_float(r[i + 3]) * alpha) : "memory");      \
-          }                                                                                                                \
-          __syncwarp();                                                                                                    \
-          _Pragma("unroll") for (int it = 0; it < 8; it++) {                                                               \
-            const int row = it * 4 + rr;                                                                                   \
-            float4 v;                                                                                                      \
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)           \
-                         : "r"(sw + (u32)row * 128u + (u32)((ru ^ (row & 7)) << 4)) : "memory");                         \
-            float* dst = cbase + (long long)row * p.ldc + (C) * 32 + ru * 4;                                               \
-            if (p.atomic)                                                                                                  \
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),      \
-                           "f"(v.w) : "memory");                                                                          \
-            else                                                                                                           \
-              *reinterpret_cast<float4*>(dst) = v;                                                                         \
-          }                                                                                                                \
-          __syncwarp();                                                                                                    \
-        }
-        NVFP4_PAIR_F32_ROUND(0) NVFP4_PAIR_F32_ROUND(1) NVFP4_PAIR_F32_ROUND(2) NVFP4_PAIR_F32_ROUND(3)
-#undef NVFP4_PAIR_F32_ROUND
-      } else {
-        __nv_bfloat16* cbase = static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0;
-#define NVFP4_PAIR_BF16_ROUND(C)                                                                                          \
-        {                                                                                                                  \
-          _Pragma("unroll") for (int u = 0; u < 8; u++) {                                                                  \
-            const int i = (C) * 64 + u * 8;                                                                                \
-            uint4 o;                                                                                                       \
-            __nv_bfloat162 h;                                                                                              \
-            h = __floats2bfloat162_rn(__uint_as_float(r[i]) * alpha, __uint_as_float(r[i + 1]) * alpha); o.x = *reinterpret_cast<u32*>(&h);     \
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * alpha, __uint_as_float(r[i + 3]) * alpha); o.y = *reinterpret_cast<u32*>(&h); \
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * alpha, __uint_as_float(r[i + 5]) * alpha); o.z = *reinterpret_cast<u32*>(&h); \
-            h = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * alpha, __uint_as_float(r[i + 7]) * alpha); o.w = *reinterpret_cast<u32*>(&h); \
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(wr + (u32)((u ^ (lane & 7)) << 4)), "r"(o.x),    \
-                         "r"(o.y), "r"(o.z), "r"(o.w) : "memory");                                                        \
-          }                                                                                                                \
-          __syncwarp();                                                                                                    \
-          _Pragma("unroll") for (int it = 0; it < 8; it++) {                                                               \
-            const int row = it * 4 + rr;                                                                                   \
-            uint4 v;                                                                                                       \
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)           \
-                         : "r"(sw + (u32)row * 128u + (u32)((ru ^ (row & 7)) << 4)) : "memory");                         \
-            *reinterpret_cast<uint4*>(cbase + (long long)row * p.ldc + (C) * 64 + ru * 8) = v;                             \
-          }                                                                                                                \
-          __syncwarp();                                                                                                    \
-        }
-        NVFP4_PAIR_BF16_ROUND(0) NVFP4_PAIR_BF16_ROUND(1)
-#undef NVFP4_PAIR_BF16_ROUND
-      }
+      const long long col0 = (long long)nt * BN + half * NC;
+      void* cbase = p.c_fp32 ? static_cast<void*>(static_cast<float*>(p.c) + row0 * p.ldc + col0)
+                             : static_cast<void*>(static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0);
+      staged_store<NC, C::kStageRowBytes>(r, alpha, sw, lane, cbase, p.ldc, p.c_fp32 != 0, p.atomic != 0,
+                                          (int)min((long long)NC, (long long)p.N - col0));
+      NVFP4_PROF_ADD(2);          // epilogue: converting and storing
     }
+#ifdef NVFP4_GEMM_DEBUG
+    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) { p.prof[5] = prof_acc[0]; p.prof[6] = prof_acc[1]; p.prof[7] = prof_acc[2]; p.prof[8] = tile; }
+#endif
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
   }
 
@@ -766,7 +905,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   cluster_sync_all();                                 // neither CTA frees tensor memory or exits while the other still works
   if (warp == 1) {
     tc_fence_after();
-    tmem2_dealloc(tmem_base, kTmemCols);
+    tmem2_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -802,8 +941,11 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 
 #ifdef NVFP4_GEMM_DEBUG
 static int g_debug = 0;
+static unsigned long long* g_prof = nullptr;
+extern "C" int nvfp4_gemm_prof(unsigned long long* p) { g_prof = p; return 0; }
 extern "C" int nvfp4_gemm_debug(int flags) { g_debug = flags; return 0; }
 #endif
+static int g_pair_bn = 0;    // 0 = heuristic, 128 / 192 / 256 = forced tile width of the CTA-pair kernel
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
 
 // Swizzled scale bytes of an [R, K/16] operand seen as a 3-D tensor of 32-bit words:
@@ -820,7 +962,7 @@ static bool make_sf_map(CUtensorMap* map, const void* base, long long rows, long
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-struct DevInfo { int sms; bool attr128, attr256, attr_pair; };
+struct DevInfo { int sms; bool attr128, attr256, attr_pair, attr_pair128, attr_pair192; };
 static DevInfo* dev_info() {
   static DevInfo info[64];
   static bool init[64] = {false};
@@ -829,7 +971,7 @@ static DevInfo* dev_info() {
   if (!init[dev]) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return nullptr;
-    info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = info[dev].attr_pair = false;
+    info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = info[dev].attr_pair = info[dev].attr_pair128 = info[dev].attr_pair192 = false;
     init[dev] = true;
   }
   return &info[dev];
@@ -894,13 +1036,17 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   if (g_force_bn == 256 && N % 256 == 0) wide = true;
   const int bn = wide ? 256 : 128;
 
-  // CTA-pair kernel (256x256 tiles over an SM pair): the fast path whenever the shape allows it
-  bool use_pair = (M % 256 == 0) && (N % 256 == 0) && g_force_bn != 128 && g_force_bn != 256;
-  if (g_force_bn == 0 && (long long)(M / 256) * (N / 256) * splitk < di->sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
+  // CTA-pair kernels (an SM pair per 256-row tile): the fast path whenever M allows it
+  bool use_pair = (M % 256 == 0) && g_force_bn != 128 && g_force_bn != 256;
+  if (g_force_bn == 0 && (long long)(M / 256) * ((N + 255) / 256) * splitk < di->sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
   if (use_pair) {
+    // tile width: 256 moves the fewest operand bytes per FLOP but consecutive tiles wait for each other's
+    // epilogue hand-off; 192 has two independent accumulators and handles any N; 128 as well, more bytes
+    int pbn = (N % 256 == 0 && (long long)per * kBK >= 8192) ? 256 : 192;
+    if (g_pair_bn == 128 || g_pair_bn == 192 || (g_pair_bn == 256 && N % 256 == 0)) pbn = g_pair_bn;
     CUtensorMap ma, mb, msa, msb;
-    if (!make_map(&ma, a, M, K / 2, lda, 128) || !make_map(&mb, b, N, K / 2, ldb, 128) ||
-        !make_sf_map(&msa, sa, M, K, 1) || !make_sf_map(&msb, sb, N, K, 2))
+    if (!make_map(&ma, a, M, K / 2, lda, 128) || !make_sf_map(&msa, sa, M, K, 1) ||
+        !make_map(&mb, b, N, K / 2, ldb, pbn / 2) || !make_sf_map(&msb, sb, N, K, pbn == 128 ? 1 : 2))
       return NVFP4_ERR_CUDA;
     PairParams pp;
     pp.c = c; pp.pa = pa; pp.pb = pb; pp.status = status; pp.ldc = ldc;
@@ -911,14 +1057,27 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.atomic = (accumulate || splitk > 1) ? 1 : 0;
     pp.splitk = splitk;
     pp.ktiles_per_split = per;
-    if (!di->attr_pair) {
-      if (cudaFuncSetAttribute(gemm_nvf4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes) != cudaSuccess)
-        return NVFP4_ERR_CUDA;
-      di->attr_pair = true;
-    }
-    const long long work = (long long)(M / 256) * (N / 256) * splitk;
+#ifdef NVFP4_GEMM_DEBUG
+    pp.dbg = g_debug;
+    pp.prof = g_prof;
+#endif
+    const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
     const long long clusters = work < di->sms / 2 ? work : di->sms / 2;
-    gemm_nvf4_pair_kernel<<<(unsigned)(2 * clusters), kThreads, pair::kSmemBytes, st>>>(ma, mb, msa, msb, pp);
+    const unsigned grid = (unsigned)(2 * clusters);
+#define NVFP4_LAUNCH_PAIR(BN_, FLAG)                                                                                      \
+    {                                                                                                                      \
+      if (!di->FLAG) {                                                                                                     \
+        if (cudaFuncSetAttribute(gemm_nvf4_pair_kernel<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
+                                 PairCfg<BN_>::kSmemBytes) != cudaSuccess)                                                 \
+          return NVFP4_ERR_CUDA;                                                                                           \
+        di->FLAG = true;                                                                                                   \
+      }                                                                                                                    \
+      gemm_nvf4_pair_kernel<BN_><<<grid, kThreads, PairCfg<BN_>::kSmemBytes, st>>>(ma, mb, msa, msb, pp);                  \
+    }
+    if (pbn == 256) NVFP4_LAUNCH_PAIR(256, attr_pair)
+    else if (pbn == 192) NVFP4_LAUNCH_PAIR(192, attr_pair192)
+    else NVFP4_LAUNCH_PAIR(128, attr_pair128)
+#undef NVFP4_LAUNCH_PAIR
     NVFP4_LAUNCH_CHECK();
     return NVFP4_OK;
   }
@@ -968,8 +1127,9 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
 }
 
 extern "C" int nvfp4_gemm_force_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256 && bn != 512) return NVFP4_ERR_ENUM;
-  g_force_bn = bn;
+  if (bn != 0 && bn != 128 && bn != 256 && bn != 512 && bn != 384 && bn != 448) return NVFP4_ERR_ENUM;
+  g_pair_bn = bn == 512 ? 256 : bn == 448 ? 192 : bn == 384 ? 128 : 0;
+  g_force_bn = bn >= 384 ? 512 : bn;
   return NVFP4_OK;
 }
 

@@ -54,7 +54,7 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_gemm_linear(p, p, 64, 8, p, p, 64, 8, p, 1, 128, 128, 128, 128, 0, None, None, 1.0, 1.0, 0, 1,
                                  None, 0, None, None) == -6
     assert lib.nvfp4_gemm_linear_workspace_bytes(128, 256, 1024) == (128 + 256) * 64
-    assert lib.nvfp4_gemm_force_tile_n(64) == -4 and lib.nvfp4_gemm_force_tile_n(0) == 0
+    assert lib.nvfp4_gemm_force_tile_n(64) == -4 and lib.nvfp4_gemm_force_tile_n(448) == 0 and lib.nvfp4_gemm_force_tile_n(0) == 0
 
 
 def test_python_wrappers_refuse_cpu_tensors():

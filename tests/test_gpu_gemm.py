@@ -44,11 +44,11 @@ def check_close(c, y, bf16):
 
 
 SHAPES = [(128, 128, 64), (128, 128, 256), (128, 256, 320), (256, 384, 1024), (512, 384, 1024),
-          (384, 512, 2048), (128, 768, 4096), (256, 256, 64), (256, 512, 832), (512, 768, 2048), (1024, 256, 4096)]
+          (384, 512, 2048), (128, 768, 4096), (256, 256, 64), (256, 512, 832), (512, 768, 2048), (1024, 256, 4096), (256, 640, 576), (512, 1152, 1024)]
 
 
-# tile 512 = the CTA-pair kernel (used when M and N are multiples of 256, ignored otherwise)
-@pytest.mark.parametrize("tile", [0, 128, 256, 512])
+# tiles 512 / 448 / 384 = the CTA-pair kernel with 256- / 192- / 128-wide tiles (needs M a multiple of 256)
+@pytest.mark.parametrize("tile", [0, 128, 256, 512, 448, 384])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_mm_vs_dequant_matmul(mods, M, N, K, tile):
     nvq, _, L = mods
@@ -76,7 +76,7 @@ def test_mm_identity_scales_exact(mods):
         return nvq.Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), torch.ones(1, device="cuda")), codes
     (qa, ca), (qb, cb) = mk(M), mk(N)
     y = O.E2M1_TABLE[ca].astype(np.float64) @ O.E2M1_TABLE[cb].astype(np.float64).T
-    for tile in (128, 256, 512):
+    for tile in (128, 256, 512, 448, 384):
         L.load().nvfp4_gemm_force_tile_n(tile)
         c = nvq.mm(qa, qb, out_dtype=torch.float32).cpu().numpy()
         assert np.array_equal(c.astype(np.float64), y)
@@ -97,14 +97,14 @@ def test_mm_scale_layout_per_row_and_kblock(mods):
         return nvq.Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), torch.ones(1, device="cuda")), sc
     (qa, sa), (qb, sb) = mk(M), mk(N)
     y = 16.0 * (O.e4m3_decode(sa).astype(np.float64) @ O.e4m3_decode(sb).astype(np.float64).T)
-    for tile in (128, 256, 512):
+    for tile in (128, 256, 512, 448, 384):
         L.load().nvfp4_gemm_force_tile_n(tile)
         check_close(nvq.mm(qa, qb, out_dtype=torch.float32), y, bf16=False)
         check_close(nvq.mm(qa, qb), y, bf16=True)
     L.check_status()
 
 
-@pytest.mark.parametrize("tile", [0, 512])
+@pytest.mark.parametrize("tile", [0, 512, 448, 384])
 def test_mm_accumulate_into_out(mods, tile):
     nvq, _, L = mods
     L.load().nvfp4_gemm_force_tile_n(tile)

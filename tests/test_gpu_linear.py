@@ -49,3 +49,28 @@ def test_linear_module_bf16_switch():
     LinCtx.fp4 = True
     assert y4.shape == (2, 64, 384)
     assert ((y4.float() - y16.float()).norm() / y16.float().norm()).item() < 0.2
+
+
+def test_fp4torch_custom_op_linear():
+    """small-model/fp4torch.py flavour: nvfp4::linear with autograd, weights quantized once by
+    FP4Weight; forward equals the dequant matmul, gradients track the exact ones within FP4 noise."""
+    from nvfp4_training_b200 import _lib, fp4ops, fp4torch
+    torch.manual_seed(0)
+    T, K, N = 256, 256, 384
+    x = torch.randn(2, T // 2, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).requires_grad_(True)
+    fw = fp4torch.FP4Weight(w)
+    y = torch.ops.nvfp4.linear(x, w, fw.wd, fw.ws, fw.wtd, fw.wts, fw.amax)
+    assert y.shape == (2, T // 2, N) and y.dtype == torch.bfloat16
+    qx = fp4ops.quant_rows(x.detach().reshape(-1, K))
+    ref = fp4ops.dequant(qx) @ fp4ops.dequant(fp4ops.Q(fw.wd, fw.ws, fw.amax)).t()
+    assert ((y.float().reshape(-1, N) - ref).norm() / ref.norm()).item() <= 4e-3
+    g = torch.randn_like(y) * 1e-3
+    y.backward(g)
+    ex_dx = g.float().reshape(-1, N) @ w.detach()
+    ex_dw = g.float().reshape(-1, N).t() @ x.detach().float().reshape(-1, K)
+    assert w.grad.dtype == torch.float32 and w.grad.shape == (N, K)
+    assert ((x.grad.float().reshape(-1, K) - ex_dx).norm() / ex_dx.norm()).item() < 0.2
+    assert ((w.grad - ex_dw).norm() / ex_dw.norm()).item() < 0.25
+    fw.refresh()
+    _lib.check_status()
