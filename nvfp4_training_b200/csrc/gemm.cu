@@ -491,8 +491,11 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a (possibly remote) barrier that hands tensor memory back to the MMA warp.  Relaxed on
+// purpose: the hand-off is ordered by tcgen05.fence::before_thread_sync; a releasing arrive would
+// also wait for this thread's earlier global stores (the previous tile's output) to become visible.
 __device__ __forceinline__ void mbar_arrive_cluster(u32 cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tma2_load_2d(u32 dst, const CUtensorMap* map, int x, int y, u32 bar) {
   asm volatile(
