@@ -345,8 +345,9 @@ def run_ours(args):
     if rank == 0:
         del stack
         torch.cuda.empty_cache()
-        roof, detail = isolated_kernels(cfg, mb, peaks)
-        roof["peak_source"] = peak_src
+        if not args.skip_isolated:
+            roof, detail = isolated_kernels(cfg, mb, peaks)
+            roof["peak_source"] = peak_src
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             cpu_reference_sample(64, threads)
@@ -385,10 +386,11 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--microbatch", type=int, default=8192)
+    ap.add_argument("--microbatch", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (not a valid bench number)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--skip-isolated", action="store_true", help="skip the isolated-kernel leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
