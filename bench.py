@@ -278,13 +278,15 @@ def run_ours(args):
     _lib.load()
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_MAX_CTAS", str(max(4, args.comm_sms)))     # NCCL stays inside the SMs left free for it
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks, peak_src = load_peaks()
 
     cfg = StackConfig(layers=args.layers) if args.layers else StackConfig()
     plan = shard_plan(world, rank, GLOBAL_TOKENS, args.microbatch)
     mb, n_micro = plan["microbatch"], plan["n_micro"]
-    stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=rank, use_graphs=not args.no_graphs)
+    stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=rank, use_graphs=not args.no_graphs,
+                        comm_sms=args.comm_sms if world > 1 else 0)
     if not args.no_graphs:
         stack.capture()
     do_ar = world > 1
@@ -318,10 +320,9 @@ def run_ours(args):
 
     def e2e_step():
         stack.refresh_weights()
-        stack.zero_grads()
         for m in range(n_micro):
             stack.x_pool["qkv"].copy_(host_x, non_blocking=True)
-            stack.microbatch(last=(m == n_micro - 1), do_allreduce=do_ar)
+            stack.microbatch(last=(m == n_micro - 1), do_allreduce=do_ar, first=(m == 0))
         if do_ar:
             torch.cuda.current_stream().wait_stream(stack.comm_stream)
         host_out.copy_(last.gw.view(-1)[:1024], non_blocking=True)
@@ -389,6 +390,7 @@ def main():
     ap.add_argument("--microbatch", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (not a valid bench number)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs left free for NCCL during backward when N > 1")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--skip-isolated", action="store_true", help="skip the isolated-kernel leg (for profiler runs)")
     args = ap.parse_args()

@@ -156,6 +156,14 @@ int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, cons
 int nvfp4_gemm_force_tile_n(int bn);
 
 /*
+ * Cap the number of SMs the persistent GEMM grids occupy (0 = all).  Meant for data-parallel runs:
+ * leaving a few SMs free lets the NCCL all-reduce kernels of the weight gradients run beside the
+ * GEMMs instead of delaying their last CTAs.  Process-wide; takes effect for later calls (a captured
+ * CUDA graph keeps the grid it was captured with).  No reference counterpart (single GPU).
+ */
+int nvfp4_gemm_set_sm_budget(int sms);
+
+/*
  * Same product for operands whose scales are in the LINEAR layout (row strides ldsa / ldsb bytes):
  * the scales are first rewritten into the swizzled layout inside `workspace`, then nvfp4_gemm runs.
  * This is the `fp4ops.gemm` contract (llm-1b/fp4ops.py:64-80: strided d and s views allowed).

@@ -32,6 +32,7 @@ SIGNATURES = {
     "nvfp4_swizzle_scales": (_i, [_vp, _ll, _i, _i, _vp, _vp]),
     "nvfp4_gemm": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _i, _vp, _vp]),
     "nvfp4_gemm_force_tile_n": (_i, [_i]),
+    "nvfp4_gemm_set_sm_budget": (_i, [_i]),
     "nvfp4_gemm_linear_workspace_bytes": (_sz, [_i, _i, _i]),
     "nvfp4_gemm_linear": (_i, [_vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f,
                                _i, _i, _vp, _sz, _vp, _vp]),

@@ -948,6 +948,7 @@ static unsigned long long* g_prof = nullptr;
 extern "C" int nvfp4_gemm_prof(unsigned long long* p) { g_prof = p; return 0; }
 extern "C" int nvfp4_gemm_debug(int flags) { g_debug = flags; return 0; }
 #endif
+static int g_sm_budget = 0;  // 0 = all SMs; otherwise the persistent GEMM grids use at most this many (even) SMs
 static int g_pair_bn = 0;    // 0 = heuristic, 128 / 192 / 256 = forced tile width of the CTA-pair kernel
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
 
@@ -1026,6 +1027,8 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   }
   DevInfo* di = dev_info();
   if (!di) return NVFP4_ERR_CUDA;
+  int sms = di->sms;
+  if (g_sm_budget > 0 && g_sm_budget < sms) sms = g_sm_budget & ~1;
 
   const int ktiles = (K + kBK - 1) / kBK;
   if (splitk > ktiles) splitk = ktiles;
@@ -1034,14 +1037,14 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
 
   // 256-wide tiles move fewer operand bytes per FLOP and need fewer issue slots; fall back to 128
   // when N demands it or when wide tiles would leave SMs without work
-  bool wide = (N % 256 == 0) && ((long long)(M / kBM) * (N / 256) * splitk >= di->sms || (long long)(M / kBM) * (N / 128) * splitk <= di->sms);
+  bool wide = (N % 256 == 0) && ((long long)(M / kBM) * (N / 256) * splitk >= sms || (long long)(M / kBM) * (N / 128) * splitk <= sms);
   if (g_force_bn == 128) wide = false;
   if (g_force_bn == 256 && N % 256 == 0) wide = true;
   const int bn = wide ? 256 : 128;
 
   // CTA-pair kernels (an SM pair per 256-row tile): the fast path whenever M allows it
   bool use_pair = (M % 256 == 0) && g_force_bn != 128 && g_force_bn != 256;
-  if (g_force_bn == 0 && (long long)(M / 256) * ((N + 255) / 256) * splitk < di->sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
+  if (g_force_bn == 0 && (long long)(M / 256) * ((N + 255) / 256) * splitk < sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
   if (use_pair) {
     // tile width: 256 moves the fewest operand bytes per FLOP but consecutive tiles wait for each other's
     // epilogue hand-off; 192 has two independent accumulators and handles any N; 128 as well, more bytes
@@ -1049,7 +1052,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     if (N % 256 == 0) {
       // measured per-tile cost (us) of a CTA pair: 256-wide 2.98 + 0.346 per K tile, 192-wide 1.81 + 0.313;
       // what decides is mostly how evenly the tile count divides over the SM pairs
-      const long long ncl = di->sms / 2;
+      const long long ncl = sms / 2;
       const long long r256 = ((long long)(M / 256) * (N / 256) * splitk + ncl - 1) / ncl;
       const long long r192 = ((long long)(M / 256) * ((N + 191) / 192) * splitk + ncl - 1) / ncl;
       if (r256 * (2.98 + 0.346 * per) <= r192 * (1.81 + 0.313 * per)) pbn = 256;
@@ -1072,7 +1075,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.prof = g_prof;
 #endif
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
-    const long long clusters = work < di->sms / 2 ? work : di->sms / 2;
+    const long long clusters = work < sms / 2 ? work : sms / 2;
     const unsigned grid = (unsigned)(2 * clusters);
 #define NVFP4_LAUNCH_PAIR(BN_, FLAG)                                                                                      \
     {                                                                                                                      \
@@ -1109,8 +1112,8 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
 #ifdef NVFP4_GEMM_DEBUG
   p.dbg = g_debug;
 #endif
-  if (wide) return launch_gemm<256>(ma, mb, p, di->sms, di->attr256, st);
-  return launch_gemm<128>(ma, mb, p, di->sms, di->attr128, st);
+  if (wide) return launch_gemm<256>(ma, mb, p, sms, di->attr256, st);
+  return launch_gemm<128>(ma, mb, p, sms, di->attr128, st);
 }
 
 extern "C" size_t nvfp4_gemm_linear_workspace_bytes(int M, int N, int K) {
@@ -1134,6 +1137,12 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
   if (rc != NVFP4_OK) return rc;
   return nvfp4_gemm(a, wsa, lda, b, wsb, ldb, c, c_dtype, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, accumulate, splitk,
                     status, stream);
+}
+
+extern "C" int nvfp4_gemm_set_sm_budget(int sms) {
+  if (sms < 0) return NVFP4_ERR_SHAPE;
+  g_sm_budget = sms;
+  return NVFP4_OK;
 }
 
 extern "C" int nvfp4_gemm_force_tile_n(int bn) {

@@ -52,12 +52,12 @@ def linear_fwd(x, qw):
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None):
+               sr_mode=None, overwrite=False):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
     returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
-    rounding (default: the module default of `nvq`)."""
+    rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding."""
     gy = gy.contiguous()
     ag = nvq.amax(gy)
     # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
@@ -66,7 +66,7 @@ def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch
     qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag, sr_mode=sr_mode)
     qxt = nvq.quant_cols_rht(x, signs, am=am_x)
     if gw_out is not None:
-        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=True)
+        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite)
     else:
         gw = nvq.mm(qgt, qxt, out_dtype=wgrad_dtype)
     return gx, gw

@@ -87,7 +87,8 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0):
+        self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
         self.sr_mode = sr_mode       # gradients: hardware cvt.rs stochastic rounding, counter-based random words
         self.use_graphs = use_graphs
@@ -157,11 +158,13 @@ class LinearStack:
             y, p.am_x = linear_fwd(self.x_pool[p.name], p.q)
             p.y = y if keep else None
 
-    def _bwd_block(self, projs, keep=False):
+    def _bwd_block(self, projs, keep=False, first=False):
+        """`first`: the step's first microbatch overwrites dW instead of adding to it, so the
+        gradients need no clearing pass."""
         for p in reversed(projs):
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(self.x_pool[p.name], p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
-                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode)
+                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first)
             p.gx = gx if keep else None
 
     def capture(self):
@@ -177,18 +180,26 @@ class LinearStack:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         pool = torch.cuda.graph_pool_handle()
-        self.graphs_fwd, self.graphs_bwd = [], []
+        self.graphs_fwd, self.graphs_bwd, self.graphs_bwd_first = [], [], []
         for projs in self.blocks:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=pool):
                 self._fwd_block(projs)
             self.graphs_fwd.append(g)
-        for projs in reversed(self.blocks):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=pool):
-                self._bwd_block(projs)
-            self.graphs_bwd.append(g)
-        self.zero_grads()
+        # backward graphs run beside the gradient all-reduce: keep `comm_sms` SMs out of the GEMM grids
+        lib = _lib.load()
+        if self.comm_sms:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            lib.nvfp4_gemm_set_sm_budget(max(2, sms - self.comm_sms))
+        try:
+            for first, store in ((True, self.graphs_bwd_first), (False, self.graphs_bwd)):
+                for projs in reversed(self.blocks):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool):
+                        self._bwd_block(projs, first=first)
+                    store.append(g)
+        finally:
+            lib.nvfp4_gemm_set_sm_budget(0)
         torch.cuda.synchronize()
 
     def kernels_per_microbatch(self):
@@ -196,7 +207,7 @@ class LinearStack:
         bwd amax + quant_rows + gemm + 2 quant_cols_rht + gemm."""
         return self.n_proj * (3 + 6)
 
-    def microbatch(self, last, do_allreduce):
+    def microbatch(self, last, do_allreduce, first=False):
         """One forward + backward over all projections.  On the rank's last microbatch each block's
         weight gradients are all-reduced on the side stream right after its backward is enqueued."""
         self._bump_seeds()
@@ -210,9 +221,9 @@ class LinearStack:
         works = []
         for i, projs in enumerate(reversed(self.blocks)):
             if self.use_graphs and self.graphs_bwd is not None:
-                self.graphs_bwd[i].replay()
+                (self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
             else:
-                self._bwd_block(projs)
+                self._bwd_block(projs, first=first)
             if last and do_allreduce:
                 ev = torch.cuda.Event()
                 ev.record(cur)
@@ -223,10 +234,10 @@ class LinearStack:
 
     def step(self, n_micro, do_allreduce):
         """One optimizer step's worth of this path: re-quantize weights, clear dW, n_micro
-        microbatches, all-reduce.  Leaves the summed FP32 gradients in `p.gw`."""
+        microbatches (the first overwrites dW, the others add), all-reduce.  Leaves the summed FP32
+        gradients in `p.gw`."""
         self.refresh_weights()
-        self.zero_grads()
         for m in range(n_micro):
-            self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce)
+            self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce, first=(m == 0))
         if do_allreduce:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
