@@ -87,57 +87,68 @@ __device__ __forceinline__ long long sw_off(long long r, int c, int ncb) {
   return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
 }
 
+// Correctly rounded a/b from the correctly rounded reciprocal rb = RN(1/b): one multiply and two
+// fused multiply-adds (Markstein's final division step: q0 = RN(a*rb) is within an ulp of a/b, the
+// remainder a - q0*b is exact in one FMA, and RN(q0 + rem*rb) = RN(a/b) unless b's significand is
+// all ones).  The divisors here never have an all-ones significand: 6 and the E4M3 block scales
+// have at most 4 significant bits, and a tensor scale RN(amax/2688) would need amax strictly
+// between two neighbouring floats (2688 * (2^(e+1) - ulp) lies 0.33 to 0.98 of amax's ulp below the
+// representable 1.3125 * 2^(e+12)).  The remainder is formed negated so that a zero keeps its sign
+// (-0/b = -0).
+__device__ __forceinline__ float div_by(float a, float b, float rb) {
+  const float q0 = __fmul_rn(a, rb);
+  const float nrem = __fmaf_rn(q0, b, -a);
+  return __fmaf_rn(-nrem, rb, q0);
+}
+
 // Per-tensor constants of a quantizer launch.
 struct TensorScale {
   float gs;      // max(k*amax/2688, 1e-30): the FP32 tensor scale
-  float r6;      // 1/(6*gs), biased up by 2^-20: fast path of the block-scale argument
+  float rgs;     // RN(1/gs)
   float inv_gs;  // 2688/(k*amax), 0 for an all-zero tensor: the reference kernels' scale (llm-1b/nvq.cu:101)
-  const float* lut;   // shared memory, 128 entries: per scale byte, the multiplier that turns v into y
+  const float2* lut;   // shared memory, 128 entries indexed by the scale byte, see make_tensor_scale
 };
 
-// Fill the per-CTA table: for round to nearest  lut[sb] = (1/(gs*bs))*(1+2^-20)  (biased fast path),
-// for stochastic rounding  lut[sb] = inv_gs/bs  (the exact multiplier).  Ends with a block barrier.
+constexpr int kLutFloats = 256;
+
+// Fill the per-CTA table: for round to nearest  lut[sb] = {RN(1/bs), bs},  for stochastic rounding
+// lut[sb] = {inv_gs/bs, bs}  (the exact multiplier of the reference kernels).  `pre` is a power of
+// two that the caller's values still have to be multiplied by (0.25 after the Hadamard butterflies,
+// else 1): it is folded into gs, which changes no quotient.  Ends with a block barrier.
 template <int ROUNDING>
-__device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, float* lut) {
+__device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, float* lut, float* gs_out = nullptr,
+                                                         float pre = 1.f) {
   TensorScale t;
   const float am = amax * k;
-  t.gs = fmaxf(__fdiv_rn(am, kFp4E4m3), kTiny);
-  t.r6 = __fmul_rn(__frcp_rn(__fmul_rn(t.gs, 6.0f)), 1.00000095367431640625f);
-  t.inv_gs = am > 0.f ? __fdiv_rn(kFp4E4m3, am) : 0.f;
-  t.lut = lut;
+  const float gs = fmaxf(__fdiv_rn(am, kFp4E4m3), kTiny);
+  if (gs_out) *gs_out = gs;
+  t.gs = __fdiv_rn(gs, pre);
+  t.rgs = __frcp_rn(t.gs);
+  t.inv_gs = am > 0.f ? __fmul_rn(__fdiv_rn(kFp4E4m3, am), pre) : 0.f;
+  t.lut = reinterpret_cast<const float2*>(lut);
   if (threadIdx.x < 128) {
     const float bsf = e4m3_dec(threadIdx.x);
     float m = 0.f;
     if (threadIdx.x >= 1 && threadIdx.x <= 126)
-      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? __fmul_rn(__frcp_rn(__fmul_rn(t.gs, bsf)), 1.00000095367431640625f)
-                                            : __fdiv_rn(t.inv_gs, bsf);
-    lut[threadIdx.x] = m;
+      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? __frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);
+    reinterpret_cast<float2*>(lut)[threadIdx.x] = make_float2(m, bsf);
   }
   __syncthreads();
   return t;
 }
 
-// The exact (slow) forms live in functions that are never inlined: a call cannot be turned into
-// straight-line speculated code, so the IEEE divisions really run only on the rare slow path.
-static __device__ __noinline__ float exact_scale_arg(float bmax, float gs) { return __fdiv_rn(__fdiv_rn(bmax, gs), 6.0f); }
-static __device__ __noinline__ float exact_scaled(float v, float gs, float bsf) { return __fdiv_rn(__fdiv_rn(v, gs), bsf); }
-
 // Quantize one block of 16 values that share a scale.
-//   v      the 16 values (x, or the Hadamard-transformed x)
+//   v      the 16 values (x, or the Hadamard-transformed x before its power-of-two factor)
 //   bmax   max |v| over everything that shares the scale (16 values, or a 16x16 weight block)
 // Block scale, all modes:  bs = e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
-// Round to nearest:  y = (v/gs)/bs, the torch path's operation order.  Both the scale argument and y
-//   are first formed with a reciprocal biased upward by 2^-20: the product then lies in
-//   (exact, exact*(1+1.5*2^-20)], so it rounds like the exact value unless it sits within 32 ulp above
-//   a rounding boundary (E4M3 boundaries have 19 zero low mantissa bits, E2M1 boundaries 21); only
-//   then are the divisions done.
+// Round to nearest:  y = (v/gs)/bs, the torch path's operation order, each division correctly
+//   rounded by div_by() (three FMA-pipe instructions, no branch).
 // Stochastic rounding:  y = v * (inv_gs / bs), the reference kernels' form (llm-1b/nvq.cu:50,54) in
 //   IEEE arithmetic; the torch path draws torch.rand and so defines no bit-level result.
 template <int ROUNDING>
 __device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, const TensorScale& ts, u32 seed,
                                               u32 blk_idx, u32 elt_idx, uint2& codes, u32& sbyte) {
-  float sarg = __fmul_rn(bmax, ts.r6);
-  if (sarg < 0.03125f || (__float_as_uint(sarg) & 0x7FFE0u) == 0u) sarg = exact_scale_arg(bmax, ts.gs);
+  const float sarg = div_by(div_by(bmax, ts.gs, ts.rgs), 6.0f, 0.16666667163372039794921875f);
   const u32 sb = e4m3_enc(sarg);
   sbyte = sb;
   u32 w[2] = {0u, 0u};
@@ -148,26 +159,16 @@ __device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, 
     codes = make_uint2(w[0], w[1]);
     return;
   }
-  const float kf = ts.lut[sb];
+  const float2 kf = ts.lut[sb];
   float y[16];
   if (ROUNDING == NVFP4_ROUND_NEAREST) {
-    u32 nearest = 0xFFFFFFFFu;
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-      y[i] = __fmul_rn(v[i], kf);
-      nearest = min(nearest, __float_as_uint(y[i]) & 0x1FFFE0u);
-    }
-    if (nearest == 0u) {
-      const float bsf = e4m3_dec(sb);
-#pragma unroll
-      for (int i = 0; i < 16; i++)
-        if ((__float_as_uint(y[i]) & 0x1FFFE0u) == 0u) y[i] = exact_scaled(v[i], ts.gs, bsf);
-    }
+    for (int i = 0; i < 16; i++) y[i] = div_by(div_by(v[i], ts.gs, ts.rgs), kf.y, kf.x);
     w[0] = e2m1x8_rn(y);
     w[1] = e2m1x8_rn(y + 8);
   } else {
 #pragma unroll
-    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(v[i], kf);
+    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(v[i], kf.x);
     if (ROUNDING == NVFP4_ROUND_SR_HW) {
       const u32 hb = hash32(seed ^ hash32(blk_idx));
 #pragma unroll

@@ -59,10 +59,39 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------ rows
-// One warp per (row, 512-column segment): lanes load 16-byte chunks l and l+32 (coalesced), lane
-// pairs swap halves so each lane owns one whole 16-block (even lanes: blocks 0..15 of the segment,
-// odd lanes: blocks 16..31), then quantize it from registers.
-template <int ROUNDING>
+struct Block32 { u32 w[8]; };   // one 16-value bf16 block
+
+template <bool WIDE>
+__device__ __forceinline__ Block32 load_block(const __nv_bfloat16* p) {
+  Block32 r;
+  if (WIDE) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]), "=r"(r.w[6]), "=r"(r.w[7])
+                 : "l"(p));
+  } else {
+    const uint4 a = ldg128(p), b = ldg128(p + 8);
+    r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
+  }
+  return r;
+}
+
+// max |.| of the 16 packed bf16 values, as a float
+__device__ __forceinline__ float block_absmax(const Block32& b) {
+  __nv_bfloat162 m[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) m[i] = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b.w[i]));
+#pragma unroll
+  for (int h = 4; h; h >>= 1)
+#pragma unroll
+    for (int i = 0; i < h; i++) m[i] = __hmax2(m[i], m[i + h]);
+  const u32 mm = *reinterpret_cast<const u32*>(&m[0]);
+  return fmaxf(__uint_as_float(mm << 16), __uint_as_float(mm & 0xFFFF0000u));
+}
+
+// One warp per (row, 512-column segment); a lane owns one 16-block (32 contiguous bytes, one
+// 256-bit load when rows are 32-byte aligned), so the warp reads 1 KB contiguous and needs no
+// exchange.  The next item's load is issued before the current one is processed.
+template <int ROUNDING, bool WIDE>
 __global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                           uint2* __restrict__ codes, unsigned char* __restrict__ scales,
                                                           const float* __restrict__ amax, int R, int C, int linear,
@@ -70,51 +99,39 @@ __global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16*
                                                           float* __restrict__ gs_out) {
   if (ROUNDING != NVFP4_ROUND_NEAREST && seed_dev) seed = __ldg(seed_dev);
   const int lane = threadIdx.x & 31;
-  const int nchunk = C >> 3, nblk = C >> 4;
-  const int nseg = (nchunk + 63) >> 6;
-  __shared__ float lut[128];
-  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 1.f, lut);
-  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = ts.gs;
+  const int nblk = C >> 4;
+  const int nseg = (nblk + 31) >> 5;
+  __shared__ __align__(8) float lut[kLutFloats];
+  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 1.f, lut,
+                                                     (blockIdx.x == 0 && threadIdx.x == 0) ? gs_out : nullptr);
   // walk (row, segment) pairs with a fixed warp stride, without a division per item
   const unsigned nwarps = gridDim.x * (blockDim.x >> 5);
   const unsigned w0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int dr = (int)(nwarps / (unsigned)nseg), ds = (int)(nwarps % (unsigned)nseg);
   int r = (int)(w0 / (unsigned)nseg), seg = (int)(w0 % (unsigned)nseg);
-  const bool odd = lane & 1;
-  uint4 A = make_uint4(0, 0, 0, 0), B = make_uint4(0, 0, 0, 0);
-  if (r < R) {
-    const __nv_bfloat16* row = x + (long long)r * ldx;
-    if (seg * 64 + lane < nchunk) A = ldg128(row + (seg * 64 + lane) * 8);
-    if (seg * 64 + lane + 32 < nchunk) B = ldg128(row + (seg * 64 + lane + 32) * 8);
-  }
+  Block32 cur = {};
+  if (r < R && seg * 32 + lane < nblk) cur = load_block<WIDE>(x + (long long)r * ldx + (seg * 32 + lane) * 16);
   while (r < R) {
-    // next item of this warp: its loads are issued before the current item is processed
     int rn = r + dr, sn = seg + ds;
     if (sn >= nseg) { sn -= nseg; rn++; }
-    uint4 An = make_uint4(0, 0, 0, 0), Bn = make_uint4(0, 0, 0, 0);
-    if (rn < R) {
-      const __nv_bfloat16* row = x + (long long)rn * ldx;
-      if (sn * 64 + lane < nchunk) An = ldg128(row + (sn * 64 + lane) * 8);
-      if (sn * 64 + lane + 32 < nchunk) Bn = ldg128(row + (sn * 64 + lane + 32) * 8);
-    }
-    uint4 snd = odd ? A : B, rcv;
-    rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, 1); rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, 1);
-    rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, 1); rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, 1);
-    const uint4 lo = odd ? rcv : A, hi = odd ? B : rcv;
-    const int blk = seg * 32 + (lane >> 1) + (odd ? 16 : 0);
+    Block32 nxt = {};
+    if (rn < R && sn * 32 + lane < nblk) nxt = load_block<WIDE>(x + (long long)rn * ldx + (sn * 32 + lane) * 16);
+    const int blk = seg * 32 + lane;
     if (blk < nblk) {
+      const float bmax = block_absmax(cur);
       float v[16];
-      unpack8(lo, v); unpack8(hi, v + 8);
-      float bmax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; i++) bmax = fmaxf(bmax, fabsf(v[i]));
+      for (int i = 0; i < 8; i++) {
+        v[2 * i] = __uint_as_float(cur.w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(cur.w[i] & 0xFFFF0000u);
+      }
       const long long b = (long long)r * nblk + blk;
       uint2 o; u32 sb;
       quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
       codes[b] = o;
       scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
     }
-    r = rn; seg = sn; A = An; B = Bn;
+    r = rn; seg = sn; cur = nxt;
   }
 }
 
@@ -135,9 +152,10 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
   const int cchunk = blockIdx.x * 16 + (lane & 15);            // 8-column chunk index
   const int mb = blockIdx.y * 16 + warp * 2 + (lane >> 4);     // 16-token block index
   const int nmb = M >> 4;
-  __shared__ float lut[128];
-  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 4.f, lut);
-  if (gs_out && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *gs_out = ts.gs;
+  __shared__ __align__(8) float lut[kLutFloats];
+  // the x0.25 that follows the butterflies is folded into the tensor scale (a power of two)
+  const TensorScale ts = make_tensor_scale<ROUNDING>(__ldg(amax), 4.f, lut,
+      (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? gs_out : nullptr, 0.25f);
   if (cchunk * 8 >= C || mb >= nmb) return;
   uint4 raw[16];
   const __nv_bfloat16* p = x + (long long)mb * 16 * C + cchunk * 8;
@@ -166,7 +184,7 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
           if (!(i & h)) { const float a = v[i], b = v[i + h]; v[i] = __fadd_rn(a, b); v[i + h] = __fsub_rn(a, b); }
       float bmax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; i++) { v[i] = __fmul_rn(v[i], 0.25f); bmax = fmaxf(bmax, fabsf(v[i])); }
+      for (int i = 0; i < 16; i++) bmax = fmaxf(bmax, fabsf(v[i]));
       const long long c = (long long)cchunk * 8 + jw * 2 + hf;
       const long long b = c * nmb + mb;
       uint2 o; u32 sb;
@@ -190,9 +208,9 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nb = N >> 4, kb = K >> 4;
-  __shared__ float lut[128];
-  const TensorScale ts = make_tensor_scale<NVFP4_ROUND_NEAREST>(__ldg(amax), 1.f, lut);
-  if (gs_out && blockIdx.x == 0 && threadIdx.x == 0) *gs_out = ts.gs;
+  __shared__ __align__(8) float lut[kLutFloats];
+  const TensorScale ts = make_tensor_scale<NVFP4_ROUND_NEAREST>(__ldg(amax), 1.f, lut,
+                                                               (blockIdx.x == 0 && threadIdx.x == 0) ? gs_out : nullptr);
   if (warp >= (long long)nb * kb) return;
   const int bn = (int)(warp / kb), bk = (int)(warp - (long long)bn * kb);
   const int r = lane >> 1, c0 = (lane & 1) * 8;
@@ -314,16 +332,20 @@ extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   uint2* cp = static_cast<uint2*>(codes);
   unsigned char* sp = static_cast<unsigned char*>(scales);
+  // 256-bit loads need 32-byte aligned rows
+  const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (ldx & 15) == 0;
+#define NVFP4_ROWS(RND)                                                                                              \
+  do {                                                                                                               \
+    if (wide) quant_rows_kernel<RND, true><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); \
+    else quant_rows_kernel<RND, false><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out);     \
+  } while (0)
   switch (rounding) {
-    case NVFP4_ROUND_NEAREST:
-      quant_rows_kernel<NVFP4_ROUND_NEAREST><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
-    case NVFP4_ROUND_SR_DITHER:
-      quant_rows_kernel<NVFP4_ROUND_SR_DITHER><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
-    case NVFP4_ROUND_SR_DITHER_K:
-      quant_rows_kernel<NVFP4_ROUND_SR_DITHER_K><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
-    default:
-      quant_rows_kernel<NVFP4_ROUND_SR_HW><<<(unsigned)blocks, 256, 0, st>>>(xp, ldx, cp, sp, amax, R, C, linear, seed, seed_dev, gs_out); break;
+    case NVFP4_ROUND_NEAREST: NVFP4_ROWS(NVFP4_ROUND_NEAREST); break;
+    case NVFP4_ROUND_SR_DITHER: NVFP4_ROWS(NVFP4_ROUND_SR_DITHER); break;
+    case NVFP4_ROUND_SR_DITHER_K: NVFP4_ROWS(NVFP4_ROUND_SR_DITHER_K); break;
+    default: NVFP4_ROWS(NVFP4_ROUND_SR_HW); break;
   }
+#undef NVFP4_ROWS
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;
 }

@@ -76,7 +76,7 @@ def test_rows_strided_and_shared_amax(mods):
 @pytest.mark.parametrize("top", [48.0, 2688.0])
 def test_rows_fast_path_boundaries(mods, top):
     """Values whose scaled magnitude sits exactly on, or one bf16 step around, every rounding
-    boundary of the E2M1 grid: the reciprocal fast path must fall back to the exact divisions."""
+    boundary of the E2M1 grid: the FMA divisions must round exactly like IEEE divisions."""
     nvq, _, _ = mods
     rng = np.random.default_rng(11)
     bounds = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
@@ -90,6 +90,31 @@ def test_rows_fast_path_boundaries(mods, top):
     x = bf16_round(x)
     codes, scales, gs = O.quant_rows(x)
     check_nvq(nvq.quant_rows(to_dev(x)), codes, scales, gs, 128, 64)
+
+
+def test_rows_signed_zeros_and_tiny_values(mods):
+    """-0 and values far below the block scale keep their sign in the code (0x8 for negative zero)."""
+    nvq, _, _ = mods
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((128, 128)).astype(np.float32)
+    x[:, ::3] = -0.0
+    x[:, 1::5] = 0.0
+    x[:, 2::7] = -1e-30
+    x[:, 4::11] = 1e-38
+    x[5, :16] = -0.0                     # a whole block of negative zeros (scale byte 0)
+    x = bf16_round(x)
+    codes, scales, gs = O.quant_rows(x)
+    check_nvq(nvq.quant_rows(to_dev(x)), codes, scales, gs, 128, 128)
+
+
+def test_rows_16_byte_aligned_rows(mods):
+    """Rows that are 16- but not 32-byte aligned take the 128-bit load variant."""
+    nvq, _, _ = mods
+    x = make_x(9, 128, 256)
+    big = to_dev(np.concatenate([np.zeros((128, 8), np.float32), x], axis=1))   # row stride 264
+    view = big[:, 8:]
+    codes, scales, gs = O.quant_rows(x)
+    check_nvq(nvq.quant_rows(view), codes, scales, gs, 128, 256)
 
 
 @pytest.mark.parametrize("mode_name", ["SR_DITHER_NVQ", "SR_DITHER_FP4K"])
