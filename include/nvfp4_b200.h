@@ -101,6 +101,26 @@ int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales,
                          const unsigned* seed_dev, void* stream);
 
 /*
+ * One pass over x [M, C] bf16 (row stride ldx elements) producing BOTH operands the linear layer
+ * needs from an activation or a gradient: the row operand of `nvfp4_quant_rows` (codes_r, scales_r,
+ * gs_r_out) and the transposed RHT16 operand of `nvfp4_quant_cols_rht` (codes_c, scales_c, gs_c_out),
+ * bit-identical to those two calls with seeds seed_r / seed_c (seed_*_dev: device words that
+ * replace them).  Either output pair may be null to skip it.  The tensor is read from HBM once
+ * (TMA tiles of 128 tokens x 64 columns in a shared-memory ring).  Fuses the reference's pair of
+ * launches `quant_rows(gy)` + `quant_cols_rht(gy)` (llm-1b/model.py:62-66, llm-1b/nvq.py:46-70).
+ * Requires M % 128 == 0, C % 64 == 0 (C % 128 == 0 with SWIZZLED scales and codes_c), ldx % 8 == 0,
+ * x and codes_c 16-byte aligned, codes_r and scales_c 8-byte aligned.  A wait that expires inside the kernel (1 s) is reported by nvfp4_quant_tile_status.
+ */
+int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void* codes_r, void* scales_r, void* codes_c,
+                     void* scales_c, int scale_layout, const float* amax, float* gs_r_out, float* gs_c_out,
+                     unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
+                     const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
+
+/* Reads (synchronously) the status word of nvfp4_quant_tile launches on the current device:
+ * 0, or the role whose wait expired first (1 producer, 2 consumer); `reset` != 0 clears it. */
+int nvfp4_quant_tile_status(int* out, int reset);
+
+/*
  * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,
  * emitting W (q [N, K/2], s for [N, K/16]) and W^T (qt [K, N/2], st for [K, N/16]) with identical
  * code values.  Either output pair may be null to skip it.

@@ -87,31 +87,61 @@ __device__ __forceinline__ long long sw_off(long long r, int c, int ncb) {
   return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
 }
 
-// Correctly rounded a/b from the correctly rounded reciprocal rb = RN(1/b): one multiply and two
-// fused multiply-adds (Markstein's final division step: q0 = RN(a*rb) is within an ulp of a/b, the
-// remainder a - q0*b is exact in one FMA, and RN(q0 + rem*rb) = RN(a/b) unless b's significand is
-// all ones).  The divisors here never have an all-ones significand: 6 and the E4M3 block scales
-// have at most 4 significant bits, and a tensor scale RN(amax/2688) would need amax strictly
-// between two neighbouring floats (2688 * (2^(e+1) - ulp) lies 0.33 to 0.98 of amax's ulp below the
-// representable 1.3125 * 2^(e+12)).  The remainder is formed negated so that a zero keeps its sign
-// (-0/b = -0).
-__device__ __forceinline__ float div_by(float a, float b, float rb) {
-  const float q0 = __fmul_rn(a, rb);
-  const float nrem = __fmaf_rn(q0, b, -a);
-  return __fmaf_rn(-nrem, rb, q0);
+// ---- packed FP32 pairs (sm_100 f32x2 arithmetic: one issue slot for two IEEE operations) ----
+__device__ __forceinline__ u64 f2_pack(float lo, float hi) { u64 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ float f2_lo(u64 p) { return __uint_as_float((u32)p); }
+__device__ __forceinline__ float f2_hi(u64 p) { return __uint_as_float((u32)(p >> 32)); }
+__device__ __forceinline__ u64 f2_mul(u64 a, u64 b) { u64 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ u64 f2_add(u64 a, u64 b) { u64 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ u64 f2_sub(u64 a, u64 b) { u64 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ u64 f2_fma(u64 a, u64 b, u64 c) { u64 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+// the two bf16 values of a packed word as an FP32 pair (low half first)
+__device__ __forceinline__ u64 f2_from_bf16x2(u32 w) { return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u)); }
+
+struct Block32 { u32 w[8]; };   // one 16-value bf16 block
+
+// max |.| of the 16 packed bf16 values, as a float
+__device__ __forceinline__ float block_absmax(const Block32& b) {
+  __nv_bfloat162 m[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) m[i] = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b.w[i]));
+#pragma unroll
+  for (int h = 4; h; h >>= 1)
+#pragma unroll
+    for (int i = 0; i < h; i++) m[i] = __hmax2(m[i], m[i + h]);
+  const u32 mm = *reinterpret_cast<const u32*>(&m[0]);
+  return fmaxf(__uint_as_float(mm << 16), __uint_as_float(mm & 0xFFFF0000u));
+}
+
+// Correctly rounded -(a/b) from nrb = -RN(1/b): one multiply and two fused multiply-adds
+// (Markstein's final division step: m = RN(a*nrb) is within an ulp of -a/b, the remainder
+// a + m*b is exact in one FMA, and RN(m + rem*nrb) = -RN(a/b) unless b's significand is all
+// ones).  The divisors here never have an all-ones significand: 6 and the E4M3 block scales have
+// at most 4 significant bits, and a tensor scale RN(amax/2688) would need amax strictly between
+// two neighbouring floats (2688 * (2^(e+1) - ulp) lies 0.33 to 0.98 of amax's ulp below the
+// representable 1.3125 * 2^(e+12)).  The form returns the NEGATED quotient so that no operand
+// needs a sign flip and a zero keeps its sign exactly: a = +0 gives -0, a = -0 gives +0.  Two
+// divisions in a row therefore give +(a/b1)/b2 with the sign of a, zeros included.
+__device__ __forceinline__ float ndiv(float a, float b, float nrb) {
+  const float m = __fmul_rn(a, nrb);
+  return __fmaf_rn(__fmaf_rn(m, b, a), nrb, m);
+}
+__device__ __forceinline__ u64 f2_ndiv(u64 a, u64 b, u64 nrb) {
+  const u64 m = f2_mul(a, nrb);
+  return f2_fma(f2_fma(m, b, a), nrb, m);
 }
 
 // Per-tensor constants of a quantizer launch.
 struct TensorScale {
-  float gs;      // max(k*amax/2688, 1e-30): the FP32 tensor scale
-  float rgs;     // RN(1/gs)
-  float inv_gs;  // 2688/(k*amax), 0 for an all-zero tensor: the reference kernels' scale (llm-1b/nvq.cu:101)
+  float gs;      // max(k*amax/2688, 1e-30)/pre: the FP32 tensor scale the values are divided by
+  float nrgs;    // -RN(1/gs)
+  float inv_gs;  // pre*2688/(k*amax), 0 for an all-zero tensor: the reference kernels' scale (llm-1b/nvq.cu:101)
   const float2* lut;   // shared memory, 128 entries indexed by the scale byte, see make_tensor_scale
 };
 
 constexpr int kLutFloats = 256;
 
-// Fill the per-CTA table: for round to nearest  lut[sb] = {RN(1/bs), bs},  for stochastic rounding
+// Fill the per-CTA table: for round to nearest  lut[sb] = {-RN(1/bs), bs},  for stochastic rounding
 // lut[sb] = {inv_gs/bs, bs}  (the exact multiplier of the reference kernels).  `pre` is a power of
 // two that the caller's values still have to be multiplied by (0.25 after the Hadamard butterflies,
 // else 1): it is folded into gs, which changes no quotient.  Ends with a block barrier.
@@ -123,73 +153,115 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
   const float gs = fmaxf(__fdiv_rn(am, kFp4E4m3), kTiny);
   if (gs_out) *gs_out = gs;
   t.gs = __fdiv_rn(gs, pre);
-  t.rgs = __frcp_rn(t.gs);
+  t.nrgs = -__frcp_rn(t.gs);
   t.inv_gs = am > 0.f ? __fmul_rn(__fdiv_rn(kFp4E4m3, am), pre) : 0.f;
   t.lut = reinterpret_cast<const float2*>(lut);
   if (threadIdx.x < 128) {
     const float bsf = e4m3_dec(threadIdx.x);
-    float m = 0.f;
+    // entry 0 (underflowed block): -0 / +0 make every scaled value a zero with the input's sign
+    float m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -0.f : 0.f;
     if (threadIdx.x >= 1 && threadIdx.x <= 126)
-      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? __frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);
+      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -__frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);
     reinterpret_cast<float2*>(lut)[threadIdx.x] = make_float2(m, bsf);
   }
   __syncthreads();
   return t;
 }
 
+// Scale byte of a block:  e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
+__device__ __forceinline__ u32 block_scale_byte(float bmax, const TensorScale& ts) {
+  return e4m3_enc(ndiv(ndiv(bmax, ts.gs, ts.nrgs), 6.0f, -0.16666667163372039794921875f));
+}
+
+// random words of the hardware-SR mode: one per group of four consecutive elements of a block
+__device__ __forceinline__ u32 sr_hw_block_key(u32 seed, u32 blk_idx) { return hash32(seed ^ (blk_idx * 0x9E3779B9u)); }
+__device__ __forceinline__ u32 sr_hw_word(u32 key, int g) {
+  const u32 mult[4] = {0x9E3779B1u, 0x85EBCA77u, 0xC2B2AE3Du, 0x27D4EB2Fu};
+  const u32 x = key * mult[g];
+  return x ^ (x >> 16);
+}
+
+// Per-block key of the random stream of a rounding mode (0 where the mode needs none).
+template <int ROUNDING>
+__device__ __forceinline__ u32 block_key(u32 seed, u32 blk_idx) {
+  if (ROUNDING == NVFP4_ROUND_SR_HW) return sr_hw_block_key(seed, blk_idx);
+  if (ROUNDING == NVFP4_ROUND_SR_DITHER) return hash32(seed ^ hash32(blk_idx));
+  return 0u;
+}
+
+// Four scaled values (elements 4g .. 4g+3 of a block) -> 16 bits of codes.
+template <int ROUNDING>
+__device__ __forceinline__ u32 round4(float a, float b, float c, float d, u32 key, u32 seed, u32 elt_idx, int g) {
+  if (ROUNDING == NVFP4_ROUND_SR_HW) return e2m1x4_rs(a, b, c, d, sr_hw_word(key, g));
+  if (ROUNDING == NVFP4_ROUND_SR_DITHER || ROUNDING == NVFP4_ROUND_SR_DITHER_K) {
+    const u32 i = 4u * (u32)g;
+    const u32 h0 = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(key + i) : hash32(seed ^ (elt_idx + i) * 0x9E3779B9u);
+    const u32 h1 = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(key + i + 2u) : hash32(seed ^ (elt_idx + i + 2u) * 0x9E3779B9u);
+    a = sr_dither(a, h0); b = sr_dither(b, (h0 >> 10) | (h0 << 22));
+    c = sr_dither(c, h1); d = sr_dither(d, (h1 >> 10) | (h1 << 22));
+  }
+  return e2m1x2_rn(a, b) | (e2m1x2_rn(c, d) << 8);
+}
+
 // Quantize one block of 16 values that share a scale.
 //   v      the 16 values (x, or the Hadamard-transformed x before its power-of-two factor)
-//   bmax   max |v| over everything that shares the scale (16 values, or a 16x16 weight block)
-// Block scale, all modes:  bs = e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
+//   sb     the block's scale byte (block_scale_byte of max |v| over everything that shares the scale)
 // Round to nearest:  y = (v/gs)/bs, the torch path's operation order, each division correctly
-//   rounded by div_by() (three FMA-pipe instructions, no branch).
+//   rounded by f2_ndiv() (three packed FMA-pipe instructions per two values, no branch).
 // Stochastic rounding:  y = v * (inv_gs / bs), the reference kernels' form (llm-1b/nvq.cu:50,54) in
 //   IEEE arithmetic; the torch path draws torch.rand and so defines no bit-level result.
+// A block whose scale byte is 0 needs no branch: table entry 0 turns every value into a zero with
+// the sign of the input, which the converts keep.
 template <int ROUNDING>
-__device__ __forceinline__ void quant_block16(const float (&v)[16], float bmax, const TensorScale& ts, u32 seed,
-                                              u32 blk_idx, u32 elt_idx, uint2& codes, u32& sbyte) {
-  const float sarg = div_by(div_by(bmax, ts.gs, ts.rgs), 6.0f, 0.16666667163372039794921875f);
-  const u32 sb = e4m3_enc(sarg);
-  sbyte = sb;
-  u32 w[2] = {0u, 0u};
-  if (sb == 0u) {
-    // underflowed block: value 0 with the sign of the input
-#pragma unroll
-    for (int i = 0; i < 16; i++) w[i >> 3] |= ((__float_as_uint(v[i]) >> 31) << 3) << ((i & 7) * 4);
-    codes = make_uint2(w[0], w[1]);
-    return;
-  }
+__device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const TensorScale& ts, u32 seed,
+                                               u32 blk_idx, u32 elt_idx) {
   const float2 kf = ts.lut[sb];
-  float y[16];
-  if (ROUNDING == NVFP4_ROUND_NEAREST) {
+  const u32 key = block_key<ROUNDING>(seed, blk_idx);
+  const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
+  const u64 B = f2_pack(kf.y, kf.y), K = f2_pack(kf.x, kf.x);
+  u32 w[2] = {0u, 0u};
 #pragma unroll
-    for (int i = 0; i < 16; i++) y[i] = div_by(div_by(v[i], ts.gs, ts.rgs), kf.y, kf.x);
-    w[0] = e2m1x8_rn(y);
-    w[1] = e2m1x8_rn(y + 8);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(v[i], kf.x);
-    if (ROUNDING == NVFP4_ROUND_SR_HW) {
-      const u32 hb = hash32(seed ^ hash32(blk_idx));
-#pragma unroll
-      for (int g = 0; g < 4; g++) {
-        const u32 rb = hash32(hb + 0x9E3779B9u * (u32)(g + 1));
-        w[g >> 1] |= e2m1x4_rs(y[4 * g], y[4 * g + 1], y[4 * g + 2], y[4 * g + 3], rb) << ((g & 1) * 16);
-      }
+  for (int g = 0; g < 4; g++) {
+    u64 r0, r1;
+    if (ROUNDING == NVFP4_ROUND_NEAREST) {
+      r0 = f2_ndiv(f2_ndiv(P[2 * g], G, NRG), B, K);
+      r1 = f2_ndiv(f2_ndiv(P[2 * g + 1], G, NRG), B, K);
     } else {
-      const u32 hb = hash32(seed ^ hash32(blk_idx));
-#pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const u32 h = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(hb + (u32)i)
-                                                          : hash32(seed ^ (elt_idx + (u32)i) * 0x9E3779B9u);
-        y[i] = sr_dither(y[i], h);
-        y[i + 1] = sr_dither(y[i + 1], (h >> 10) | (h << 22));
-      }
-      w[0] = e2m1x8_rn(y);
-      w[1] = e2m1x8_rn(y + 8);
+      r0 = f2_mul(P[2 * g], K);
+      r1 = f2_mul(P[2 * g + 1], K);
     }
+    w[g >> 1] |= round4<ROUNDING>(f2_lo(r0), f2_hi(r0), f2_lo(r1), f2_hi(r1), key, seed, elt_idx, g) << ((g & 1) * 16);
   }
-  codes = make_uint2(w[0], w[1]);
+  return make_uint2(w[0], w[1]);
+}
+
+// Two blocks at once, interleaved: P[i] = (value i of block 0, value i of block 1), e.g. two
+// neighbouring columns of 16 tokens.  Same arithmetic as quant_block16, the two blocks' scales
+// riding in the two halves of the packed constants.
+template <int ROUNDING>
+__device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const TensorScale& ts, u32 seed, u32 blk0, u32 blk1,
+                                                uint2& o0, uint2& o1, u32& sb0, u32& sb1) {
+  float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; i++) { m0 = fmaxf(m0, fabsf(f2_lo(P[i]))); m1 = fmaxf(m1, fabsf(f2_hi(P[i]))); }
+  sb0 = block_scale_byte(m0, ts);
+  sb1 = block_scale_byte(m1, ts);
+  const float2 k0 = ts.lut[sb0], k1 = ts.lut[sb1];
+  const u32 key0 = block_key<ROUNDING>(seed, blk0), key1 = block_key<ROUNDING>(seed, blk1);
+  const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
+  const u64 B = f2_pack(k0.y, k1.y), K = f2_pack(k0.x, k1.x);
+  u32 w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    u64 r[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      r[j] = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[4 * g + j], G, NRG), B, K) : f2_mul(P[4 * g + j], K);
+    w0[g >> 1] |= round4<ROUNDING>(f2_lo(r[0]), f2_lo(r[1]), f2_lo(r[2]), f2_lo(r[3]), key0, seed, blk0 * 16u, g) << ((g & 1) * 16);
+    w1[g >> 1] |= round4<ROUNDING>(f2_hi(r[0]), f2_hi(r[1]), f2_hi(r[2]), f2_hi(r[3]), key1, seed, blk1 * 16u, g) << ((g & 1) * 16);
+  }
+  o0 = make_uint2(w0[0], w0[1]);
+  o1 = make_uint2(w1[0], w1[1]);
 }
 
 }  // namespace nvfp4

@@ -19,9 +19,7 @@
 // advanced by adds, high words are constants): a single thread feeds the whole tensor core.
 // Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, reports a code through
 // `status`, lets copies in flight land, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace nvfp4 {
 
@@ -30,7 +28,6 @@ constexpr int kBKBytes = 128;       // bytes of K per stage row = 256 FP4 values
 constexpr int kBK = 256;            // FP4 values of K per stage
 constexpr int kEpiWarps = 8;         // two warps per 32-lane quadrant of tensor memory
 constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr u64 kWaitLimitNs = 1000000000ull;   // 1 s per wait, far above any legitimate wait
 
 template <int BN>
 struct Cfg {
@@ -70,54 +67,6 @@ struct GemmParams {
 };
 
 // ---------------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(u32 bar, u32 count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(u32 bar, u32 bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(u32 bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ u32 mbar_try_wait(u32 bar, u32 parity) {
-  u32 ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-__device__ __forceinline__ u64 globaltimer_ns() {
-  u64 t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one expired).
-__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const u64 t0 = globaltimer_ns();
-  for (u32 it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 127u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(u32 dst, const CUtensorMap* map, int x, int y, u32 bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void bulk_load(u32 dst, const void* src, u32 bytes, u32 bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
 __device__ __forceinline__ void tmem_alloc(u32 smem_dst, u32 ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -177,13 +126,6 @@ __host__ __device__ constexpr u32 make_idesc(int n) {
 }
 
 // ---------------------------------------------------------------------------------------- kernel
-// true in exactly one lane of a converged warp
-__device__ __forceinline__ bool elect_one() {
-  u32 pred;
-  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-  return pred != 0u;
-}
-
 __device__ __forceinline__ u64 pack64(u32 lo, u32 hi) {
   u64 d;
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
@@ -913,22 +855,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 // ---------------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
 // rows x kbytes byte matrix with row stride ld bytes; box = box_rows x 128 bytes, 128-byte swizzle
 static bool make_map(CUtensorMap* map, const void* base, long long rows, long long kbytes, long long ld, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();

@@ -59,8 +59,6 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------ rows
-struct Block32 { u32 w[8]; };   // one 16-value bf16 block
-
 template <bool WIDE>
 __device__ __forceinline__ Block32 load_block(const __nv_bfloat16* p) {
   Block32 r;
@@ -73,19 +71,6 @@ __device__ __forceinline__ Block32 load_block(const __nv_bfloat16* p) {
     r.w[0] = a.x; r.w[1] = a.y; r.w[2] = a.z; r.w[3] = a.w; r.w[4] = b.x; r.w[5] = b.y; r.w[6] = b.z; r.w[7] = b.w;
   }
   return r;
-}
-
-// max |.| of the 16 packed bf16 values, as a float
-__device__ __forceinline__ float block_absmax(const Block32& b) {
-  __nv_bfloat162 m[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) m[i] = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b.w[i]));
-#pragma unroll
-  for (int h = 4; h; h >>= 1)
-#pragma unroll
-    for (int i = 0; i < h; i++) m[i] = __hmax2(m[i], m[i + h]);
-  const u32 mm = *reinterpret_cast<const u32*>(&m[0]);
-  return fmaxf(__uint_as_float(mm << 16), __uint_as_float(mm & 0xFFFF0000u));
 }
 
 // One warp per (row, 512-column segment); a lane owns one 16-block (32 contiguous bytes, one
@@ -118,17 +103,12 @@ __global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16*
     if (rn < R && sn * 32 + lane < nblk) nxt = load_block<WIDE>(x + (long long)rn * ldx + (sn * 32 + lane) * 16);
     const int blk = seg * 32 + lane;
     if (blk < nblk) {
-      const float bmax = block_absmax(cur);
-      float v[16];
+      const u32 sb = block_scale_byte(block_absmax(cur), ts);
+      u64 P[8];
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        v[2 * i] = __uint_as_float(cur.w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(cur.w[i] & 0xFFFF0000u);
-      }
+      for (int i = 0; i < 8; i++) P[i] = f2_from_bf16x2(cur.w[i]);
       const long long b = (long long)r * nblk + blk;
-      uint2 o; u32 sb;
-      quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
-      codes[b] = o;
+      codes[b] = quant_block16<ROUNDING>(P, sb, ts, seed, (u32)b, (u32)(b * 16));
       scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
     }
     r = rn; seg = sn; cur = nxt;
@@ -141,7 +121,7 @@ __global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16*
 // block lives in its registers: sign flip, 4 butterfly stages, x0.25 and quantization need no
 // shared memory.  Outputs: 8 bytes of codes + 1 scale byte per (column, token block).
 template <int ROUNDING>
-__global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256, 2) quant_cols_rht_kernel(const __nv_bfloat16* __restrict__ x,
                                                               unsigned char* __restrict__ codes,
                                                               unsigned char* __restrict__ scales,
                                                               const float* __restrict__ amax, int M, int C, int linear,
@@ -167,31 +147,27 @@ __global__ void __launch_bounds__(256) quant_cols_rht_kernel(const __nv_bfloat16
     const u32 f = ((signs >> i) & 1u) ? 0x80008000u : 0u;
     raw[i].x ^= f; raw[i].y ^= f; raw[i].z ^= f; raw[i].w ^= f;
   }
-  // four rounds of two columns: the packed words are rotated so that the loop body (two block
-  // quantizations) exists once in the instruction stream
+  // four rounds of two columns (one packed word per token): the words are rotated so that the
+  // loop body exists once in the instruction stream.  The two columns ride in the two halves of
+  // packed FP32 pairs through the butterflies and the scaling.
 #pragma unroll 1
   for (int jw = 0; jw < 4; jw++) {
+    u64 P[16];
 #pragma unroll
-    for (int hf = 0; hf < 2; hf++) {
-      float v[16];
+    for (int i = 0; i < 16; i++) P[i] = f2_from_bf16x2(raw[i].x);
+#pragma unroll
+    for (int h = 1; h < 16; h <<= 1)
 #pragma unroll
       for (int i = 0; i < 16; i++)
-        v[i] = hf ? __uint_as_float(raw[i].x & 0xFFFF0000u) : __uint_as_float(raw[i].x << 16);
-#pragma unroll
-      for (int h = 1; h < 16; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-          if (!(i & h)) { const float a = v[i], b = v[i + h]; v[i] = __fadd_rn(a, b); v[i + h] = __fsub_rn(a, b); }
-      float bmax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; i++) bmax = fmaxf(bmax, fabsf(v[i]));
-      const long long c = (long long)cchunk * 8 + jw * 2 + hf;
-      const long long b = c * nmb + mb;
-      uint2 o; u32 sb;
-      quant_block16<ROUNDING>(v, bmax, ts, seed, (u32)b, (u32)(b * 16), o, sb);
-      *reinterpret_cast<uint2*>(codes + b * 8) = o;
-      scales[linear ? b : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb;
-    }
+        if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
+    const long long c = (long long)cchunk * 8 + jw * 2;
+    const long long b0 = c * nmb + mb, b1 = b0 + nmb;
+    uint2 o0, o1; u32 sb0, sb1;
+    quant_block16x2<ROUNDING>(P, ts, seed, (u32)b0, (u32)b1, o0, o1, sb0, sb1);
+    *reinterpret_cast<uint2*>(codes + b0 * 8) = o0;
+    *reinterpret_cast<uint2*>(codes + b1 * 8) = o1;
+    scales[linear ? b0 : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb0;
+    scales[linear ? b1 : sw_off(c + 1, mb, nmb >> 2)] = (unsigned char)sb1;
 #pragma unroll
     for (int i = 0; i < 16; i++) { raw[i].x = raw[i].y; raw[i].y = raw[i].z; raw[i].z = raw[i].w; }
   }
@@ -215,7 +191,7 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
   const int bn = (int)(warp / kb), bk = (int)(warp - (long long)bn * kb);
   const int r = lane >> 1, c0 = (lane & 1) * 8;
   const T* src = w + (long long)(bn * 16 + r) * K + bk * 16 + c0;
-  float v[16];
+  float v[8];
   if constexpr (sizeof(T) == 2) {
     unpack8(ldg128(src), v);
   } else {
@@ -227,12 +203,13 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
   for (int i = 0; i < 8; i++) bmax = fmaxf(bmax, fabsf(v[i]));
 #pragma unroll
   for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
-  // reuse the 16-wide block quantizer on 8 live values (upper half = copies, discarded)
-#pragma unroll
-  for (int i = 0; i < 8; i++) v[8 + i] = v[i];
-  uint2 o; u32 sb;
-  quant_block16<NVFP4_ROUND_NEAREST>(v, bmax, ts, 0u, 0u, 0u, o, sb);
-  const u32 word = o.x;
+  const u32 sb = block_scale_byte(bmax, ts);
+  const float2 kf = ts.lut[sb];
+  const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs), B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
+  const u64 q01 = f2_ndiv(f2_ndiv(f2_pack(v[0], v[1]), G, NRG), B, NRB), q23 = f2_ndiv(f2_ndiv(f2_pack(v[2], v[3]), G, NRG), B, NRB);
+  const u64 q45 = f2_ndiv(f2_ndiv(f2_pack(v[4], v[5]), G, NRG), B, NRB), q67 = f2_ndiv(f2_ndiv(f2_pack(v[6], v[7]), G, NRG), B, NRB);
+  const u32 word = round4<NVFP4_ROUND_NEAREST>(f2_lo(q01), f2_hi(q01), f2_lo(q23), f2_hi(q23), 0u, 0u, 0u, 0) |
+                   (round4<NVFP4_ROUND_NEAREST>(f2_lo(q45), f2_hi(q45), f2_lo(q67), f2_hi(q67), 0u, 0u, 0u, 1) << 16);
   if (q) {
     q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;
     if (!(lane & 1)) s[linear ? (long long)(bn * 16 + r) * kb + bk : sw_off(bn * 16 + r, bk, kb >> 2)] = (unsigned char)sb;

@@ -79,6 +79,46 @@ def quant_cols_rht(x, signs, sr=False, seed=0, am=None, sr_mode=None):
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 
 
+def quant_rows_cols_rht(x, signs, sr=False, seed=0, seed_cols=0, am=None, sr_mode=None, want=(True, True)):
+    """x [M, C] bf16 -> (Q of x along C, Q of x^T along M after the 16-pt RHT): the results of
+    `quant_rows(x, ...)` and `quant_cols_rht(x, signs, ...)` (llm-1b/nvq.py:47-70) from one pass
+    over x.  `seed` rounds the row operand, `seed_cols` the transposed one; `want` skips an output."""
+    L.require_cuda(x)
+    M, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    assert M % 128 == 0 and C % 128 == 0, (M, C)
+    if am is None:
+        am = amax(x.contiguous())
+    dev = x.device
+    qr = qc = None
+    dr = sr_ = gr = dc = sc = gc = None
+    if want[0]:
+        dr = torch.empty(M, C // 2, dtype=torch.uint8, device=dev)
+        sr_ = torch.empty(M * C // 16, dtype=torch.uint8, device=dev)
+        gr = _new_gs(am)
+        qr = Q(dr.view(torch.float4_e2m1fn_x2), sr_.view(torch.float8_e4m3fn), gr)
+    if want[1]:
+        dc = torch.empty(C, M // 2, dtype=torch.uint8, device=dev)
+        sc = torch.empty(C * M // 16, dtype=torch.uint8, device=dev)
+        gc = _new_gs(am)
+        qc = Q(dc.view(torch.float4_e2m1fn_x2), sc.view(torch.float8_e4m3fn), gc)
+    seed_r, seed_r_dev = L.seed_args(seed)
+    seed_c, seed_c_dev = L.seed_args(seed_cols)
+    L.check(L.load().nvfp4_quant_tile(L.ptr(x), x.stride(0), M, C, L.ptr(dr), L.ptr(sr_), L.ptr(dc), L.ptr(sc),
+                                      L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gr), L.ptr(gc), signs & 0xFFFF,
+                                      (sr_mode or SR_MODE) if sr else L.ROUND_NEAREST, seed_r, seed_c, seed_r_dev, seed_c_dev,
+                                      L.stream()), "quant_tile")
+    return qr, qc
+
+
+def quant_tile_status(reset=True):
+    """Status word of the tile quantizer on the current device (0 = no wait ever expired)."""
+    import ctypes
+    out = ctypes.c_int(0)
+    L.check(L.load().nvfp4_quant_tile_status(ctypes.byref(out), 1 if reset else 0), "quant_tile_status")
+    return out.value
+
+
 def quant_w2d(w, am=None, want=(True, True), out=None):
     """w [N, K] bf16 -> (Q of w, Q of w^T), identical values (16x16 blocks) (llm-1b/nvq.py:73-87).
     `want` lets a caller skip one of the two outputs (its slot is then None); `out` = a pair

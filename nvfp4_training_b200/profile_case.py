@@ -64,7 +64,16 @@ def main():
                          ("quant_cols_rht_sr_hw", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, am=am))):
             us = timed(fn, a.iters)
             out[name] = {"us": us, "gbs": n * 2.5625 / us / 1e3}
+        for name, fn, bpe in (("tile_rows+cols_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am), 3.125),
+                              ("tile_cols_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am, want=(False, True)), 2.5625),
+                              ("tile_rows_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am, want=(True, False)), 2.5625)):
+            us = timed(fn, a.iters)
+            out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
         nvq.SR_MODE = _lib.ROUND_SR_DITHER
+        for name, fn, bpe in (("tile_rows+cols_rn", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, am=am), 3.125),
+                              ("tile_cols_rn", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, am=am, want=(False, True)), 2.5625)):
+            us = timed(fn, a.iters)
+            out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
         w = torch.randn(a.N, a.K, generator=g, device="cuda").bfloat16()
         us = timed(lambda: nvq.quant_w2d(w), a.iters)
         out["amax+quant_w2d"] = {"us": us, "gbs": a.N * a.K * 5.125 / us / 1e3}

@@ -214,15 +214,19 @@ def sr_bits_fp4k(seed, elt_idx):
     return out
 
 
+_SR_HW_MULT = (0x9E3779B1, 0x85EBCA77, 0xC2B2AE3D, 0x27D4EB2F)
+
+
 def sr_words_hw(seed, blk_idx):
     """Counter-based stream of this library for the hardware-SR mode: one 32-bit word per group of
-    four consecutive elements, hb = hash32(seed ^ hash32(blk)); word g = hash32(hb + 0x9E3779B9*(g+1)).
-    Returns [..., 4] words."""
+    four consecutive elements.  key = hash32(seed ^ blk * 0x9E3779B9); word g = x ^ (x >> 16) with
+    x = key * mult[g] (four odd constants), all mod 2^32.  Returns [..., 4] words."""
     blk_idx = np.asarray(blk_idx, dtype=np.uint32)
-    hb = hash32(np.uint32(seed & 0xFFFFFFFF) ^ hash32(blk_idx))
+    key = hash32(np.uint32(seed & 0xFFFFFFFF) ^ (blk_idx * np.uint32(0x9E3779B9)))
     out = np.empty(blk_idx.shape + (4,), dtype=np.uint32)
     for g in range(4):
-        out[..., g] = hash32(hb + np.uint32((0x9E3779B9 * (g + 1)) & 0xFFFFFFFF))
+        x = key * np.uint32(_SR_HW_MULT[g])
+        out[..., g] = x ^ (x >> np.uint32(16))
     return out
 
 

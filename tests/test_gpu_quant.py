@@ -216,6 +216,70 @@ def test_cols_rht_sr_dither_bit_exact(mods, signs):
     assert np.array_equal(u8(q.d), codes) and np.array_equal(u8(q.s), scales)
 
 
+SR_MODES = {"rn": None, "dither": "SR_DITHER_NVQ", "dither_k": "SR_DITHER_FP4K", "hw": "SR_HW"}
+
+
+@pytest.mark.parametrize("mode", ["rn", "dither", "dither_k", "hw"])
+@pytest.mark.parametrize("M,C", [(128, 128), (384, 640), (2048, 256)])
+def test_tile_quantizer_matches_both_oracles(mods, mode, M, C):
+    """The one-read tile kernel gives the row operand and the transposed RHT operand bit for bit,
+    in every rounding mode, with separate seeds for the two outputs."""
+    nvq, _, L = mods
+    signs = 0x9C3A
+    x = make_dy(M + C, M, C)
+    x[5, :16] = 0.0                 # an all-zero block (scale byte 0)
+    x[16:32, 3] = -0.0
+    xd = to_dev(x)
+    if mode == "rn":
+        r = O.quant_rows(x)
+        c = O.quant_cols_rht(x, signs)
+        qr, qc = nvq.quant_rows_cols_rht(xd, signs)
+    else:
+        om = getattr(O, SR_MODES[mode])
+        lm = {"dither": L.ROUND_SR_DITHER, "dither_k": L.ROUND_SR_DITHER_K, "hw": L.ROUND_SR_HW}[mode]
+        r = O.quant_rows(x, sr_mode=om, seed=11)
+        c = O.quant_cols_rht(x, signs, sr_mode=om, seed=0xBEEF)
+        qr, qc = nvq.quant_rows_cols_rht(xd, signs, sr=True, seed=11, seed_cols=0xBEEF, sr_mode=lm)
+    check_nvq(qr, r[0], r[1], r[2], M, C)
+    check_nvq(qc, c[0], c[1], c[2], C, M)
+    assert nvq.quant_tile_status() == 0
+
+
+def test_tile_quantizer_single_outputs_strided_input_and_device_seeds(mods):
+    nvq, _, L = mods
+    signs = 0x0F0F
+    x = make_x(21, 256, 256)
+    big = to_dev(np.concatenate([x, x], axis=1))
+    view = big[:, 256:]                                   # row stride 512
+    r = O.quant_rows(x)
+    c = O.quant_cols_rht(x, signs)
+    qr, none = nvq.quant_rows_cols_rht(view, signs, want=(True, False))
+    assert none is None
+    check_nvq(qr, r[0], r[1], r[2], 256, 256)
+    none, qc = nvq.quant_rows_cols_rht(view, signs, want=(False, True))
+    assert none is None
+    check_nvq(qc, c[0], c[1], c[2], 256, 256)
+    sd = torch.tensor([77, 78], dtype=torch.int32, device="cuda")
+    r = O.quant_rows(x, sr_mode=O.SR_HW, seed=77)
+    c = O.quant_cols_rht(x, signs, sr_mode=O.SR_HW, seed=78)
+    qr, qc = nvq.quant_rows_cols_rht(view, signs, sr=True, seed=sd[0:1], seed_cols=sd[1:2], sr_mode=L.ROUND_SR_HW)
+    check_nvq(qr, r[0], r[1], r[2], 256, 256)
+    check_nvq(qc, c[0], c[1], c[2], 256, 256)
+
+
+def test_tile_quantizer_rejects_bad_shapes(mods):
+    nvq, _, L = mods
+    lib = L.load()
+    x = torch.zeros(128, 192, dtype=torch.bfloat16, device="cuda")
+    am = torch.ones(1, device="cuda")
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    args = lambda M, C: (x.data_ptr(), C, M, C, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(),
+                         L.SCALES_SWIZZLED, am.data_ptr(), None, None, 0, 0, 0, 0, None, None, None)
+    assert lib.nvfp4_quant_tile(*args(128, 192)) == -2       # swizzled column scales need C % 128
+    assert lib.nvfp4_quant_tile(*args(64, 128)) == -2
+    assert lib.nvfp4_quant_tile(*args(0, 128)) == 0
+
+
 def test_device_side_seed(mods):
     """A seed read from device memory gives the same bits as the same seed passed by value."""
     nvq, _, _ = mods
