@@ -184,6 +184,11 @@ def time_events(fn, iters, warm=3):
     return a.elapsed_time(b) / iters * 1e-3
 
 
+def _lib_consts():
+    from nvfp4_training_b200 import _lib
+    return _lib
+
+
 def isolated_kernels(cfg, T, peaks):
     """Time the GEMM and the quantizers alone (CUDA events on the launch stream), rotating operand
     sets so consecutive launches do not find their inputs in L2.  Returns the roofline object for
@@ -245,12 +250,18 @@ def isolated_kernels(cfg, T, peaks):
     detail["amax"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.0 / t / 1e9}
     t = q(lambda t, a: nvq.quant_rows(t, am=a))
     detail["quant_rows_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
-    t = q(lambda t, a: nvq.quant_rows(t, sr=True, seed=1, am=a))
-    detail["quant_rows_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    HW = _lib_consts().ROUND_SR_HW          # the stack rounds gradients with the hardware convert
+    t = q(lambda t, a: nvq.quant_rows(t, sr=True, seed=1, am=a, sr_mode=HW))
+    detail["quant_rows_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     t = q(lambda t, a: nvq.quant_cols_rht(t, 0xA6B1, am=a))
     detail["quant_cols_rht_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
-    t = q(lambda t, a: nvq.quant_cols_rht(t, 0xA6B1, sr=True, seed=1, am=a))
-    detail["quant_cols_rht_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_cols_rht(t, 0xA6B1, sr=True, seed=1, am=a, sr_mode=HW))
+    detail["quant_cols_rht_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    # the one-read tile quantizer (row + transposed operand): 2 B in, 2 x 0.5625 B out per element
+    t = q(lambda t, a: nvq.quant_rows_cols_rht(t, 0xA6B1, am=a))
+    detail["quant_tile_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 3.125 / t / 1e9}
+    t = q(lambda t, a: nvq.quant_rows_cols_rht(t, 0xA6B1, sr=True, seed=1, seed_cols=2, am=a, sr_mode=HW))
+    detail["quant_tile_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 3.125 / t / 1e9}
     w = [torch.randn(11264, 2048, generator=g, device=dev).bfloat16() for _ in range(4)]
     it = [0]
 

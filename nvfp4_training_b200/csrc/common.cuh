@@ -95,22 +95,27 @@ __device__ __forceinline__ u64 f2_mul(u64 a, u64 b) { u64 r; asm("mul.rn.f32x2 %
 __device__ __forceinline__ u64 f2_add(u64 a, u64 b) { u64 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 __device__ __forceinline__ u64 f2_sub(u64 a, u64 b) { u64 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 __device__ __forceinline__ u64 f2_fma(u64 a, u64 b, u64 c) { u64 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+// max(|a|, |b|, |c|) in one instruction (sm_100 three-input max)
+__device__ __forceinline__ float absmax3(float a, float b, float c) {
+  float d;
+  asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // the two bf16 values of a packed word as an FP32 pair (low half first)
 __device__ __forceinline__ u64 f2_from_bf16x2(u32 w) { return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u)); }
 
 struct Block32 { u32 w[8]; };   // one 16-value bf16 block
 
-// max |.| of the 16 packed bf16 values, as a float
-__device__ __forceinline__ float block_absmax(const Block32& b) {
-  __nv_bfloat162 m[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) m[i] = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b.w[i]));
-#pragma unroll
-  for (int h = 4; h; h >>= 1)
-#pragma unroll
-    for (int i = 0; i < h; i++) m[i] = __hmax2(m[i], m[i + h]);
-  const u32 mm = *reinterpret_cast<const u32*>(&m[0]);
-  return fmaxf(__uint_as_float(mm << 16), __uint_as_float(mm & 0xFFFF0000u));
+// max |.| over the 16 values of 8 packed pairs
+__device__ __forceinline__ float absmax16(const u64 (&P)[8]) {
+  float m = absmax3(f2_lo(P[0]), f2_hi(P[0]), f2_lo(P[1]));
+  m = absmax3(m, f2_hi(P[1]), f2_lo(P[2]));
+  m = absmax3(m, f2_hi(P[2]), f2_lo(P[3]));
+  m = absmax3(m, f2_hi(P[3]), f2_lo(P[4]));
+  m = absmax3(m, f2_hi(P[4]), f2_lo(P[5]));
+  m = absmax3(m, f2_hi(P[5]), f2_lo(P[6]));
+  m = absmax3(m, f2_hi(P[6]), f2_lo(P[7]));
+  return absmax3(m, f2_hi(P[7]), m);
 }
 
 // Correctly rounded -(a/b) from nrb = -RN(1/b): one multiply and two fused multiply-adds
@@ -189,18 +194,21 @@ __device__ __forceinline__ u32 block_key(u32 seed, u32 blk_idx) {
   return 0u;
 }
 
-// Four scaled values (elements 4g .. 4g+3 of a block) -> 16 bits of codes.
+// Eight scaled values (elements 8h .. 8h+7 of a block, h = 0 or 1) -> one 32-bit word of codes.
 template <int ROUNDING>
-__device__ __forceinline__ u32 round4(float a, float b, float c, float d, u32 key, u32 seed, u32 elt_idx, int g) {
-  if (ROUNDING == NVFP4_ROUND_SR_HW) return e2m1x4_rs(a, b, c, d, sr_hw_word(key, g));
+__device__ __forceinline__ u32 round8(float (&y)[8], u32 key, u32 seed, u32 elt_idx, int h) {
+  if (ROUNDING == NVFP4_ROUND_SR_HW)
+    return e2m1x4_rs(y[0], y[1], y[2], y[3], sr_hw_word(key, 2 * h)) | (e2m1x4_rs(y[4], y[5], y[6], y[7], sr_hw_word(key, 2 * h + 1)) << 16);
   if (ROUNDING == NVFP4_ROUND_SR_DITHER || ROUNDING == NVFP4_ROUND_SR_DITHER_K) {
-    const u32 i = 4u * (u32)g;
-    const u32 h0 = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(key + i) : hash32(seed ^ (elt_idx + i) * 0x9E3779B9u);
-    const u32 h1 = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(key + i + 2u) : hash32(seed ^ (elt_idx + i + 2u) * 0x9E3779B9u);
-    a = sr_dither(a, h0); b = sr_dither(b, (h0 >> 10) | (h0 << 22));
-    c = sr_dither(c, h1); d = sr_dither(d, (h1 >> 10) | (h1 << 22));
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const u32 i = 8u * (u32)h + (u32)j;
+      const u32 hh = (ROUNDING == NVFP4_ROUND_SR_DITHER) ? hash32(key + i) : hash32(seed ^ (elt_idx + i) * 0x9E3779B9u);
+      y[j] = sr_dither(y[j], hh);
+      y[j + 1] = sr_dither(y[j + 1], (hh >> 10) | (hh << 22));
+    }
   }
-  return e2m1x2_rn(a, b) | (e2m1x2_rn(c, d) << 8);
+  return e2m1x8_rn(y);
 }
 
 // Quantize one block of 16 values that share a scale.
@@ -219,18 +227,16 @@ __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const 
   const u32 key = block_key<ROUNDING>(seed, blk_idx);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(kf.y, kf.y), K = f2_pack(kf.x, kf.x);
-  u32 w[2] = {0u, 0u};
+  u32 w[2];
 #pragma unroll
-  for (int g = 0; g < 4; g++) {
-    u64 r0, r1;
-    if (ROUNDING == NVFP4_ROUND_NEAREST) {
-      r0 = f2_ndiv(f2_ndiv(P[2 * g], G, NRG), B, K);
-      r1 = f2_ndiv(f2_ndiv(P[2 * g + 1], G, NRG), B, K);
-    } else {
-      r0 = f2_mul(P[2 * g], K);
-      r1 = f2_mul(P[2 * g + 1], K);
+  for (int h = 0; h < 2; h++) {
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[4 * h + j], G, NRG), B, K) : f2_mul(P[4 * h + j], K);
+      y[2 * j] = f2_lo(r); y[2 * j + 1] = f2_hi(r);
     }
-    w[g >> 1] |= round4<ROUNDING>(f2_lo(r0), f2_hi(r0), f2_lo(r1), f2_hi(r1), key, seed, elt_idx, g) << ((g & 1) * 16);
+    w[h] = round8<ROUNDING>(y, key, seed, elt_idx, h);
   }
   return make_uint2(w[0], w[1]);
 }
@@ -241,24 +247,27 @@ __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const 
 template <int ROUNDING>
 __device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const TensorScale& ts, u32 seed, u32 blk0, u32 blk1,
                                                 uint2& o0, uint2& o1, u32& sb0, u32& sb1) {
-  float m0 = 0.f, m1 = 0.f;
+  float m0 = absmax3(f2_lo(P[0]), f2_lo(P[1]), f2_lo(P[2])), m1 = absmax3(f2_hi(P[0]), f2_hi(P[1]), f2_hi(P[2]));
 #pragma unroll
-  for (int i = 0; i < 16; i++) { m0 = fmaxf(m0, fabsf(f2_lo(P[i]))); m1 = fmaxf(m1, fabsf(f2_hi(P[i]))); }
+  for (int i = 3; i < 15; i += 2) { m0 = absmax3(m0, f2_lo(P[i]), f2_lo(P[i + 1])); m1 = absmax3(m1, f2_hi(P[i]), f2_hi(P[i + 1])); }
+  m0 = absmax3(m0, f2_lo(P[15]), m0); m1 = absmax3(m1, f2_hi(P[15]), m1);
   sb0 = block_scale_byte(m0, ts);
   sb1 = block_scale_byte(m1, ts);
   const float2 k0 = ts.lut[sb0], k1 = ts.lut[sb1];
   const u32 key0 = block_key<ROUNDING>(seed, blk0), key1 = block_key<ROUNDING>(seed, blk1);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(k0.y, k1.y), K = f2_pack(k0.x, k1.x);
-  u32 w0[2] = {0u, 0u}, w1[2] = {0u, 0u};
+  u32 w0[2], w1[2];
 #pragma unroll
-  for (int g = 0; g < 4; g++) {
-    u64 r[4];
+  for (int h = 0; h < 2; h++) {
+    float y0[8], y1[8];
 #pragma unroll
-    for (int j = 0; j < 4; j++)
-      r[j] = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[4 * g + j], G, NRG), B, K) : f2_mul(P[4 * g + j], K);
-    w0[g >> 1] |= round4<ROUNDING>(f2_lo(r[0]), f2_lo(r[1]), f2_lo(r[2]), f2_lo(r[3]), key0, seed, blk0 * 16u, g) << ((g & 1) * 16);
-    w1[g >> 1] |= round4<ROUNDING>(f2_hi(r[0]), f2_hi(r[1]), f2_hi(r[2]), f2_hi(r[3]), key1, seed, blk1 * 16u, g) << ((g & 1) * 16);
+    for (int j = 0; j < 8; j++) {
+      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[8 * h + j], G, NRG), B, K) : f2_mul(P[8 * h + j], K);
+      y0[j] = f2_lo(r); y1[j] = f2_hi(r);
+    }
+    w0[h] = round8<ROUNDING>(y0, key0, seed, blk0 * 16u, h);
+    w1[h] = round8<ROUNDING>(y1, key1, seed, blk1 * 16u, h);
   }
   o0 = make_uint2(w0[0], w0[1]);
   o1 = make_uint2(w1[0], w1[1]);

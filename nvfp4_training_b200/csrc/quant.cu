@@ -103,10 +103,10 @@ __global__ void __launch_bounds__(256, 4) quant_rows_kernel(const __nv_bfloat16*
     if (rn < R && sn * 32 + lane < nblk) nxt = load_block<WIDE>(x + (long long)rn * ldx + (sn * 32 + lane) * 16);
     const int blk = seg * 32 + lane;
     if (blk < nblk) {
-      const u32 sb = block_scale_byte(block_absmax(cur), ts);
       u64 P[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) P[i] = f2_from_bf16x2(cur.w[i]);
+      const u32 sb = block_scale_byte(absmax16(P), ts);
       const long long b = (long long)r * nblk + blk;
       codes[b] = quant_block16<ROUNDING>(P, sb, ts, seed, (u32)b, (u32)(b * 16));
       scales[linear ? b : sw_off(r, blk, nblk >> 2)] = (unsigned char)sb;
@@ -206,10 +206,13 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
   const u32 sb = block_scale_byte(bmax, ts);
   const float2 kf = ts.lut[sb];
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs), B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
-  const u64 q01 = f2_ndiv(f2_ndiv(f2_pack(v[0], v[1]), G, NRG), B, NRB), q23 = f2_ndiv(f2_ndiv(f2_pack(v[2], v[3]), G, NRG), B, NRB);
-  const u64 q45 = f2_ndiv(f2_ndiv(f2_pack(v[4], v[5]), G, NRG), B, NRB), q67 = f2_ndiv(f2_ndiv(f2_pack(v[6], v[7]), G, NRG), B, NRB);
-  const u32 word = round4<NVFP4_ROUND_NEAREST>(f2_lo(q01), f2_hi(q01), f2_lo(q23), f2_hi(q23), 0u, 0u, 0u, 0) |
-                   (round4<NVFP4_ROUND_NEAREST>(f2_lo(q45), f2_hi(q45), f2_lo(q67), f2_hi(q67), 0u, 0u, 0u, 1) << 16);
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) {
+    const u64 r = f2_ndiv(f2_ndiv(f2_pack(v[i], v[i + 1]), G, NRG), B, NRB);
+    y[i] = f2_lo(r); y[i + 1] = f2_hi(r);
+  }
+  const u32 word = e2m1x8_rn(y);
   if (q) {
     q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;
     if (!(lane & 1)) s[linear ? (long long)(bn * 16 + r) * kb + bk : sw_off(bn * 16 + r, bk, kb >> 2)] = (unsigned char)sb;

@@ -48,15 +48,27 @@ __device__ __forceinline__ bool consumers_all(bool ok) {
 }
 __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// Write the staged transposed-operand outputs of tile (mt, ct): consumer thread `ctid` moves 16
-// bytes of codes (a quarter of one column's 64-byte run), the first 64 threads 8 scale bytes each.
-__device__ __forceinline__ void drain_cols(const TileParams& p, const u32* sc, const unsigned char* ss, int mt, int ct, int ctid) {
+// Walks the tiles of one CTA in (token tile, column tile) coordinates without a division per tile.
+struct TileWalk {
+  int mt, ct, dq, dr, nct, nmt;
+  __device__ __forceinline__ TileWalk(int M, int C) {
+    nct = C / kTileCol; nmt = M / kTileTok;
+    mt = (int)blockIdx.x / nct; ct = (int)blockIdx.x - mt * nct;
+    dq = (int)gridDim.x / nct; dr = (int)gridDim.x - dq * nct;
+  }
+  __device__ __forceinline__ bool valid() const { return mt < nmt; }
+  __device__ __forceinline__ void next() { mt += dq; ct += dr; if (ct >= nct) { ct -= nct; mt++; } }
+};
+
+// Write the staged transposed-operand outputs of tile (mt, ct): every consumer thread moves 16
+// bytes of codes (a quarter of one column's 64-byte run, `code_off` = its offset inside the tile's
+// output), the first 64 threads 8 scale bytes each.
+__device__ __forceinline__ void drain_cols(const TileParams& p, const u32* src, const unsigned char* ss, int mt, int ct,
+                                           int ctid, long long code_off) {
   const int nmb = p.M >> 4;
-  const int cl = ctid >> 2, q = ctid & 3;
-  const u32* src = sc + (cl & 1) * (32 * 17 + 1) + (cl >> 1) * 17 + q * 4;
   const uint4 v = make_uint4(src[0], src[1], src[2], src[3]);
   const long long c0 = (long long)ct * kTileCol;
-  *reinterpret_cast<uint4*>(p.codes_c + ((c0 + cl) * nmb + mt * (kTileTok / 16)) * 8 + q * 16) = v;
+  *reinterpret_cast<uint4*>(p.codes_c + (c0 * nmb + mt * (kTileTok / 16)) * 8 + code_off) = v;
   if (ctid < 64) {
     const uint2 sv = *reinterpret_cast<const uint2*>(ss + ctid * 8);
     long long off;
@@ -101,21 +113,17 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   if (COLS) ts_c = make_tensor_scale<ROUNDING>(amax, 4.f, lut_c, first ? p.gs_c_out : nullptr, 0.25f);
   __syncthreads();
 
-  const int nct = p.C / kTileCol;
-  const int ntiles = (p.M / kTileTok) * nct;
-
   if (warp == 0) {
     // ---- producer
     u32 stage = 0, phase = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    for (TileWalk tw(p.M, p.C); tw.valid(); tw.next()) {
       if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag))) {
         if (lane == 0) atomicCAS(&g_quant_status, 0, 1);
         break;
       }
       if (elect_one()) {
-        const int mt = t / nct, ct = t - mt * nct;
         mbar_arrive_expect_tx(full0 + 8 * stage, kTileBytes);
-        tma_load_2d(tiles0 + stage * kTileBytes, &map, ct * kTileCol, mt * kTileTok, full0 + 8 * stage);
+        tma_load_2d(tiles0 + stage * kTileBytes, &map, tw.ct * kTileCol, tw.mt * kTileTok, full0 + 8 * stage);
       }
       __syncwarp();
       if (++stage == kTileStages) { stage = 0; phase ^= 1u; }
@@ -134,18 +142,27 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   }
   const int nblk = p.C >> 4;                     // 16-column blocks per row
   const int nmb = p.M >> 4;                      // 16-token blocks per column
+  // per-thread constants of the transposed path: swizzled shared-memory offsets of the thread's word
+  // column for the 8 values of (token & 7), its slots in the staging buffers and in a tile's output
+  u32 xoff[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) xoff[k] = (u32)(cw * 2048 + ((((lane >> 2) ^ k) << 4) | ((lane & 3) << 2)));
+  const int dcl = ctid >> 2, dq4 = ctid & 3;                       // drain: column of the tile, quarter of its run
+  const int drain_src = (dcl & 1) * (32 * 17 + 1) + (dcl >> 1) * 17 + dq4 * 4;
+  const long long drain_dst = (long long)dcl * nmb * 8 + dq4 * 16;
   u32 stage = 0, phase = 0;
-  int prev = -1, buf = 0;                        // tile whose transposed outputs wait in stage_*[buf ^ 1]
-  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const int mt = t / nct, ct = t - mt * nct;
+  int prev_mt = -1, prev_ct = 0, buf = 0;        // tile whose transposed outputs wait in stage_*[buf ^ 1]
+  for (TileWalk tw(p.M, p.C); tw.valid(); tw.next()) {
+    const int mt = tw.mt, ct = tw.ct;
     // one consumer-wide barrier per tile: it makes the abort decision uniform and orders the
-    // staging buffers (everyone has staged tile `prev`, everyone has drained the tile before it)
+    // staging buffers (everyone has staged the previous tile, everyone has drained the one before it)
     if (!consumers_all(mbar_wait(full0 + 8 * stage, phase, abort_flag))) {
       if (threadIdx.x == 32) atomicCAS(&g_quant_status, 0, 2);
-      prev = -1;
+      prev_mt = -1;
       break;
     }
-    if (COLS && prev >= 0) drain_cols(p, stage_codes[buf ^ 1], stage_scales[buf ^ 1], prev / nct, prev % nct, ctid);
+    if (COLS && prev_mt >= 0)
+      drain_cols(p, stage_codes[buf ^ 1] + drain_src, stage_scales[buf ^ 1], prev_mt, prev_ct, ctid, drain_dst);
     const u32 tile = tiles0 + stage * kTileBytes;
 
     if (COLS) {
@@ -155,10 +172,9 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
 #pragma unroll
       for (int i = 0; i < 16; i++) {
         u32 w;
-        const u32 addr = tile + (u32)((cw * 16 + i) * 128) + (u32)((((lane >> 2) ^ (i & 7)) << 4) | ((lane & 3) << 2));
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(addr));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(tile + xoff[i & 7] + (u32)(i * 128)));
         const u32 f = ((p.signs >> i) & 1u) << 31;           // token i is negated when bit i of signs is set
-        P[i] = f2_pack(__uint_as_float((w << 16) ^ f), __uint_as_float((w & 0xFFFF0000u) ^ f));
+        P[i] = f2_pack(__uint_as_float((w << 16) + f), __uint_as_float((w & 0xFFFF0000u) ^ f));
       }
 #pragma unroll
       for (int h = 1; h < 16; h <<= 1)
@@ -179,7 +195,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
         const int o = (cw >> 2) * 256 + (cl & 31) * 8 + (cl >> 5) * 4 + (cw & 3);
         ss[o] = (unsigned char)sb0; ss[o + 8] = (unsigned char)sb1;
       }
-      prev = t; buf ^= 1;
+      prev_mt = mt; prev_ct = ct; buf ^= 1;
     }
 
     if (ROWS) {
@@ -193,10 +209,10 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
         Block32 cur;
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[0]), "=r"(cur.w[1]), "=r"(cur.w[2]), "=r"(cur.w[3]) : "r"(rowaddr + (ch << 4)));
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[4]), "=r"(cur.w[5]), "=r"(cur.w[6]), "=r"(cur.w[7]) : "r"(rowaddr + ((ch ^ 1u) << 4)));
-        const u32 sb = block_scale_byte(block_absmax(cur), ts_r);
         u64 P[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) P[i] = f2_from_bf16x2(cur.w[i]);
+        const u32 sb = block_scale_byte(absmax16(P), ts_r);
         const long long r = (long long)mt * kTileTok + tok;
         const int cb = ct * (kTileCol / 16) + blk;
         const long long b = r * nblk + cb;
@@ -209,9 +225,9 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
     if (lane == 0) mbar_arrive(empty0 + 8 * stage);
     if (++stage == kTileStages) { stage = 0; phase ^= 1u; }
   }
-  if (COLS && prev >= 0) {
+  if (COLS && prev_mt >= 0) {
     consumers_sync();
-    drain_cols(p, stage_codes[buf ^ 1], stage_scales[buf ^ 1], prev / nct, prev % nct, ctid);
+    drain_cols(p, stage_codes[buf ^ 1] + drain_src, stage_scales[buf ^ 1], prev_mt, prev_ct, ctid, drain_dst);
   }
   if (*abort_flag) settle_copies();
 }

@@ -44,27 +44,46 @@ class WeightCache:
         return self
 
 
-def linear_fwd(x, qw):
+def _tileable(t):
+    """Shapes the one-read tile quantizer takes (else the row and column kernels run separately)."""
+    return t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0
+
+
+def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS):
     """fprop of llm-1b/model.py:46-53 with W already quantized: returns (y bf16 [T, N], amax(x)).
-    amax(x) is handed back so the backward pass does not recompute it (same value)."""
+    amax(x) is handed back so the backward pass does not recompute it (same value).  With
+    `keep_xt` the transposed RHT operand of x that wgrad needs (llm-1b/model.py:66) is produced in
+    the same pass over x and returned as a third value, so the backward pass neither re-reads nor
+    has to keep x."""
     am = nvq.amax(x.contiguous())
-    return nvq.mm(nvq.quant_rows(x, am=am), qw), am
+    if keep_xt and _tileable(x):
+        qx, qxt = nvq.quant_rows_cols_rht(x, signs, am=am)
+        return nvq.mm(qx, qw), am, qxt
+    y = nvq.mm(nvq.quant_rows(x, am=am), qw)
+    return (y, am, nvq.quant_cols_rht(x, signs, am=am)) if keep_xt else (y, am)
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None, overwrite=False):
+               sr_mode=None, overwrite=False, qxt=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
     returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
-    rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding."""
+    rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding.
+    `qxt`: the transposed operand of x from `linear_fwd(..., keep_xt=True)`; x may then be None."""
     gy = gy.contiguous()
     ag = nvq.amax(gy)
+    if _tileable(gy):
+        # both operands of gy from one pass over it
+        qg, qgt = nvq.quant_rows_cols_rht(gy, signs, sr=True, seed=seed, seed_cols=seed_cols, am=ag, sr_mode=sr_mode)
+    else:
+        qg = nvq.quant_rows(gy, sr=True, seed=seed, am=ag, sr_mode=sr_mode)
+        qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag, sr_mode=sr_mode)
     # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
-    gx = nvq.mm(nvq.quant_rows(gy, sr=True, seed=seed, am=ag, sr_mode=sr_mode), qwt)
+    gx = nvq.mm(qg, qwt)
     # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
-    qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag, sr_mode=sr_mode)
-    qxt = nvq.quant_cols_rht(x, signs, am=am_x)
+    if qxt is None:
+        qxt = nvq.quant_cols_rht(x, signs, am=am_x)
     if gw_out is not None:
         gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite)
     else:
@@ -78,17 +97,20 @@ class FP4LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, lid, cache=None):
         qw = cache.q if cache is not None else nvq.quant_w2d(w, want=(True, False))[0]
-        y, am = linear_fwd(x, qw)
-        ctx.save_for_backward(x, w, am)
+        # the backward pass needs x only as the transposed RHT operand: keep that (0.56 byte per
+        # element) instead of x
+        y, am, qxt = linear_fwd(x, qw, keep_xt=True)
+        ctx.save_for_backward(w, am, qxt.d, qxt.s, qxt.gs)
         ctx.lid, ctx.cache = lid, cache
         return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, w, am = ctx.saved_tensors
+        w, am, xd, xs, xg = ctx.saved_tensors
         seed = sr_seed(ctx.lid)
         qwt = ctx.cache.qt if ctx.cache is not None else nvq.quant_w2d(w, want=(False, True))[1]
-        gx, gw = linear_bwd(x, am, gy, qwt, seed, seed ^ 0x5bd1e995, wgrad_dtype=LinCtx.wgrad_dtype)
+        gx, gw = linear_bwd(None, am, gy, qwt, seed, seed ^ 0x5bd1e995, wgrad_dtype=LinCtx.wgrad_dtype,
+                            qxt=nvq.Q(xd, xs, xg))
         return gx, gw, None, None
 
 

@@ -76,7 +76,7 @@ def allreduce_sum_(tensors, group=None):
 
 
 class _Proj:
-    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx")
+    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx", "qxt")
 
 
 def student_t(shape, gen, device, df=3):
@@ -155,7 +155,7 @@ class LinearStack:
 
     def _fwd_block(self, projs, keep=False):
         for p in projs:
-            y, p.am_x = linear_fwd(self.x_pool[p.name], p.q)
+            y, p.am_x, p.qxt = linear_fwd(self.x_pool[p.name], p.q, keep_xt=True, signs=_RHT_SIGNS)
             p.y = y if keep else None
 
     def _bwd_block(self, projs, keep=False, first=False):
@@ -163,8 +163,8 @@ class LinearStack:
         gradients need no clearing pass."""
         for p in reversed(projs):
             sd = self.seeds[p.lid]
-            gx, _ = linear_bwd(self.x_pool[p.name], p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
-                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first)
+            gx, _ = linear_bwd(None, p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
+                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt)
             p.gx = gx if keep else None
 
     def capture(self):
@@ -203,9 +203,9 @@ class LinearStack:
         torch.cuda.synchronize()
 
     def kernels_per_microbatch(self):
-        """Kernels of this library launched per microbatch: fwd amax + quant_rows + gemm;
-        bwd amax + quant_rows + gemm + 2 quant_cols_rht + gemm."""
-        return self.n_proj * (3 + 6)
+        """Kernels of this library launched per microbatch: fwd amax + tile quantizer + gemm;
+        bwd amax + tile quantizer + 2 gemm."""
+        return self.n_proj * (3 + 4)
 
     def microbatch(self, last, do_allreduce, first=False):
         """One forward + backward over all projections.  On the rank's last microbatch each block's
