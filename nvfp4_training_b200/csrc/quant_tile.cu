@@ -147,6 +147,16 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   u32 xoff[8];
 #pragma unroll
   for (int k = 0; k < 8; k++) xoff[k] = (u32)(cw * 2048 + ((((lane >> 2) ^ k) << 4) | ((lane & 3) << 2)));
+  const int thr_cblk = 2 * lane * nmb + cw;                        // transposed block index inside the tile's range
+  const int sc_off = lane * 17 + cw * 2;                           // staging slot of column 2*lane (codes)
+  const int ss_off = p.linear ? 2 * lane * 8 + cw
+                              : (cw >> 2) * 256 + ((2 * lane) & 31) * 8 + ((2 * lane) >> 5) * 4 + (cw & 3);
+  // row path: unit j = (token tok0 + 64*j, 16-column block rblk); all offsets are tile base + constant
+  const int tok0 = ctid >> 2, rblk = ctid & 3;
+  const u32 r_off0 = (u32)(tok0 * 128 + (((2 * rblk) ^ (tok0 & 7)) << 4));
+  const u32 r_off1 = (u32)(tok0 * 128 + ((((2 * rblk) ^ (tok0 & 7)) ^ 1) << 4));
+  const int thr_rblk = tok0 * nblk + rblk;
+  const int thr_rsc = p.linear ? thr_rblk : (tok0 & 31) * 16 + ((tok0 >> 5) & 3) * 4 + rblk;
   const int dcl = ctid >> 2, dq4 = ctid & 3;                       // drain: column of the tile, quarter of its run
   const int drain_src = (dcl & 1) * (32 * 17 + 1) + (dcl >> 1) * 17 + dq4 * 4;
   const long long drain_dst = (long long)dcl * nmb * 8 + dq4 * 16;
@@ -181,43 +191,34 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
 #pragma unroll
         for (int i = 0; i < 16; i++)
           if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
-      const long long b0 = ((long long)ct * kTileCol + 2 * lane) * nmb + mt * (kTileTok / 16) + cw, b1 = b0 + nmb;
+      const u32 b0 = (u32)((long long)ct * kTileCol * nmb + mt * (kTileTok / 16)) + (u32)thr_cblk, b1 = b0 + (u32)nmb;
       uint2 o0, o1; u32 sb0, sb1;
-      quant_block16x2<ROUNDING>(P, ts_c, seed_c, (u32)b0, (u32)b1, o0, o1, sb0, sb1);
-      u32* sc = stage_codes[buf];
-      sc[lane * 17 + cw * 2] = o0.x; sc[lane * 17 + cw * 2 + 1] = o0.y;                       // column 2*lane
-      sc[32 * 17 + 1 + lane * 17 + cw * 2] = o1.x; sc[32 * 17 + 1 + lane * 17 + cw * 2 + 1] = o1.y;   // column 2*lane+1
-      unsigned char* ss = stage_scales[buf];
-      const int cl = 2 * lane;
-      if (p.linear) {
-        ss[cl * 8 + cw] = (unsigned char)sb0; ss[cl * 8 + 8 + cw] = (unsigned char)sb1;
-      } else {
-        const int o = (cw >> 2) * 256 + (cl & 31) * 8 + (cl >> 5) * 4 + (cw & 3);
-        ss[o] = (unsigned char)sb0; ss[o + 8] = (unsigned char)sb1;
-      }
+      quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, o0, o1, sb0, sb1);
+      u32* sc = stage_codes[buf] + sc_off;
+      sc[0] = o0.x; sc[1] = o0.y;                                   // column 2*lane
+      sc[32 * 17 + 1] = o1.x; sc[32 * 17 + 2] = o1.y;               // column 2*lane+1
+      unsigned char* ss = stage_scales[buf] + ss_off;
+      ss[0] = (unsigned char)sb0; ss[8] = (unsigned char)sb1;
       prev_mt = mt; prev_ct = ct; buf ^= 1;
     }
 
     if (ROWS) {
       // thread = two (token, 16-column block) units; four neighbouring lanes cover one token's 128 bytes
+      const long long tile_b = (long long)mt * kTileTok * nblk + ct * (kTileCol / 16);
+      const long long tile_s = p.linear ? tile_b : ((long long)mt * (nblk >> 2) + ct) * 512;
 #pragma unroll
       for (int j = 0; j < 2; j++) {
-        const int u = ctid + 256 * j;
-        const int tok = u >> 2, blk = u & 3;
-        const u32 rowaddr = tile + (u32)(tok * 128);
-        const u32 ch = (u32)((2 * blk) ^ (tok & 7));
         Block32 cur;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[0]), "=r"(cur.w[1]), "=r"(cur.w[2]), "=r"(cur.w[3]) : "r"(rowaddr + (ch << 4)));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[4]), "=r"(cur.w[5]), "=r"(cur.w[6]), "=r"(cur.w[7]) : "r"(rowaddr + ((ch ^ 1u) << 4)));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[0]), "=r"(cur.w[1]), "=r"(cur.w[2]), "=r"(cur.w[3]) : "r"(tile + r_off0 + (u32)(j * 64 * 128)));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(cur.w[4]), "=r"(cur.w[5]), "=r"(cur.w[6]), "=r"(cur.w[7]) : "r"(tile + r_off1 + (u32)(j * 64 * 128)));
         u64 P[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) P[i] = f2_from_bf16x2(cur.w[i]);
         const u32 sb = block_scale_byte(absmax16(P), ts_r);
-        const long long r = (long long)mt * kTileTok + tok;
-        const int cb = ct * (kTileCol / 16) + blk;
-        const long long b = r * nblk + cb;
-        p.codes_r[b] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)(b * 16));
-        p.scales_r[p.linear ? b : sw_off(r, cb, nblk >> 2)] = (unsigned char)sb;
+        const long long b = tile_b + thr_rblk + (long long)j * 64 * nblk;
+        p.codes_r[b] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)b * 16u);
+        // 64 tokens further: same 512-byte scale chunk, 8 bytes on (swizzled) / 64 rows on (linear)
+        p.scales_r[tile_s + thr_rsc + (p.linear ? (long long)j * 64 * nblk : (long long)j * 8)] = (unsigned char)sb;
       }
     }
 

@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--fp32", action="store_true")
     ap.add_argument("--tile", type=int, default=0)
+    ap.add_argument("--sets", type=int, default=1)
     a = ap.parse_args()
     _lib.load().nvfp4_gemm_force_tile_n(a.tile)
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -49,30 +50,33 @@ def main():
         us = timed(lambda: nvq.mm(qa, qb, out_dtype=dt, out=c), a.iters)
         out.update(us=us, tflops=2.0 * a.M * a.N * a.K / us / 1e6)
     elif a.what == "quant":
-        x = torch.randn(a.M, a.N, generator=g, device="cuda").bfloat16()
-        am = nvq.amax(x)
+        # `--sets` input tensors taken in turn: with sets * M * N * 2 bytes well above the L2 size
+        # every launch reads its input from HBM
+        xs = [torch.randn(a.M, a.N, generator=g, device="cuda").bfloat16() for _ in range(a.sets)]
+        turn = [0]
+
+        def nxt():
+            turn[0] += 1
+            return xs[turn[0] % a.sets]
+        am = nvq.amax(xs[0])
         n = a.M * a.N
-        for name, fn, bpe in (("amax", lambda: nvq.amax(x), 2.0),
-                              ("quant_rows_rn", lambda: nvq.quant_rows(x, am=am), 2.5625),
-                              ("quant_rows_sr", lambda: nvq.quant_rows(x, sr=True, seed=1, am=am), 2.5625),
-                              ("quant_cols_rht_rn", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, am=am), 2.5625),
-                              ("quant_cols_rht_sr", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, am=am), 2.5625)):
-            us = timed(fn, a.iters)
-            out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
-        nvq.SR_MODE = _lib.ROUND_SR_HW
-        for name, fn in (("quant_rows_sr_hw", lambda: nvq.quant_rows(x, sr=True, seed=1, am=am)),
-                         ("quant_cols_rht_sr_hw", lambda: nvq.quant_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, am=am))):
-            us = timed(fn, a.iters)
-            out[name] = {"us": us, "gbs": n * 2.5625 / us / 1e3}
-        for name, fn, bpe in (("tile_rows+cols_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am), 3.125),
-                              ("tile_cols_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am, want=(False, True)), 2.5625),
-                              ("tile_rows_sr_hw", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am, want=(True, False)), 2.5625)):
-            us = timed(fn, a.iters)
-            out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
-        nvq.SR_MODE = _lib.ROUND_SR_DITHER
-        for name, fn, bpe in (("tile_rows+cols_rn", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, am=am), 3.125),
-                              ("tile_cols_rn", lambda: nvq.quant_rows_cols_rht(x, _RHT_SIGNS, am=am, want=(False, True)), 2.5625)):
-            us = timed(fn, a.iters)
+        HW, S = _lib.ROUND_SR_HW, _RHT_SIGNS
+        cases = (
+            ("amax", lambda x: nvq.amax(x), 2.0),
+            ("quant_rows_rn", lambda x: nvq.quant_rows(x, am=am), 2.5625),
+            ("quant_rows_sr", lambda x: nvq.quant_rows(x, sr=True, seed=1, am=am), 2.5625),
+            ("quant_cols_rht_rn", lambda x: nvq.quant_cols_rht(x, S, am=am), 2.5625),
+            ("quant_cols_rht_sr", lambda x: nvq.quant_cols_rht(x, S, sr=True, seed=1, am=am), 2.5625),
+            ("quant_rows_sr_hw", lambda x: nvq.quant_rows(x, sr=True, seed=1, am=am, sr_mode=HW), 2.5625),
+            ("quant_cols_rht_sr_hw", lambda x: nvq.quant_cols_rht(x, S, sr=True, seed=1, am=am, sr_mode=HW), 2.5625),
+            ("tile_rows+cols_sr_hw", lambda x: nvq.quant_rows_cols_rht(x, S, sr=True, seed=1, seed_cols=2, am=am, sr_mode=HW), 3.125),
+            ("tile_cols_sr_hw", lambda x: nvq.quant_rows_cols_rht(x, S, sr=True, seed=1, seed_cols=2, am=am, sr_mode=HW, want=(False, True)), 2.5625),
+            ("tile_rows_sr_hw", lambda x: nvq.quant_rows_cols_rht(x, S, sr=True, seed=1, seed_cols=2, am=am, sr_mode=HW, want=(True, False)), 2.5625),
+            ("tile_rows+cols_rn", lambda x: nvq.quant_rows_cols_rht(x, S, am=am), 3.125),
+            ("tile_cols_rn", lambda x: nvq.quant_rows_cols_rht(x, S, am=am, want=(False, True)), 2.5625),
+        )
+        for name, fn, bpe in cases:
+            us = timed(lambda: fn(nxt()), a.iters)
             out[name] = {"us": us, "gbs": n * bpe / us / 1e3}
         w = torch.randn(a.N, a.K, generator=g, device="cuda").bfloat16()
         us = timed(lambda: nvq.quant_w2d(w), a.iters)
