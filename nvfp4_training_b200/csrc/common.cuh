@@ -141,7 +141,7 @@ struct TensorScale {
   float gs;      // max(k*amax/2688, 1e-30)/pre: the FP32 tensor scale the values are divided by
   float nrgs;    // -RN(1/gs)
   float inv_gs;  // pre*2688/(k*amax), 0 for an all-zero tensor: the reference kernels' scale (llm-1b/nvq.cu:101)
-  const float2* lut;   // shared memory, 128 entries indexed by the scale byte, see make_tensor_scale
+  u32 lut;       // shared-memory address of 128 float2 entries indexed by the scale byte, see make_tensor_scale
 };
 
 constexpr int kLutFloats = 256;
@@ -160,7 +160,7 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
   t.gs = __fdiv_rn(gs, pre);
   t.nrgs = -__frcp_rn(t.gs);
   t.inv_gs = am > 0.f ? __fmul_rn(__fdiv_rn(kFp4E4m3, am), pre) : 0.f;
-  t.lut = reinterpret_cast<const float2*>(lut);
+  t.lut = (u32)__cvta_generic_to_shared(lut);
   if (threadIdx.x < 128) {
     const float bsf = e4m3_dec(threadIdx.x);
     // entry 0 (underflowed block): -0 / +0 make every scaled value a zero with the input's sign
@@ -171,6 +171,13 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
   }
   __syncthreads();
   return t;
+}
+
+// table entry of a scale byte (explicit shared-memory load: a generic one takes the long path)
+__device__ __forceinline__ float2 lut_entry(const TensorScale& ts, u32 sb) {
+  float2 r;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(r.x), "=f"(r.y) : "r"(ts.lut + sb * 8u));
+  return r;
 }
 
 // Scale byte of a block:  e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
@@ -223,7 +230,7 @@ __device__ __forceinline__ u32 round8(float (&y)[8], u32 key, u32 seed, u32 elt_
 template <int ROUNDING>
 __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const TensorScale& ts, u32 seed,
                                                u32 blk_idx, u32 elt_idx) {
-  const float2 kf = ts.lut[sb];
+  const float2 kf = lut_entry(ts, sb);
   const u32 key = block_key<ROUNDING>(seed, blk_idx);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(kf.y, kf.y), K = f2_pack(kf.x, kf.x);
@@ -253,7 +260,7 @@ __device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const Tensor
   m0 = absmax3(m0, f2_lo(P[15]), m0); m1 = absmax3(m1, f2_hi(P[15]), m1);
   sb0 = block_scale_byte(m0, ts);
   sb1 = block_scale_byte(m1, ts);
-  const float2 k0 = ts.lut[sb0], k1 = ts.lut[sb1];
+  const float2 k0 = lut_entry(ts, sb0), k1 = lut_entry(ts, sb1);
   const u32 key0 = block_key<ROUNDING>(seed, blk0), key1 = block_key<ROUNDING>(seed, blk1);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(k0.y, k1.y), K = f2_pack(k0.x, k1.x);

@@ -579,6 +579,22 @@ __device__ __forceinline__ void staged_store(const u32 (&r)[NCOLS], float alpha,
 #define NVFP4_PROF_ADD(slot)
 #endif
 
+// Work item -> (row tile, column tile, K slice) of the pair kernel.  Tiles are walked in bands of
+// kBand tile columns, row by row inside a band: the clusters of one wave then cover a roughly square
+// patch of C, so every A and B tile they load is shared by about kBand clusters (one HBM read, the
+// rest L2 hits) instead of each cluster streaming its own rows of A.
+constexpr int kBand = 8;
+__device__ __forceinline__ void decode_tile(int w, int tiles_m, int tiles_n, int& mt, int& nt, int& z) {
+  const int per_z = tiles_m * tiles_n;
+  z = w / per_z;
+  const int r = w - z * per_z;
+  const int band = r / (kBand * tiles_m);
+  const int r2 = r - band * kBand * tiles_m;
+  const int width = min(kBand, tiles_n - band * kBand);
+  mt = r2 / width;
+  nt = band * kBand + (r2 - mt * width);
+}
+
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -640,10 +656,8 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #endif
     NVFP4_PROF_T0();
     for (int w = cid; w < num_work && ok; w += ncl) {
-      const int mt = w % tiles_m;
-      const int rest = w / tiles_m;
-      const int nt = rest % tiles_n;
-      const int z = rest / tiles_n;
+      int mt, nt, z;
+      decode_tile(w, tiles_m, tiles_n, mt, nt, z);
       const int kt0 = z * p.ktiles_per_split;
       const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
       const int ya = mt * 256 + (int)rank * 128, yb = nt * BN + (int)rank * (BN / 2);
@@ -684,8 +698,8 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #endif
       NVFP4_PROF_T0();
       for (int w = cid; w < num_work && ok; w += ncl, tile++) {
-        const int z = w / (tiles_m * tiles_n);
-        const int nt = (w / tiles_m) % tiles_n;
+        int mt, nt, z;
+        decode_tile(w, tiles_m, tiles_n, mt, nt, z);
         const int kt0 = z * p.ktiles_per_split;
         const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
         const u32 acc = tile & 1u;
@@ -774,8 +788,8 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #endif
     NVFP4_PROF_T0();
     for (int w = cid; w < num_work && ok; w += ncl, tile++) {
-      const int mt = w % tiles_m;
-      const int nt = (w / tiles_m) % tiles_n;
+      int mt, nt, zz;
+      decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
       const u32 acc = tile & 1u;
       {
         const u32 bar = BN == 256 ? accf0 : accf0 + 8 * acc;

@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
 #pragma unroll
   for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
   const u32 sb = block_scale_byte(bmax, ts);
-  const float2 kf = ts.lut[sb];
+  const float2 kf = lut_entry(ts, sb);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs), B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
   float y[8];
 #pragma unroll

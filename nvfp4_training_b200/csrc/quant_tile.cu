@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
     // ---- producer
     u32 stage = 0, phase = 0;
     for (TileWalk tw(p.M, p.C); tw.valid(); tw.next()) {
-      if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(empty0 + 8 * stage, phase ^ 1u, abort_flag))) {
         if (lane == 0) atomicCAS(&g_quant_status, 0, 1);
         break;
       }
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
     const int mt = tw.mt, ct = tw.ct;
     // one consumer-wide barrier per tile: it makes the abort decision uniform and orders the
     // staging buffers (everyone has staged the previous tile, everyone has drained the one before it)
-    if (!consumers_all(mbar_wait(full0 + 8 * stage, phase, abort_flag))) {
+    if (!consumers_all(mbar_wait_parked(full0 + 8 * stage, phase, abort_flag))) {
       if (threadIdx.x == 32) atomicCAS(&g_quant_status, 0, 2);
       prev_mt = -1;
       break;

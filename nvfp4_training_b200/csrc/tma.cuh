@@ -46,6 +46,25 @@ __device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abo
   }
 }
 
+// Bounded wait for warps that can afford to sleep: the try_wait carries a suspend-time hint, so a
+// waiting warp polls rarely instead of competing for issue slots with the warps that have work.
+__device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile int* abort_flag) {
+  const u64 t0 = globaltimer_ns();
+  for (u32 it = 1;; ++it) {
+    u32 ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
+    if (ok) return true;
+    if ((it & 15u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(u32 dst, const CUtensorMap* map, int x, int y, u32 bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
