@@ -384,7 +384,9 @@ def run_ours(args):
             "frac_fp4_nominal_9000": flops / (ms * 1e-3) / world / 1e12 / 9000.0,
             "e2e": {"value": GLOBAL_TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": n_micro * mb * cfg.d * 2, "d2h_bytes_per_step": 4096, "steps": e2e_steps},
-            "gpu_launches": args.steps * (n_micro * (cfg.layers * 4 + 1) * 9 + (cfg.layers * 4 + 1) * 2),
+            # this library's kernels in the timed region: per microbatch and projection amax + tile quantizer +
+            # GEMM (forward) and amax + tile quantizer + 2 GEMMs (backward); per step and weight amax + quant_w2d
+            "gpu_launches": args.steps * (n_micro * stack.kernels_per_microbatch() + stack.n_proj * 2),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "detail": detail,
         }
         print(json.dumps(line))

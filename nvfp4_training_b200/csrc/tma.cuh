@@ -49,7 +49,7 @@ __device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abo
 // Bounded wait for warps that can afford to sleep: the try_wait carries a suspend-time hint, so a
 // waiting warp polls rarely instead of competing for issue slots with the warps that have work.
 __device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile int* abort_flag) {
-  const u64 t0 = globaltimer_ns();
+  u64 t0 = 0;
   for (u32 it = 1;; ++it) {
     u32 ok;
     asm volatile(
@@ -60,7 +60,9 @@ __device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile i
     if (ok) return true;
     if ((it & 15u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      const u64 now = globaltimer_ns();      // the clock is read only once a wait has lasted a while
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
     }
   }
 }
