@@ -328,6 +328,7 @@ def run_ours(args):
     host_x = torch.randn(mb, cfg.d).bfloat16().pin_memory()
     host_out = torch.empty(1024, dtype=torch.float32).pin_memory()
     last = stack.blocks[-1][-1]
+    launches_per_step = n_micro * stack.kernels_per_microbatch() + stack.n_proj * 2
 
     def e2e_step():
         stack.refresh_weights()
@@ -386,7 +387,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": n_micro * mb * cfg.d * 2, "d2h_bytes_per_step": 4096, "steps": e2e_steps},
             # this library's kernels in the timed region: per microbatch and projection amax + tile quantizer +
             # GEMM (forward) and amax + tile quantizer + 2 GEMMs (backward); per step and weight amax + quant_w2d
-            "gpu_launches": args.steps * (n_micro * stack.kernels_per_microbatch() + stack.n_proj * 2),
+            "gpu_launches": args.steps * launches_per_step,
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "detail": detail,
         }
         print(json.dumps(line))
