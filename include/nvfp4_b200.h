@@ -126,7 +126,7 @@ int nvfp4_quant_tile_status(int* out, int reset);
  * code values.  Either output pair may be null to skip it.
  * Replaces kernel `quant_w2d` (llm-1b/nvq.cu:162-196 bf16; llm-1b/fp4k.cu:121-158 fp32) and
  * launchers `nvq.quant_w2d` (llm-1b/nvq.py:73-87), `fp4ops.quant_w2d` (llm-1b/fp4ops.py:52-61).
- * Requires N % 16 == 0, K % 16 == 0; SWIZZLED also N % 128 == 0, K % 128 == 0.
+ * Requires N % 16 == 0, K % 16 == 0; SWIZZLED also N % 128 == 0, K % 128 == 0; w 16-byte, q / qt / st 4-byte aligned.
  */
 int nvfp4_quant_w2d(const void* w, int w_dtype, int N, int K, void* q, void* s, void* qt, void* st,
                     int scale_layout, const float* amax, float* gs_out, void* stream);

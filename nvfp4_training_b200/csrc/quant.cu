@@ -174,61 +174,111 @@ __global__ void __launch_bounds__(256, 2) quant_cols_rht_kernel(const __nv_bfloa
 }
 
 // ------------------------------------------------------------------------------------------ 16x16 weights
-// One warp per 16x16 block: lane = (row, 8-column half).  Block max by warp shuffles, codes for W
-// written as one word per lane, codes for W^T gathered with shuffles (lane = (k row, 8-row half)).
+// Persistent CTAs; one warp per group of four 16x16 blocks that are neighbours along N (same K
+// block): lane = (row, 8-column half) of each block, four independent 16-byte loads in flight per
+// lane.  Block max by warp shuffles, codes for W written as one word per lane and block, codes for
+// W^T gathered with shuffles (lane = (k row, 8-row half)) and, after one exchange inside each lane
+// pair, stored as 16 contiguous bytes per lane: a k row's 32 bytes for the four blocks leave together.
 template <typename T>
 __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w, u32* __restrict__ q,
                                                          unsigned char* __restrict__ s, u32* __restrict__ qt,
                                                          unsigned char* __restrict__ st, const float* __restrict__ amax,
                                                          int N, int K, int linear, float* __restrict__ gs_out) {
   const int lane = threadIdx.x & 31;
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nb = N >> 4, kb = K >> 4;
+  const int ngrp = (nb + 3) >> 2;
   __shared__ __align__(8) float lut[kLutFloats];
   const TensorScale ts = make_tensor_scale<NVFP4_ROUND_NEAREST>(__ldg(amax), 1.f, lut,
                                                                (blockIdx.x == 0 && threadIdx.x == 0) ? gs_out : nullptr);
-  if (warp >= (long long)nb * kb) return;
-  const int bn = (int)(warp / kb), bk = (int)(warp - (long long)bn * kb);
+  const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const int r = lane >> 1, c0 = (lane & 1) * 8;
-  const T* src = w + (long long)(bn * 16 + r) * K + bk * 16 + c0;
-  float v[8];
-  if constexpr (sizeof(T) == 2) {
-    unpack8(ldg128(src), v);
-  } else {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-  float bmax = 0.f;
+  const bool wide_t = !(N & 31) && !(reinterpret_cast<uintptr_t>(qt) & 15u);   // 16-byte stores of W^T codes possible
+  const long long nitems = (long long)ngrp * kb;
+  const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < nitems; item += wstride) {
+    // consecutive warps walk K: the loads of a CTA are contiguous along each row
+    const int grp = (int)(item / kb), bk = (int)(item - (long long)grp * kb);
+    float v[4][8];
 #pragma unroll
-  for (int i = 0; i < 8; i++) bmax = fmaxf(bmax, fabsf(v[i]));
+    for (int j = 0; j < 4; j++) {
+      const int bn = grp * 4 + j;
+      if (bn < nb) {
+        const T* src = w + (long long)(bn * 16 + r) * K + bk * 16 + c0;
+        if constexpr (sizeof(T) == 2) {
+          unpack8(ldg128(src), v[j]);
+        } else {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+          v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w; v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+        }
+      } else {
 #pragma unroll
-  for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
-  const u32 sb = block_scale_byte(bmax, ts);
-  const float2 kf = lut_entry(ts, sb);
-  const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs), B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
-  float y[8];
+        for (int i = 0; i < 8; i++) v[j][i] = 0.f;
+      }
+    }
+    u32 wt[4], sbs[4];
 #pragma unroll
-  for (int i = 0; i < 8; i += 2) {
-    const u64 r = f2_ndiv(f2_ndiv(f2_pack(v[i], v[i + 1]), G, NRG), B, NRB);
-    y[i] = f2_lo(r); y[i + 1] = f2_hi(r);
-  }
-  const u32 word = e2m1x8_rn(y);
-  if (q) {
-    q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;
-    if (!(lane & 1)) s[linear ? (long long)(bn * 16 + r) * kb + bk : sw_off(bn * 16 + r, bk, kb >> 2)] = (unsigned char)sb;
-  }
-  // transposed block: this lane builds k-row kk = lane>>1, n values (lane&1)*8 .. +7
-  const int kk = lane >> 1;
-  u32 wt = 0u;
+    for (int j = 0; j < 4; j++) {
+      const int bn = grp * 4 + j;
+      float bmax = absmax3(v[j][0], v[j][1], v[j][2]);
+      bmax = absmax3(bmax, v[j][3], v[j][4]);
+      bmax = absmax3(bmax, v[j][5], v[j][6]);
+      bmax = absmax3(bmax, v[j][7], bmax);
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int row = c0 + i;
-    const u32 ww = __shfl_sync(0xffffffffu, word, 2 * row + (kk >> 3));
-    wt |= ((ww >> (4 * (kk & 7))) & 15u) << (4 * i);
-  }
-  if (qt) {
-    qt[((long long)(bk * 16 + kk) * N + bn * 16 + c0) >> 3] = wt;
-    if (!(lane & 1)) st[linear ? (long long)(bk * 16 + kk) * nb + bn : sw_off(bk * 16 + kk, bn, nb >> 2)] = (unsigned char)sb;
+      for (int o = 16; o; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+      const u32 sb = block_scale_byte(bmax, ts);
+      sbs[j] = sb;
+      const float2 kf = lut_entry(ts, sb);
+      const u64 B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        const u64 t = f2_ndiv(f2_ndiv(f2_pack(v[j][i], v[j][i + 1]), G, NRG), B, NRB);
+        y[i] = f2_lo(t); y[i + 1] = f2_hi(t);
+      }
+      const u32 word = e2m1x8_rn(y);
+      if (q && bn < nb) {
+        q[((long long)(bn * 16 + r) * K + bk * 16 + c0) >> 3] = word;
+        if (!(lane & 1)) s[linear ? (long long)(bn * 16 + r) * kb + bk : sw_off(bn * 16 + r, bk, kb >> 2)] = (unsigned char)sb;
+      }
+      // transposed block: this lane builds k-row kk = lane>>1, n values (lane&1)*8 .. +7
+      const int kk = lane >> 1;
+      u32 t = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const u32 ww = __shfl_sync(0xffffffffu, word, 2 * (c0 + i) + (kk >> 3));
+        t |= ((ww >> (4 * (kk & 7))) & 15u) << (4 * i);
+      }
+      wt[j] = t;
+    }
+    if (qt) {
+      const int kk = lane >> 1;
+      const long long krow = (long long)bk * 16 + kk;
+      if (grp * 4 + 3 < nb && wide_t) {
+        // even lane keeps blocks 0,1 (both 8-row halves), odd lane blocks 2,3: 16 contiguous bytes each
+        const bool odd = lane & 1;
+        const u32 give0 = odd ? wt[0] : wt[2], give1 = odd ? wt[1] : wt[3];
+        const u32 got0 = __shfl_xor_sync(0xffffffffu, give0, 1), got1 = __shfl_xor_sync(0xffffffffu, give1, 1);
+        const uint4 o = odd ? make_uint4(got0, wt[2], got1, wt[3]) : make_uint4(wt[0], got0, wt[1], got1);
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(qt) + krow * (N >> 1) + grp * 32 + (odd ? 16 : 0)) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (grp * 4 + j < nb) qt[(krow * N + (grp * 4 + j) * 16 + c0) >> 3] = wt[j];
+      }
+      if (!(lane & 1)) {
+        if (grp * 4 + 3 < nb && (!linear || !(nb & 3))) {
+          // the four blocks' scale bytes are neighbours in both layouts
+          const long long o = linear ? krow * nb + grp * 4 : sw_off(krow, grp * 4, nb >> 2);
+          *reinterpret_cast<u32*>(st + o) = sbs[0] | (sbs[1] << 8) | (sbs[2] << 16) | (sbs[3] << 24);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int bn = grp * 4 + j;
+            if (bn < nb) st[linear ? krow * nb + bn : sw_off(krow, bn, nb >> 2)] = (unsigned char)sbs[j];
+          }
+        }
+      }
+    }
   }
 }
 
@@ -369,13 +419,14 @@ extern "C" int nvfp4_quant_w2d(const void* w, int w_dtype, int N, int K, void* q
   if (w_dtype != NVFP4_DTYPE_BF16 && w_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
   if (N < 0 || K < 0 || (N & 15) || (K & 15)) return NVFP4_ERR_SHAPE;
   if (scale_layout == NVFP4_SCALES_SWIZZLED && ((N & 127) || (K & 127))) return NVFP4_ERR_SHAPE;
-  if (!aligned16(w) || (q && (reinterpret_cast<uintptr_t>(q) & 3u)) || (qt && (reinterpret_cast<uintptr_t>(qt) & 3u)))
+  if (!aligned16(w) || (q && (reinterpret_cast<uintptr_t>(q) & 3u)) || (qt && ((reinterpret_cast<uintptr_t>(qt) | reinterpret_cast<uintptr_t>(st_)) & 3u)))
     return NVFP4_ERR_ALIGN;
   if (N == 0 || K == 0) return NVFP4_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long nwarps = (long long)(N >> 4) * (K >> 4);
-  const long long blocks = (nwarps + 7) / 8;
-  if (blocks > 0x7FFFFFFFLL) return NVFP4_ERR_TOO_LARGE;
+  const long long nwarps = (long long)(((N >> 4) + 3) >> 2) * (K >> 4);
+  long long blocks = (nwarps + 7) / 8;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
   const int linear = scale_layout == NVFP4_SCALES_LINEAR;
   if (w_dtype == NVFP4_DTYPE_BF16)
     quant_w2d_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), static_cast<u32*>(q),
