@@ -223,6 +223,18 @@ def isolated_kernels(cfg, T, peaks):
             t = time_events(run, iters=max(10, 2 * nset))
             fl = 2.0 * M_ * N_ * K_
             detail[f"gemm_{name}_{pas}"] = {"M": M_, "N": N_, "K": K_, "us": t * 1e6, "tflops": fl / t / 1e12}
+            if not fp32:
+                # on-box comparator, a library call that is only timed: the reference's own GEMM
+                # (torch._scaled_mm on the packed operands, llm-1b/nvq.py:92) on the same shape
+                def run_lib():
+                    a, b, _ = ops[it[0] % nset]
+                    it[0] += 1
+                    torch._scaled_mm(a.d, b.d.t(), a.s.view(-1), b.s.view(-1), out_dtype=torch.bfloat16)
+                try:
+                    tl = time_events(run_lib, iters=max(10, 2 * nset))
+                    detail[f"gemm_{name}_{pas}"]["scaled_mm_tflops"] = fl / tl / 1e12
+                except Exception as e:      # the comparator is optional: a torch build without FP4 _scaled_mm
+                    detail[f"gemm_{name}_{pas}"]["scaled_mm_error"] = repr(e)[:120]
             tot_flops += fl * counts[name]
             tot_time += t * counts[name]
             del ops
@@ -262,6 +274,14 @@ def isolated_kernels(cfg, T, peaks):
     detail["quant_tile_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 3.125 / t / 1e9}
     t = q(lambda t, a: nvq.quant_rows_cols_rht(t, 0xA6B1, sr=True, seed=1, seed_cols=2, am=a, sr_mode=HW))
     detail["quant_tile_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 3.125 / t / 1e9}
+    # row operand with per-row scales (the reference trainer's emitter): one read, no amax pass
+    from nvfp4_training_b200 import emit
+    rq = emit.RowQ(T, 5632)
+    rng = torch.tensor([1, 0], dtype=torch.int32, device=dev)
+    t = q(lambda t, a: emit.row_emit(t, rq, None))
+    detail["emit_rows_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: emit.row_emit(t, rq, rng, sr=True))
+    detail["emit_rows_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     w = [torch.randn(11264, 2048, generator=g, device=dev).bfloat16() for _ in range(4)]
     it = [0]
 

@@ -121,6 +121,22 @@ int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void* codes_r, 
 int nvfp4_quant_tile_status(int* out, int reset);
 
 /*
+ * Row operand with an exact per-row FP32 scale, produced in one launch without a tensor-wide amax
+ * pass: x [T, C] bf16 (row stride ldx) -> codes [T, C/2], swizzled block scales for [T, C/16] and
+ * rs_out[t] = rowmax * (1/2688); a consumer multiplies the raw GEMM result by rs[t] * (weight scale).
+ * Replaces kernel `row_emit` (llm-1b/emit.cu:263-285, and its fixed-width variants :228-260) and
+ * launcher `emit.row_emit` (llm-1b/emit.py:72-79).  Arithmetic per row, IEEE FP32: inv = 2688/rowmax;
+ * per 16 values sb = e4m3((max*inv)*(1/6)), k = inv/dec(sb), code = rn(x*k).  sr != 0: stochastic
+ * rounding by 11-bit mantissa dither (llm-1b/emit.cu:38-43) with the reference's random sequence:
+ * lane l = (column/8) % 32 of row r runs s <- s*1664525+1013904223 from hash32(rng[0] ^ salt ^
+ * hash32(r*32+l)) over its 8-column chunks in column order, one step per pair of values.
+ * rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0, T % 128 == 0,
+ * ldx % 8 == 0, x 16-byte aligned.
+ */
+int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
+                    int sr, const unsigned* rng, unsigned salt, void* stream);
+
+/*
  * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,
  * emitting W (q [N, K/2], s for [N, K/16]) and W^T (qt [K, N/2], st for [K, N/16]) with identical
  * code values.  Either output pair may be null to skip it.

@@ -1,0 +1,133 @@
+// Row-operand emitter with an exact per-row FP32 scale (sm_100a): one launch, no tensor-wide amax
+// pass.  Reference: `row_emit` of llm-1b/emit.cu:263-285 (launcher llm-1b/emit.py:72-79), whose
+// arithmetic (multiplications by reciprocals) and random stream it reproduces bit for bit.
+//
+// One warp per row.  Lane l owns the 8-column chunks 256 j + 8 l of its row: that is the unit the
+// reference's per-lane random sequence is defined on, and a warp-wide load of one chunk index j
+// is 512 contiguous bytes.  Rows of up to 5632 columns stay in registers between the row-max pass
+// and the quantization pass (packed bf16, 4 registers per chunk); longer rows are read a second
+// time, which L2 serves.
+#include "common.cuh"
+
+namespace nvfp4 {
+
+__device__ __forceinline__ uint4 ld_chunk(const __nv_bfloat16* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+
+// bf16 magnitudes order like unsigned 16-bit integers: running max of both halves of each word
+__device__ __forceinline__ u32 absmax_packed(u32 m, const uint4& q) {
+  m = __vmaxu2(m, q.x & 0x7FFF7FFFu); m = __vmaxu2(m, q.y & 0x7FFF7FFFu);
+  m = __vmaxu2(m, q.z & 0x7FFF7FFFu); m = __vmaxu2(m, q.w & 0x7FFF7FFFu);
+  return m;
+}
+
+// dither with bits already in place (11 random bits at positions 11..21), truncate to the E2M1
+// grid, clamp to 6, restore the sign (llm-1b/emit.cu:38-43)
+__device__ __forceinline__ float sr_dither11(float v, u32 r22) {
+  const float a = fabsf(v), lift = a < 1.f ? 1.f : 0.f;
+  const float b = __fadd_rn(a, lift);
+  const float q = __fsub_rn(__uint_as_float((__float_as_uint(b) + r22) & 0xFFC00000u), lift);
+  return __uint_as_float(__float_as_uint(fminf(q, 6.f)) | (__float_as_uint(v) & 0x80000000u));
+}
+
+// Quantize one 8-column chunk (half a block; lane ^ 1 holds the other half) of row r.
+template <bool SR>
+__device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg, long long r, int col, int C,
+                                           u32* __restrict__ codes, unsigned char* __restrict__ scales, int lane) {
+  float v[8];
+  const u32 w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+  float m = absmax3(v[0], v[1], v[2]);
+  m = absmax3(m, v[3], v[4]);
+  m = absmax3(m, v[5], v[6]);
+  m = absmax3(m, v[7], m);
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  const u32 sb = e4m3_enc(__fmul_rn(__fmul_rn(m, inv), 1.f / 6.f));
+  const float sd = e4m3_dec(sb);
+  const float k = sd > 0.f ? __fdiv_rn(inv, sd) : 0.f;
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) y[i] = __fmul_rn(v[i], k);
+  if (SR) {
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      lcg = lcg * 1664525u + 1013904223u;
+      const u32 rnd = lcg ^ (lcg >> 16);
+      y[i] = sr_dither11(y[i], (rnd << 11) & 0x3FF800u);
+      y[i + 1] = sr_dither11(y[i + 1], (rnd >> 5) & 0x3FF800u);
+    }
+  }
+  codes[(r * C + col) >> 3] = e2m1x8_rn(y);
+  if (!(lane & 1)) scales[sw_off(r, col >> 4, C >> 6)] = (unsigned char)sb;
+}
+
+// KEEP = number of chunks per lane held in registers (C == 256 * KEEP), or 0 for rows of any
+// length that are read twice.
+template <int KEEP, bool SR>
+__global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int C,
+                                                        u32* __restrict__ codes, unsigned char* __restrict__ scales,
+                                                        float* __restrict__ rs_out, int T, const u32* __restrict__ rng,
+                                                        u32 salt) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= T) return;
+  const __nv_bfloat16* row = x + r * ldx + lane * 8;
+  constexpr int NK = KEEP > 0 ? KEEP : 1;
+  uint4 kept[NK];
+  u32 mm = 0u;
+  if (KEEP > 0) {
+#pragma unroll
+    for (int j = 0; j < NK; j++) kept[j] = ld_chunk(row + j * 256);
+#pragma unroll
+    for (int j = 0; j < NK; j++) mm = absmax_packed(mm, kept[j]);
+  } else {
+    for (int c = 0; c < C; c += 256) mm = absmax_packed(mm, ld_chunk(row + c));
+  }
+  mm = max(mm & 0xFFFFu, mm >> 16);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mm = max(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+  const float am = __uint_as_float(mm << 16);
+  const float inv = am > 0.f ? __fdiv_rn(kFp4E4m3, am) : 0.f;
+  if (lane == 0) rs_out[r] = __fmul_rn(am, 1.f / kFp4E4m3);
+  u32 lcg = hash32((SR ? __ldg(rng) : 0u) ^ salt ^ hash32((u32)(r * 32 + lane)));
+  if (KEEP > 0) {
+#pragma unroll
+    for (int j = 0; j < NK; j++) emit_chunk<SR>(kept[j], inv, lcg, r, j * 256 + lane * 8, C, codes, scales, lane);
+  } else {
+    for (int c = 0; c < C; c += 256) emit_chunk<SR>(ld_chunk(row + c), inv, lcg, r, c + lane * 8, C, codes, scales, lane);
+  }
+}
+
+template <int KEEP>
+static void launch_rows(bool sr, unsigned blocks, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int C, u32* codes,
+                        unsigned char* scales, float* rs, int T, const u32* rng, u32 salt) {
+  if (sr) emit_rows_kernel<KEEP, true><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
+  else emit_rows_kernel<KEEP, false><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+extern "C" int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
+                               int sr, const unsigned* rng, unsigned salt, void* stream) {
+  if (!x || !codes || !scales || !rs_out || (sr && !rng)) return NVFP4_ERR_NULL;
+  if (T < 0 || C < 0 || (C & 255) || ldx < C || (T & 127)) return NVFP4_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes) & 3u)) return NVFP4_ERR_ALIGN;
+  if (T == 0 || C == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)((T + 7) / 8);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  u32* cp = static_cast<u32*>(codes);
+  unsigned char* sp = static_cast<unsigned char*>(scales);
+  switch (C / 256) {
+    case 8: launch_rows<8>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 12: launch_rows<12>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 22: launch_rows<22>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    default: launch_rows<0>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+  }
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}

@@ -1,0 +1,95 @@
+"""Operand emitters of the reference's 1B trainer (llm-1b/emit.py) on the sm_100a library: the
+row operand with an exact per-row FP32 scale, so no tensor-wide amax pass precedes it, and the raw
+block-scaled GEMM whose result the consumer multiplies by `rs[t] * gs`.
+
+Built so far: `RowQ`, `row_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`.  The fused producers
+(`rms_emit`, `swiglu_emit`) and the delayed-scale column emitter (`col_emit`) are not built.
+"""
+import torch
+
+from . import _lib as L
+from . import nvq
+
+F4, F8 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+
+
+class RowQ:
+    """Row operand [R, C]: data (fp4x2 [R, C/2]), swizzled scales, rs[R] per-row fp32 scale
+    (llm-1b/emit.py:20-27)."""
+    __slots__ = ("d", "s", "rs")
+
+    def __init__(self, R, C, dev="cuda"):
+        self.d = torch.empty(R, C // 2, dtype=torch.uint8, device=dev)
+        self.s = torch.empty(R * C // 16, dtype=torch.uint8, device=dev)
+        self.rs = torch.empty(R, dtype=torch.float32, device=dev)
+
+
+def row_emit(x, q: RowQ, rng, sr=False, salt=0):
+    """Quantize the rows of x [T, C] into q (llm-1b/emit.py:72-79).  `rng`: CUDA int32/uint32 words,
+    rng[0] = stochastic-rounding seed (read on the device, so a captured graph sees fresh seeds)."""
+    L.require_cuda(x, q.d, q.s, q.rs)
+    T, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and C % 256 == 0
+    assert T % 128 == 0, T
+    if sr:
+        assert rng is not None and rng.is_cuda and rng.element_size() == 4
+    L.check(L.load().nvfp4_emit_rows(L.ptr(x), x.stride(0), T, C, L.ptr(q.d), L.ptr(q.s), L.ptr(q.rs), int(bool(sr)),
+                                     L.ptr(rng) if rng is not None else None, salt & 0xFFFFFFFF, L.stream()), "emit_rows")
+    return q
+
+
+class WQ:
+    """FP4 form of a weight W [N, K] and of W^T, per-tensor scale gs = amax/2688 (llm-1b/emit.py:100-128).
+    The reference re-quantizes just in time into a scratch shared by same-shape weights; here
+    `refresh` quantizes once per optimizer step into buffers the object owns."""
+
+    def __init__(self, N, K, dev="cuda"):
+        self.N, self.K = N, K
+        self.q = self.qt = None
+
+    def refresh(self, w):
+        w = w.detach().to(torch.bfloat16)
+        if self.q is None:
+            self.q, self.qt = nvq.quant_w2d(w)
+        else:
+            nvq.quant_w2d(w, out=(self.q, self.qt))
+        return self
+
+    def prep(self):
+        return self
+
+    @property
+    def gs(self):
+        return self.q.gs
+
+    d = property(lambda self: self.q.d)
+    s = property(lambda self: self.q.s)
+    td = property(lambda self: self.qt.d)
+    ts = property(lambda self: self.qt.s)
+
+
+_ONES = {}
+
+
+def _one(dev):
+    if dev not in _ONES:
+        _ONES[dev] = torch.ones(1, dtype=torch.float32, device=dev)
+    return _ONES[dev]
+
+
+def mm(ad, as_, bd, bs, out_dtype=torch.bfloat16):
+    """raw = A @ B^T with block scales only; A [M, K], B [N, K] fp4 row-major (llm-1b/emit.py:131-133)."""
+    one = _one(ad.device)
+    a = nvq.Q(ad.view(F4), as_.view(F8), one)
+    b = nvq.Q(bd.view(F4), bs.view(F8), one)
+    return nvq.mm(a, b, out_dtype=out_dtype, scale=False)[0]
+
+
+def mm_row_w(q: RowQ, w: WQ):
+    """forward: y_raw = Q(x) @ Q(W)^T; true y = y_raw * q.rs[:, None] * w.gs (llm-1b/emit.py:136-140)."""
+    return mm(q.d, q.s, w.d, w.s)
+
+
+def mm_row_wt(q: RowQ, w: WQ):
+    """dgrad: dx_raw = Q(dy) @ Q(W); true = raw * q.rs[:, None] * w.gs (llm-1b/emit.py:143-145)."""
+    return mm(q.d, q.s, w.td, w.ts)

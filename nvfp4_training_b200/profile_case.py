@@ -75,6 +75,12 @@ def main():
             ("tile_rows+cols_rn", lambda x: nvq.quant_rows_cols_rht(x, S, am=am), 3.125),
             ("tile_cols_rn", lambda x: nvq.quant_rows_cols_rht(x, S, am=am, want=(False, True)), 2.5625),
         )
+        if a.N % 256 == 0:
+            from . import emit
+            rq = emit.RowQ(a.M, a.N)
+            rng = torch.tensor([1, 0], dtype=torch.int32, device="cuda")
+            cases = cases + (("emit_rows_rn", lambda x: emit.row_emit(x, rq, None), 2.5625),
+                             ("emit_rows_sr", lambda x: emit.row_emit(x, rq, rng, sr=True), 2.5625))
         for name, fn, bpe in cases:
             us = timed(lambda: fn(nxt()), a.iters)
             out[name] = {"us": us, "gbs": n * bpe / us / 1e3}

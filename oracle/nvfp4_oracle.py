@@ -415,6 +415,81 @@ def quant_w2d(w, amax=None):
 
 
 # ----------------------------------------------------------------------------- decode / GEMM
+# ----------------------------------------------------------------------------- operand emitters
+# Restatement of the row / column operand emitters of the reference's 1B trainer (llm-1b/emit.cu):
+# kernel arithmetic (multiplications by reciprocals), not the torch path's divisions.  PARITY
+# UNPINNED: the reference holds no CPU implementation or fixture of these kernels, so this follows
+# the CUDA source line by line and is checked only for self-consistency (dequantization error).
+def lcg_next(s):
+    """`rng_next` of llm-1b/emit.cu:45: s = s*1664525 + 1013904223; returns (s, s ^ (s >> 16))."""
+    s = (np.asarray(s, dtype=np.uint32) * np.uint32(1664525) + np.uint32(1013904223)).astype(np.uint32)
+    return s, s ^ (s >> np.uint32(16))
+
+
+def sr2(v, r22):
+    """`sr2` of llm-1b/emit.cu:38-43: dither with the (already masked) bits r22, truncate to the
+    E2M1 grid, clamp to 6, keep the sign of v."""
+    v = np.asarray(v, dtype=np.float32)
+    a = np.abs(v)
+    lift = np.where(a < np.float32(1.0), np.float32(1.0), np.float32(0.0)).astype(np.float32)
+    b = (a + lift).astype(np.float32)
+    q = (u2f((f2u(b) + np.asarray(r22, dtype=np.uint32)) & np.uint32(0xFFC00000)) - lift).astype(np.float32)
+    mag = f2u(np.minimum(q, FP4_MAX).astype(np.float32)) | (f2u(v) & np.uint32(0x80000000))
+    return u2f(mag)
+
+
+def _emit_pack8(v8, k, sr, state):
+    """`pack8` of llm-1b/emit.cu:49-58 on [..., 8] values: scale, optional SR (one LCG step per
+    pair: element i takes (r << 11) & 0x3FF800, element i+1 takes (r >> 5) & 0x3FF800), RN codes."""
+    x = (np.asarray(v8, dtype=np.float32) * np.asarray(k, dtype=np.float32)[..., None]).astype(np.float32)
+    if sr:
+        for i in range(0, 8, 2):
+            state, r = lcg_next(state)
+            x[..., i] = sr2(x[..., i], (r << np.uint32(11)) & np.uint32(0x3FF800))
+            x[..., i + 1] = sr2(x[..., i + 1], (r >> np.uint32(5)) & np.uint32(0x3FF800))
+    return e2m1_rn_code(x), state
+
+
+def emit_rows(x, seed=0, sr=False, salt=0):
+    """Row operand with an exact per-row FP32 scale (`row_emit`, llm-1b/emit.cu:263-285).
+    x: [T, C] float32 holding bf16 values, C % 256 == 0.  Returns (packed codes [T, C/2], scale
+    bytes [T, C/16] row-major, rs [T] float32).  Arithmetic per row: inv = 2688/rowmax (0 for a
+    zero row), rs = rowmax * (1/2688); per 16 values: sb = e4m3((m*inv)*(1/6)), k = inv/dec(sb)
+    (0 when the byte is 0), code = rn(x*k).  SR: lane l = (column/8) % 32 of row r starts an LCG at
+    hash32(seed ^ salt ^ hash32(r*32 + l)) and walks its 8-column chunks in column order."""
+    x = np.asarray(x, dtype=np.float32)
+    T, C = x.shape
+    assert C % 256 == 0
+    am = np.abs(x).max(axis=1).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(am > 0, np.float32(FP4_E4M3) / am, np.float32(0)).astype(np.float32)
+    rs = (am * np.float32(np.float32(1.0) / np.float32(FP4_E4M3))).astype(np.float32)
+    xb = x.reshape(T, C // 16, 16)
+    m = np.abs(xb).max(axis=2).astype(np.float32)
+    sarg = ((m * inv[:, None]).astype(np.float32) * np.float32(np.float32(1.0) / np.float32(6.0))).astype(np.float32)
+    sbyte = e4m3_encode(sarg)
+    sd = e4m3_decode(sbyte).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        k = np.where(sd > 0, inv[:, None] / np.where(sd > 0, sd, np.float32(1)), np.float32(0)).astype(np.float32)
+    codes = np.empty((T, C), dtype=np.uint8)
+    rows = np.arange(T, dtype=np.uint32)[:, None]
+    lanes = np.arange(32, dtype=np.uint32)[None, :]
+    state = hash32(np.uint32((seed if sr else 0) & 0xFFFFFFFF) ^ np.uint32(salt & 0xFFFFFFFF) ^ hash32(rows * np.uint32(32) + lanes))
+    for j in range(C // 256):                      # chunk j of lane l covers columns 256 j + 8 l .. + 8
+        v8 = x[:, 256 * j:256 * (j + 1)].reshape(T, 32, 8)
+        kk = np.repeat(k[:, 16 * j:16 * (j + 1)], 2, axis=1)          # lanes 2b, 2b+1 share block b
+        c8, state = _emit_pack8(v8, kk, sr, state)
+        codes[:, 256 * j:256 * (j + 1)] = c8.reshape(T, 256)
+    return pack_codes(codes), sbyte, rs
+
+
+def emit_rows_dequant(packed, sbyte, rs):
+    """Values a consumer reconstructs from a row operand: code * block scale * rs[row]."""
+    T = packed.shape[0]
+    vals = E2M1_TABLE[unpack_codes(packed)].reshape(T, -1, 16)
+    return (vals * e4m3_decode(sbyte)[:, :, None] * np.asarray(rs, dtype=np.float32)[:, None, None]).reshape(T, -1).astype(np.float32)
+
+
 def dequant(packed, scales, gs):
     """value * block scale * tensor scale, in that order (llm-1b/nvq.py:110-117)."""
     v = E2M1_TABLE[unpack_codes(packed)]
