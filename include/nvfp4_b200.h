@@ -137,6 +137,22 @@ int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, voi
                     int sr, const unsigned* rng, unsigned salt, void* stream);
 
 /*
+ * Column operand with a delayed per-tensor scale: x [M, C] bf16 (row stride ldx) -> x^T quantized
+ * along the tokens after the 16-point random Hadamard transform, codes [C, M/2], swizzled scales for
+ * [C, M/16].  The scale comes from *amax_use, an RHT-domain amax observed earlier (inv = 2688/amax_use);
+ * the RHT-domain amax of THIS tensor is recorded into *amax_cur with atomicMax on float bits (the
+ * caller zeroes it).  No amax pass over x is needed.  Replaces kernel `col_emit` (llm-1b/emit.cu:287-341)
+ * and launcher `emit.col_emit` (llm-1b/emit.py:82-85).  rng: device words, rng[0] = SR seed, rng[1] =
+ * Hadamard sign bits (required).  sr != 0: 11-bit mantissa dither with the reference's random
+ * sequence (the thread of column c and 64-token group g starts at hash32(rng[0] ^ salt ^ hash32(c*4099+g))
+ * and takes its four 16-token blocks in order, one LCG step per pair of values).
+ * Requires M % 128 == 0, C % 128 == 0, ldx % 8 == 0, x and codes 16-byte aligned, scales 8-byte aligned.
+ */
+int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void* codes, void* scales,
+                    const float* amax_use, unsigned* amax_cur, int sr, const unsigned* rng, unsigned salt,
+                    void* stream);
+
+/*
  * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,
  * emitting W (q [N, K/2], s for [N, K/16]) and W^T (qt [K, N/2], st for [K, N/16]) with identical
  * code values.  Either output pair may be null to skip it.

@@ -30,6 +30,7 @@ SIGNATURES = {
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),
     "nvfp4_quant_tile_status": (_i, [_vp, _i]),
     "nvfp4_emit_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp, _u, _vp]),
+    "nvfp4_emit_cols": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _u, _vp]),
     "nvfp4_quant_w2d": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
     "nvfp4_e2m1x4_sr": (_i, [_vp, _vp, _vp, _ll, _vp]),
     "nvfp4_swizzle_scales": (_i, [_vp, _ll, _i, _i, _vp, _vp]),

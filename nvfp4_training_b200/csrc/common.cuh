@@ -82,6 +82,24 @@ __device__ __forceinline__ float sr_dither(float v, u32 rnd) {
   return copysignf(fminf(r, 6.f), v);
 }
 
+// Internal modes of the operand emitters (llm-1b/emit.cu arithmetic: block scale and values by
+// multiplications, no exact divisions); not part of the public rounding enum.
+#define NVFP4_EMIT_NEAREST 4   /* y = v * (inv/bs), round to nearest */
+#define NVFP4_EMIT_SR      5   /* same, 11-bit mantissa dither driven by a per-thread LCG */
+
+// dither with bits already in place (11 random bits at positions 11..21), truncate to the E2M1
+// grid, clamp to 6, restore the sign (llm-1b/emit.cu:38-43)
+__device__ __forceinline__ float sr_dither11(float v, u32 r22) {
+  const float a = fabsf(v), lift = a < 1.f ? 1.f : 0.f;
+  const float b = __fadd_rn(a, lift);
+  const float q = __fsub_rn(__uint_as_float((__float_as_uint(b) + r22) & 0xFFC00000u), lift);
+  return __uint_as_float(__float_as_uint(fminf(q, 6.f)) | (__float_as_uint(v) & 0x80000000u));
+}
+// the emitters' generator (llm-1b/emit.cu:45) and its n-step jump  s -> A^n s + C_n
+__device__ __forceinline__ u32 lcg_step(u32& s) { s = s * 1664525u + 1013904223u; return s ^ (s >> 16); }
+__host__ __device__ constexpr u32 lcg_jump_mul(int n) { u32 a = 1u; for (int i = 0; i < n; i++) a *= 1664525u; return a; }
+__host__ __device__ constexpr u32 lcg_jump_add(int n) { u32 c = 0u; for (int i = 0; i < n; i++) c = c * 1664525u + 1013904223u; return c; }
+
 // byte offset of the scale of (row r, 16-block c) in the swizzled layout; ncb = (C/16)/4
 __device__ __forceinline__ long long sw_off(long long r, int c, int ncb) {
   return ((r >> 7) * ncb + (c >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
@@ -166,7 +184,7 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
     // entry 0 (underflowed block): -0 / +0 make every scaled value a zero with the input's sign
     float m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -0.f : 0.f;
     if (threadIdx.x >= 1 && threadIdx.x <= 126)
-      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -__frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);
+      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -__frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);   // emit modes: inv/bs too
     reinterpret_cast<float2*>(lut)[threadIdx.x] = make_float2(m, bsf);
   }
   __syncthreads();
@@ -183,6 +201,10 @@ __device__ __forceinline__ float2 lut_entry(const TensorScale& ts, u32 sb) {
 // Scale byte of a block:  e4m3(min((bmax/gs)/6, 448))  in IEEE FP32 (the reference's torch path).
 __device__ __forceinline__ u32 block_scale_byte(float bmax, const TensorScale& ts) {
   return e4m3_enc(ndiv(ndiv(bmax, ts.gs, ts.nrgs), 6.0f, -0.16666667163372039794921875f));
+}
+// the emitters' form (llm-1b/emit.cu:85): e4m3((bmax * inv) * (1/6))
+__device__ __forceinline__ u32 block_scale_byte_mul(float bmax, const TensorScale& ts) {
+  return e4m3_enc(__fmul_rn(__fmul_rn(bmax, ts.inv_gs), 1.f / 6.f));
 }
 
 // random words of the hardware-SR mode: one per group of four consecutive elements of a block
@@ -203,7 +225,17 @@ __device__ __forceinline__ u32 block_key(u32 seed, u32 blk_idx) {
 
 // Eight scaled values (elements 8h .. 8h+7 of a block, h = 0 or 1) -> one 32-bit word of codes.
 template <int ROUNDING>
-__device__ __forceinline__ u32 round8(float (&y)[8], u32 key, u32 seed, u32 elt_idx, int h) {
+__device__ __forceinline__ u32 round8(float (&y)[8], u32& key, u32 seed, u32 elt_idx, int h) {
+  if (ROUNDING == NVFP4_EMIT_SR) {
+    // `key` is the running LCG state of this thread: one step per pair of values
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const u32 rnd = lcg_step(key);
+      y[j] = sr_dither11(y[j], (rnd << 11) & 0x3FF800u);
+      y[j + 1] = sr_dither11(y[j + 1], (rnd >> 5) & 0x3FF800u);
+    }
+    return e2m1x8_rn(y);
+  }
   if (ROUNDING == NVFP4_ROUND_SR_HW)
     return e2m1x4_rs(y[0], y[1], y[2], y[3], sr_hw_word(key, 2 * h)) | (e2m1x4_rs(y[4], y[5], y[6], y[7], sr_hw_word(key, 2 * h + 1)) << 16);
   if (ROUNDING == NVFP4_ROUND_SR_DITHER || ROUNDING == NVFP4_ROUND_SR_DITHER_K) {
@@ -231,7 +263,7 @@ template <int ROUNDING>
 __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const TensorScale& ts, u32 seed,
                                                u32 blk_idx, u32 elt_idx) {
   const float2 kf = lut_entry(ts, sb);
-  const u32 key = block_key<ROUNDING>(seed, blk_idx);
+  u32 key = block_key<ROUNDING>(seed, blk_idx);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(kf.y, kf.y), K = f2_pack(kf.x, kf.x);
   u32 w[2];
@@ -253,15 +285,17 @@ __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const 
 // riding in the two halves of the packed constants.
 template <int ROUNDING>
 __device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const TensorScale& ts, u32 seed, u32 blk0, u32 blk1,
-                                                uint2& o0, uint2& o1, u32& sb0, u32& sb1) {
+                                                u32 key0, u32 key1, uint2& o0, uint2& o1, u32& sb0, u32& sb1,
+                                                float* bmax_out = nullptr) {
+  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR;
   float m0 = absmax3(f2_lo(P[0]), f2_lo(P[1]), f2_lo(P[2])), m1 = absmax3(f2_hi(P[0]), f2_hi(P[1]), f2_hi(P[2]));
 #pragma unroll
   for (int i = 3; i < 15; i += 2) { m0 = absmax3(m0, f2_lo(P[i]), f2_lo(P[i + 1])); m1 = absmax3(m1, f2_hi(P[i]), f2_hi(P[i + 1])); }
   m0 = absmax3(m0, f2_lo(P[15]), m0); m1 = absmax3(m1, f2_hi(P[15]), m1);
-  sb0 = block_scale_byte(m0, ts);
-  sb1 = block_scale_byte(m1, ts);
+  if (bmax_out) *bmax_out = fmaxf(m0, m1);
+  sb0 = EMIT ? block_scale_byte_mul(m0, ts) : block_scale_byte(m0, ts);
+  sb1 = EMIT ? block_scale_byte_mul(m1, ts) : block_scale_byte(m1, ts);
   const float2 k0 = lut_entry(ts, sb0), k1 = lut_entry(ts, sb1);
-  const u32 key0 = block_key<ROUNDING>(seed, blk0), key1 = block_key<ROUNDING>(seed, blk1);
   const u64 G = f2_pack(ts.gs, ts.gs), NRG = f2_pack(ts.nrgs, ts.nrgs);
   const u64 B = f2_pack(k0.y, k1.y), K = f2_pack(k0.x, k1.x);
   u32 w0[2], w1[2];

@@ -22,15 +22,6 @@ __device__ __forceinline__ u32 absmax_packed(u32 m, const uint4& q) {
   return m;
 }
 
-// dither with bits already in place (11 random bits at positions 11..21), truncate to the E2M1
-// grid, clamp to 6, restore the sign (llm-1b/emit.cu:38-43)
-__device__ __forceinline__ float sr_dither11(float v, u32 r22) {
-  const float a = fabsf(v), lift = a < 1.f ? 1.f : 0.f;
-  const float b = __fadd_rn(a, lift);
-  const float q = __fsub_rn(__uint_as_float((__float_as_uint(b) + r22) & 0xFFC00000u), lift);
-  return __uint_as_float(__float_as_uint(fminf(q, 6.f)) | (__float_as_uint(v) & 0x80000000u));
-}
-
 // Quantize one 8-column chunk (half a block; lane ^ 1 holds the other half) of row r.
 template <bool SR>
 __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg, long long r, int col, int C,
@@ -53,8 +44,7 @@ __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg
   if (SR) {
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
-      lcg = lcg * 1664525u + 1013904223u;
-      const u32 rnd = lcg ^ (lcg >> 16);
+      const u32 rnd = lcg_step(lcg);
       y[i] = sr_dither11(y[i], (rnd << 11) & 0x3FF800u);
       y[i + 1] = sr_dither11(y[i + 1], (rnd >> 5) & 0x3FF800u);
     }

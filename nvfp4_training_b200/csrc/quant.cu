@@ -163,7 +163,8 @@ __global__ void __launch_bounds__(256, 2) quant_cols_rht_kernel(const __nv_bfloa
     const long long c = (long long)cchunk * 8 + jw * 2;
     const long long b0 = c * nmb + mb, b1 = b0 + nmb;
     uint2 o0, o1; u32 sb0, sb1;
-    quant_block16x2<ROUNDING>(P, ts, seed, (u32)b0, (u32)b1, o0, o1, sb0, sb1);
+    quant_block16x2<ROUNDING>(P, ts, seed, (u32)b0, (u32)b1, block_key<ROUNDING>(seed, (u32)b0), block_key<ROUNDING>(seed, (u32)b1),
+                              o0, o1, sb0, sb1);
     *reinterpret_cast<uint2*>(codes + b0 * 8) = o0;
     *reinterpret_cast<uint2*>(codes + b1 * 8) = o1;
     scales[linear ? b0 : sw_off(c, mb, nmb >> 2)] = (unsigned char)sb0;

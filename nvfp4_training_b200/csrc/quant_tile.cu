@@ -37,6 +37,10 @@ struct TileParams {
   u32 signs;
   u32 seed_r, seed_c;
   const u32* seed_r_dev; const u32* seed_c_dev;
+  // operand-emitter mode only (llm-1b/emit.cu `col_emit`): `amax` is the delayed RHT-domain amax
+  unsigned* amax_cur;      // observed RHT-domain amax of this tensor, float bits, atomicMax
+  const u32* rng;          // device words: rng[0] = SR seed, rng[1] = Hadamard sign bits
+  u32 salt;
 };
 
 // barrier over the 256 consumer threads (named barrier 1) with an AND of `ok`
@@ -109,8 +113,10 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   const bool first = blockIdx.x == 0 && threadIdx.x == 0;
   TensorScale ts_r, ts_c;
   if (ROWS) ts_r = make_tensor_scale<ROUNDING>(amax, 1.f, lut_r, first ? p.gs_r_out : nullptr);
-  // the x0.25 that follows the butterflies is folded into the tensor scale (a power of two)
-  if (COLS) ts_c = make_tensor_scale<ROUNDING>(amax, 4.f, lut_c, first ? p.gs_c_out : nullptr, 0.25f);
+  // the x0.25 that follows the butterflies is folded into the tensor scale (a power of two); the
+  // emitter's delayed amax is already an RHT-domain value (no factor 4)
+  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR;
+  if (COLS) ts_c = make_tensor_scale<ROUNDING>(amax, EMIT ? 1.f : 4.f, lut_c, first ? p.gs_c_out : nullptr, 0.25f);
   __syncthreads();
 
   if (warp == 0) {
@@ -136,9 +142,15 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   const int cw = warp - 1;                       // 0..7
   const int ctid = threadIdx.x - 32;             // 0..255
   u32 seed_r = p.seed_r, seed_c = p.seed_c;
-  if (ROUNDING != NVFP4_ROUND_NEAREST) {
+  if (ROUNDING != NVFP4_ROUND_NEAREST && !EMIT) {
     if (p.seed_r_dev) seed_r = __ldg(p.seed_r_dev);
     if (p.seed_c_dev) seed_c = __ldg(p.seed_c_dev);
+  }
+  u32 signs = p.signs;
+  float seen = 0.f;                              // emitter: largest transformed magnitude this thread met
+  if (EMIT) {
+    seed_c = (ROUNDING == NVFP4_EMIT_SR ? __ldg(p.rng) : 0u) ^ p.salt;
+    if (p.rng) signs = __ldg(p.rng + 1) & 0xFFFFu;
   }
   const int nblk = p.C >> 4;                     // 16-column blocks per row
   const int nmb = p.M >> 4;                      // 16-token blocks per column
@@ -183,7 +195,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
       for (int i = 0; i < 16; i++) {
         u32 w;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(tile + xoff[i & 7] + (u32)(i * 128)));
-        const u32 f = ((p.signs >> i) & 1u) << 31;           // token i is negated when bit i of signs is set
+        const u32 f = ((signs >> i) & 1u) << 31;             // token i is negated when bit i of signs is set
         P[i] = f2_pack(__uint_as_float((w << 16) + f), __uint_as_float((w & 0xFFFF0000u) ^ f));
       }
 #pragma unroll
@@ -193,7 +205,23 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
           if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
       const u32 b0 = (u32)((long long)ct * kTileCol * nmb + mt * (kTileTok / 16)) + (u32)thr_cblk, b1 = b0 + (u32)nmb;
       uint2 o0, o1; u32 sb0, sb1;
-      quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, o0, o1, sb0, sb1);
+      u32 key0, key1;
+      float bmax = 0.f;
+      if (EMIT) {
+        // the reference's thread of (column, 64-token group) walks its four blocks in order: jump to block mb & 3
+        const u32 c = (u32)(ct * kTileCol + 2 * lane), mb = (u32)(mt * (kTileTok / 16) + cw);
+        key0 = hash32(seed_c ^ hash32(c * 4099u + (mb >> 2)));
+        key1 = hash32(seed_c ^ hash32((c + 1u) * 4099u + (mb >> 2)));
+        constexpr u32 jm[4] = {1u, lcg_jump_mul(8), lcg_jump_mul(16), lcg_jump_mul(24)};
+        constexpr u32 ja[4] = {0u, lcg_jump_add(8), lcg_jump_add(16), lcg_jump_add(24)};
+        key0 = key0 * jm[mb & 3u] + ja[mb & 3u];
+        key1 = key1 * jm[mb & 3u] + ja[mb & 3u];
+      } else {
+        key0 = block_key<ROUNDING>(seed_c, b0);
+        key1 = block_key<ROUNDING>(seed_c, b1);
+      }
+      quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, key0, key1, o0, o1, sb0, sb1, EMIT ? &bmax : nullptr);
+      if (EMIT) seen = fmaxf(seen, bmax);
       u32* sc = stage_codes[buf] + sc_off;
       sc[0] = o0.x; sc[1] = o0.y;                                   // column 2*lane
       sc[32 * 17 + 1] = o1.x; sc[32 * 17 + 2] = o1.y;               // column 2*lane+1
@@ -225,6 +253,11 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * stage);
     if (++stage == kTileStages) { stage = 0; phase ^= 1u; }
+  }
+  if (EMIT && p.amax_cur) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, o));
+    if (lane == 0) atomicMax(p.amax_cur, __float_as_uint(__fmul_rn(seen, 0.25f)));
   }
   if (COLS && prev_mt >= 0) {
     consumers_sync();
@@ -287,7 +320,7 @@ extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap map;
   if (!make_tile_map(&map, x, M, C, ldx)) return NVFP4_ERR_CUDA;
-  TileParams p;
+  TileParams p = {};
   p.codes_r = static_cast<uint2*>(codes_r); p.scales_r = static_cast<unsigned char*>(scales_r);
   p.codes_c = static_cast<unsigned char*>(codes_c); p.scales_c = static_cast<unsigned char*>(scales_c);
   p.amax = amax; p.gs_r_out = gs_r_out; p.gs_c_out = gs_c_out;
@@ -308,6 +341,34 @@ extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void
     case NVFP4_ROUND_SR_DITHER_K: return launch_tile_mode<NVFP4_ROUND_SR_DITHER_K>(map, p, grid, st);
     default: return launch_tile_mode<NVFP4_ROUND_SR_HW>(map, p, grid, st);
   }
+}
+
+extern "C" int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void* codes, void* scales,
+                               const float* amax_use, unsigned* amax_cur, int sr, const unsigned* rng, unsigned salt,
+                               void* stream) {
+  if (!x || !codes || !scales || !amax_use || !rng) return NVFP4_ERR_NULL;
+  if (M < 0 || C < 0 || (M % kTileTok) || (C & 127) || ldx < C) return NVFP4_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes) & 15u) ||
+      (reinterpret_cast<uintptr_t>(scales) & 7u))
+    return NVFP4_ERR_ALIGN;
+  if (M == 0 || C == 0) return NVFP4_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap map;
+  if (!make_tile_map(&map, x, M, C, ldx)) return NVFP4_ERR_CUDA;
+  TileParams p = {};
+  p.codes_c = static_cast<unsigned char*>(codes); p.scales_c = static_cast<unsigned char*>(scales);
+  p.amax = amax_use; p.amax_cur = amax_cur; p.rng = rng; p.salt = salt;
+  p.M = M; p.C = C; p.linear = 0;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
+  }
+  const long long ntiles = (long long)(M / kTileTok) * (C / kTileCol);
+  int grid = 2 * sms;
+  if (ntiles < grid) grid = (int)ntiles;
+  return sr ? launch_tile<NVFP4_EMIT_SR, false, true>(map, p, grid, st)
+            : launch_tile<NVFP4_EMIT_NEAREST, false, true>(map, p, grid, st);
 }
 
 extern "C" int nvfp4_quant_tile_status(int* out, int reset) {

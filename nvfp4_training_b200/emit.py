@@ -2,8 +2,8 @@
 row operand with an exact per-row FP32 scale, so no tensor-wide amax pass precedes it, and the raw
 block-scaled GEMM whose result the consumer multiplies by `rs[t] * gs`.
 
-Built so far: `RowQ`, `row_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`.  The fused producers
-(`rms_emit`, `swiglu_emit`) and the delayed-scale column emitter (`col_emit`) are not built.
+Built so far: `RowQ`, `ColQ`, `row_emit`, `col_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`, `mm_col`.
+The fused producers (`rms_emit`, `swiglu_emit`) and `mom_acc` are not built.
 """
 import torch
 
@@ -22,6 +22,30 @@ class RowQ:
         self.d = torch.empty(R, C // 2, dtype=torch.uint8, device=dev)
         self.s = torch.empty(R * C // 16, dtype=torch.uint8, device=dev)
         self.rs = torch.empty(R, dtype=torch.float32, device=dev)
+
+
+class ColQ:
+    """Column operand of X [M, C]: X^T quantized along M -> data [C, M/2], swizzled scales
+    (llm-1b/emit.py:30-36)."""
+    __slots__ = ("d", "s")
+
+    def __init__(self, M, C, dev="cuda"):
+        self.d = torch.empty(C, M // 2, dtype=torch.uint8, device=dev)
+        self.s = torch.empty(C * M // 16, dtype=torch.uint8, device=dev)
+
+
+def col_emit(x, q: ColQ, amax_use, amax_cur, rng, sr=False, salt=0):
+    """RHT16 along the tokens + quantization of x^T with the delayed scale `amax_use`; records the
+    RHT-domain amax of x into `amax_cur` (float bits, atomicMax: zero it first) (llm-1b/emit.py:82-85).
+    `rng`: CUDA int32 words, rng[0] = SR seed, rng[1] = Hadamard sign bits."""
+    L.require_cuda(x, q.d, q.s, amax_use, amax_cur, rng)
+    M, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and M % 256 == 0 and C % 64 == 0
+    assert C % 128 == 0, C          # swizzled scale tiles of 128 columns are written whole
+    assert rng.element_size() == 4 and rng.numel() >= 2 and amax_cur.element_size() == 4
+    L.check(L.load().nvfp4_emit_cols(L.ptr(x), x.stride(0), M, C, L.ptr(q.d), L.ptr(q.s), L.ptr(amax_use), L.ptr(amax_cur),
+                                     int(bool(sr)), L.ptr(rng), salt & 0xFFFFFFFF, L.stream()), "emit_cols")
+    return q
 
 
 def row_emit(x, q: RowQ, rng, sr=False, salt=0):
@@ -83,6 +107,12 @@ def mm(ad, as_, bd, bs, out_dtype=torch.bfloat16):
     a = nvq.Q(ad.view(F4), as_.view(F8), one)
     b = nvq.Q(bd.view(F4), bs.view(F8), one)
     return nvq.mm(a, b, out_dtype=out_dtype, scale=False)[0]
+
+
+def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32):
+    """wgrad: dW_raw = Q(H dy)^T Q(H x) [N, K]; true = raw * gsA * gsB with gs = amax_use/2688
+    (llm-1b/emit.py:148-150)."""
+    return mm(a.d, a.s, b.d, b.s, out_dtype=out_dtype)
 
 
 def mm_row_w(q: RowQ, w: WQ):

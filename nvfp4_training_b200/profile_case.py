@@ -81,6 +81,12 @@ def main():
             rng = torch.tensor([1, 0], dtype=torch.int32, device="cuda")
             cases = cases + (("emit_rows_rn", lambda x: emit.row_emit(x, rq, None), 2.5625),
                              ("emit_rows_sr", lambda x: emit.row_emit(x, rq, rng, sr=True), 2.5625))
+            if a.M % 256 == 0:
+                cq = emit.ColQ(a.M, a.N)
+                use = torch.full((1,), 16.0, dtype=torch.float32, device="cuda")
+                cur = torch.zeros(1, dtype=torch.int32, device="cuda")
+                cases = cases + (("emit_cols_rn", lambda x: emit.col_emit(x, cq, use, cur, rng), 2.5625),
+                                 ("emit_cols_sr", lambda x: emit.col_emit(x, cq, use, cur, rng, sr=True), 2.5625))
         for name, fn, bpe in cases:
             us = timed(lambda: fn(nxt()), a.iters)
             out[name] = {"us": us, "gbs": n * bpe / us / 1e3}

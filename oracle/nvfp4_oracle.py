@@ -483,6 +483,41 @@ def emit_rows(x, seed=0, sr=False, salt=0):
     return pack_codes(codes), sbyte, rs
 
 
+def emit_cols(x, signs, amax_use, seed=0, sr=False, salt=0):
+    """Column operand with a delayed per-tensor scale (`col_emit`, llm-1b/emit.cu:287-341): x^T
+    quantized along the tokens after the 16-point RHT, the scale taken from `amax_use` (an RHT-domain
+    amax observed earlier), the current RHT-domain amax returned for the next use.
+    x: [M, C] float32 holding bf16 values, M % 64 == 0.  Returns (packed codes [C, M/2], scale bytes
+    [C, M/16] row-major, amax_cur float32).  Per 16-token block: sb = e4m3((m*inv)*(1/6)) with
+    inv = 2688/amax_use, k = inv/dec(sb), code = rn(v*k).  SR: the thread of (column c, 64-token
+    group g) starts an LCG at hash32(seed ^ salt ^ hash32(c*4099 + g)) and walks its four blocks in
+    token order, one step per pair of values."""
+    x = np.asarray(x, dtype=np.float32)
+    M, C = x.shape
+    assert M % 64 == 0
+    t = rht16_cols(x, signs)                                   # [C, M/16, 16], already x0.25
+    au = np.float32(amax_use)
+    inv = np.float32(FP4_E4M3) / au if au > 0 else np.float32(0)
+    m = np.abs(t).max(axis=2).astype(np.float32)               # [C, M/16]
+    amax_cur = np.float32(m.max()) if m.size else np.float32(0)
+    sarg = ((m * inv).astype(np.float32) * np.float32(np.float32(1.0) / np.float32(6.0))).astype(np.float32)
+    sbyte = e4m3_encode(sarg)
+    sd = e4m3_decode(sbyte).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        k = np.where(sd > 0, inv / np.where(sd > 0, sd, np.float32(1)), np.float32(0)).astype(np.float32)
+    codes = np.empty((C, M // 16, 16), dtype=np.uint8)
+    cols = np.arange(C, dtype=np.uint32)[:, None]
+    grps = np.arange(M // 64, dtype=np.uint32)[None, :]
+    state = hash32(np.uint32((seed if sr else 0) & 0xFFFFFFFF) ^ np.uint32(salt & 0xFFFFFFFF) ^ hash32(cols * np.uint32(4099) + grps))
+    for b in range(4):                                         # blocks of a 64-token group, in order
+        tb = t[:, b::4, :]                                     # [C, M/64, 16]
+        kb = k[:, b::4]
+        for half in range(2):
+            c8, state = _emit_pack8(tb[:, :, 8 * half:8 * half + 8], kb, sr, state)
+            codes[:, b::4, 8 * half:8 * half + 8] = c8
+    return pack_codes(codes.reshape(C, M)), sbyte, amax_cur
+
+
 def emit_rows_dequant(packed, sbyte, rs):
     """Values a consumer reconstructs from a row operand: code * block scale * rs[row]."""
     T = packed.shape[0]

@@ -79,6 +79,64 @@ def test_forward_through_raw_gemm_and_row_scales(emit):
     assert rel_fro(y, xd @ wd.T) <= 4e-3
 
 
+def _rng(seed, signs):
+    return torch.tensor([seed, signs], dtype=torch.int64, device="cuda").to(torch.int32)
+
+
+def _check_cols(q, ref, amax_cur, M, C):
+    codes, sbyte, cur = ref
+    assert np.array_equal(u8(q.d), codes)
+    assert np.array_equal(O.unswizzle_scales(u8(q.s), C, M // 16), sbyte)
+    assert amax_cur.view(torch.float32).item() == float(cur)
+
+
+@pytest.mark.parametrize("M,C,seed", [(256, 128, 0), (512, 384, 1), (2048, 256, 2)])
+@pytest.mark.parametrize("margin", [1.0, 1.25, 0.5])
+def test_col_emit_rn_bit_exact(emit, M, C, seed, margin):
+    """`margin` scales the delayed amax: 1.25 = the usual head-room, 0.5 = a stale amax that is too
+    small, so blocks saturate (both sides clamp)."""
+    signs = 0x3C5A
+    g = make_dy(seed + 40, M, C)
+    g[:16, 7] = 0.0                                          # a zero block in one column
+    au = np.float32(np.abs(O.rht16_cols(g, signs)).max() * np.float32(margin))
+    use = torch.tensor([float(au)], dtype=torch.float32, device="cuda")
+    cur = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = emit.col_emit(to_dev(g), emit.ColQ(M, C), use, cur, _rng(0, signs))
+    _check_cols(q, O.emit_cols(g, signs, au), cur, M, C)
+
+
+@pytest.mark.parametrize("seed,salt", [(1, 0), (0x12345678, 0xABC)])
+def test_col_emit_sr_bit_exact_with_the_reference_stream(emit, seed, salt):
+    M, C, signs = 1024, 256, 0xA6B1
+    g = make_dy(77, M, C)
+    au = np.float32(np.abs(O.rht16_cols(g, signs)).max() * np.float32(1.1))
+    use = torch.tensor([float(au)], dtype=torch.float32, device="cuda")
+    cur = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = emit.col_emit(to_dev(g), emit.ColQ(M, C), use, cur, _rng(seed, signs), sr=True, salt=salt)
+    _check_cols(q, O.emit_cols(g, signs, au, seed=seed, sr=True, salt=salt), cur, M, C)
+
+
+def test_wgrad_from_two_column_operands(emit):
+    """dW = (Q(H dy)^T Q(H x)) * gsA * gsB (llm-1b/emit.py:148-150): equal to the FP64 product of the
+    oracle's dequantized operands (FP32 accumulation tolerance), and close to dy^T x (the RHT cancels
+    in the product, so only quantization error remains)."""
+    M, N, K, signs = 1024, 256, 384, 0x9D2B
+    x, g = make_x(3, M, K, outliers=0), make_dy(4, M, N)
+    rng = _rng(5, signs)
+    ops = []
+    for t in (g, x):
+        au = np.float32(np.abs(O.rht16_cols(t, signs)).max())
+        use = torch.tensor([float(au)], dtype=torch.float32, device="cuda")
+        cur = torch.zeros(1, dtype=torch.int32, device="cuda")
+        q = emit.col_emit(to_dev(t), emit.ColQ(M, t.shape[1]), use, cur, rng)
+        codes, sbyte, _ = O.emit_cols(t, signs, au)
+        ops.append((q, au, O.dequant(codes, sbyte, au / np.float32(2688)).astype(np.float64)))
+    (qa, aa, da), (qb, ab, db) = ops
+    dw = emit.mm_col(qa, qb).cpu().numpy().astype(np.float64) * float(aa / np.float32(2688)) * float(ab / np.float32(2688))
+    assert rel_fro(dw, da @ db.T) <= 1e-5
+    assert rel_fro(dw, g.astype(np.float64).T @ x.astype(np.float64)) <= 0.25
+
+
 def test_row_emit_rejects_bad_arguments(emit):
     from nvfp4_training_b200 import _lib as L
     lib = L.load()
