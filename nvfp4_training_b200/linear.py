@@ -64,15 +64,16 @@ def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS):
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None, overwrite=False, qxt=None):
+               sr_mode=None, overwrite=False, qxt=None, am_gy=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
     returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
     rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding.
-    `qxt`: the transposed operand of x from `linear_fwd(..., keep_xt=True)`; x may then be None."""
+    `qxt`: the transposed operand of x from `linear_fwd(..., keep_xt=True)`; x may then be None.
+    `am_gy`: amax(gy) if the caller already has it."""
     gy = gy.contiguous()
-    ag = nvq.amax(gy)
+    ag = am_gy if am_gy is not None else nvq.amax(gy)
     if _tileable(gy):
         # both operands of gy from one pass over it
         qg, qgt = nvq.quant_rows_cols_rht(gy, signs, sr=True, seed=seed, seed_cols=seed_cols, am=ag, sr_mode=sr_mode)
