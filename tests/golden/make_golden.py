@@ -14,7 +14,9 @@ import sys
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/nvfp4-training")
+ref_root = sys.argv[1]
 sys.path.insert(0, os.path.join(ref_root, "small-model"))
 import model_ref  # noqa: E402
 
