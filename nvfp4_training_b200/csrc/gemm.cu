@@ -995,13 +995,15 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     // epilogue hand-off; 192 has two independent accumulators and handles any N; 128 as well, more bytes
     int pbn = 192;
     if (N % 256 == 0) {
-      // measured per-tile cost (us) of a CTA pair: 256-wide 2.98 + 0.346 per K tile, 192-wide 1.81 + 0.313;
-      // what decides is mostly how evenly the tile count divides over the SM pairs
+      // relative per-tile cost of a CTA pair fitted to measurements: 256-wide 2.98 + 0.346 per K tile, 192-wide
+      // 1.88 + 0.3255 (0.78 of the 256-wide tile at K = 2048, 0.89 at K = 11264); what decides is mostly how
+      // evenly the tile count divides over the SM pairs
       const long long ncl = sms / 2;
       const long long r256 = ((long long)(M / 256) * (N / 256) * splitk + ncl - 1) / ncl;
       const long long r192 = ((long long)(M / 256) * ((N + 191) / 192) * splitk + ncl - 1) / ncl;
-      if (r256 * (2.98 + 0.346 * per) <= r192 * (1.81 + 0.313 * per)) pbn = 256;
+      if (r256 * (2.98 + 0.346 * per) <= r192 * (1.88 + 0.3255 * per)) pbn = 256;
     }
+    if (g_pair_bn == 128 || g_pair_bn == 192 || (g_pair_bn == 256 && N % 256 == 0)) pbn = g_pair_bn;   // forced (tuning and tests)
     CUtensorMap ma, mb, msa, msb;
     if (!make_map(&ma, a, M, K / 2, lda, 128) || !make_sf_map(&msa, sa, M, K, 1) ||
         !make_map(&mb, b, N, K / 2, ldb, pbn / 2) || !make_sf_map(&msb, sb, N, K, pbn == 128 ? 1 : 2))
