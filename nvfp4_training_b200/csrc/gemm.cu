@@ -26,6 +26,10 @@
 // which measured 1-2 % faster on the large shapes (fewer issue slots and less power spent spinning).
 #define NVFP4_IDLE_WAIT mbar_wait_parked
 
+// 16-byte store of finished bf16 output with the streaming hint: the output is not read again by this
+// kernel and should not push operand tiles out of L2 (measured +3 % on 16384x11264x2048, neutral elsewhere)
+#define NVFP4_STORE_C16(ptr, v) __stcs(reinterpret_cast<uint4*>(ptr), v)
+
 namespace nvfp4 {
 
 constexpr int kBM = 128;            // rows of A per tile (UMMA M)
@@ -569,7 +573,7 @@ __device__ __forceinline__ void staged_store(const u32 (&r)[NCOLS], float alpha,
         uint4 v;
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                      : "r"(sw + (u32)row * ROWB + (((u32)ru ^ rswz) << 4)) : "memory");
-        *reinterpret_cast<uint4*>(cb + (long long)row * ldc + c * CPR + ru * 8) = v;
+        NVFP4_STORE_C16(cb + (long long)row * ldc + c * CPR + ru * 8, v);
       }
       __syncwarp();
     }
