@@ -433,7 +433,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--microbatch", type=int, default=16384)
+    ap.add_argument("--microbatch", type=int, default=65536,
+                    help="rows per microbatch (default: the whole local batch; 148.0 ms per step at N = 1 against 150.8 with 32768 and 156.1 with 16384)")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (not a valid bench number)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm-sms", type=int, default=None,
