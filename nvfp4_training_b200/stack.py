@@ -106,6 +106,16 @@ class LinearStack:
             self.blocks.append([self._make_proj("head", cfg.vocab, cfg.d, 0.02, lid, gen)])
             lid += 1
         self.n_proj = lid
+        # the weight gradients of a block live in one flat FP32 buffer, so that the block's
+        # all-reduce is one collective instead of one per projection
+        self.gw_flat = []
+        for projs in self.blocks:
+            flat = torch.zeros(sum(p.N * p.K for p in projs), dtype=torch.float32, device=self.device)
+            off = 0
+            for p in projs:
+                p.gw = flat[off:off + p.N * p.K].view(p.N, p.K)
+                off += p.N * p.K
+            self.gw_flat.append(flat)
         # synthetic pools: X ~ N(0,1) bf16, dY ~ Student-t(3) * 1e-3 bf16, one per projection kind
         gen_in = torch.Generator(device=self.device).manual_seed(seed + 1000)
         self.x_pool, self.gy_pool = {}, {}
@@ -127,7 +137,7 @@ class LinearStack:
         w = torch.empty(N, K, device=self.device)
         torch.nn.init.trunc_normal_(w, std=std, a=-3 * std, b=3 * std, generator=gen)
         p.w = w.bfloat16()
-        p.gw = torch.zeros(N, K, dtype=torch.float32, device=self.device)
+        p.gw = None      # a view of the block's flat gradient buffer, set by the constructor
         p.q = p.qt = p.am_x = p.y = p.gx = None
         return p
 
@@ -219,6 +229,7 @@ class LinearStack:
             for projs in self.blocks:
                 self._fwd_block(projs)
         works = []
+        nblk = len(self.blocks)
         for i, projs in enumerate(reversed(self.blocks)):
             if self.use_graphs and self.graphs_bwd is not None:
                 (self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
@@ -229,7 +240,7 @@ class LinearStack:
                 ev.record(cur)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ev)
-                    allreduce_sum_([p.gw for p in projs], self.group)
+                    allreduce_sum_([self.gw_flat[nblk - 1 - i]], self.group)
         return works
 
     def step(self, n_micro, do_allreduce):
