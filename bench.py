@@ -329,7 +329,7 @@ def run_ours(args):
     plan = shard_plan(world, rank, GLOBAL_TOKENS, args.microbatch)
     mb, n_micro = plan["microbatch"], plan["n_micro"]
     stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=rank, use_graphs=not args.no_graphs,
-                        comm_sms=args.comm_sms if world > 1 else 0)
+                        comm_sms=args.comm_sms if world > 1 else 0, ar_blocks=args.ar_blocks)
     if not args.no_graphs:
         stack.capture()
     do_ar = world > 1
@@ -437,6 +437,7 @@ def main():
                     help="rows per microbatch (default: the whole local batch; 148.0 ms per step at N = 1 against 150.8 with 32768 and 156.1 with 16384)")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (not a valid bench number)")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs left free for NCCL during backward when N > 1 (default: 32 at N >= 8, else 16)")
     ap.add_argument("--no-cpu", action="store_true")

@@ -87,8 +87,9 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1):
         self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
+        self.ar_blocks = max(1, ar_blocks)   # transformer blocks per gradient all-reduce
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
         self.sr_mode = sr_mode       # gradients: hardware cvt.rs stochastic rounding, counter-based random words
         self.use_graphs = use_graphs
@@ -106,16 +107,23 @@ class LinearStack:
             self.blocks.append([self._make_proj("head", cfg.vocab, cfg.d, 0.02, lid, gen)])
             lid += 1
         self.n_proj = lid
-        # the weight gradients of a block live in one flat FP32 buffer, so that the block's
-        # all-reduce is one collective instead of one per projection
-        self.gw_flat = []
-        for projs in self.blocks:
+        # the weight gradients of `ar_blocks` consecutive blocks live in one flat FP32 buffer, so that
+        # their all-reduce is one collective (the LM head keeps a buffer of its own: it is first in
+        # the backward order and its collective should start at once)
+        self.gw_flat, self.ar_after = [], {}       # ar_after[block index] = flat buffer to reduce once that block is done
+        nb = cfg.layers
+        groups = [list(range(b, min(b + self.ar_blocks, nb))) for b in range(0, nb, self.ar_blocks)]
+        if cfg.lm_head:
+            groups.append([nb])
+        for grp in groups:
+            projs = [p for b in grp for p in self.blocks[b]]
             flat = torch.zeros(sum(p.N * p.K for p in projs), dtype=torch.float32, device=self.device)
             off = 0
             for p in projs:
                 p.gw = flat[off:off + p.N * p.K].view(p.N, p.K)
                 off += p.N * p.K
             self.gw_flat.append(flat)
+            self.ar_after[grp[0]] = flat           # backward walks the blocks downwards: the group's lowest block is last
         # synthetic pools: X ~ N(0,1) bf16, dY ~ Student-t(3) * 1e-3 bf16, one per projection kind
         gen_in = torch.Generator(device=self.device).manual_seed(seed + 1000)
         self.x_pool, self.gy_pool = {}, {}
@@ -235,12 +243,12 @@ class LinearStack:
                 (self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
             else:
                 self._bwd_block(projs, first=first)
-            if last and do_allreduce:
+            if last and do_allreduce and (nblk - 1 - i) in self.ar_after:
                 ev = torch.cuda.Event()
                 ev.record(cur)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ev)
-                    allreduce_sum_([self.gw_flat[nblk - 1 - i]], self.group)
+                    allreduce_sum_([self.ar_after[nblk - 1 - i]], self.group)
         return works
 
     def step(self, n_micro, do_allreduce):
