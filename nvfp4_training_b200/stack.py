@@ -137,6 +137,7 @@ class LinearStack:
         self._bump_seeds()
         self.comm_stream = torch.cuda.Stream(device=self.device)
         self.graphs_fwd = self.graphs_bwd = None
+        self.graph_refresh = None
         self.launches_per_micro = 0
 
     def _make_proj(self, name, N, K, std, lid, gen):
@@ -158,7 +159,11 @@ class LinearStack:
         self.micro_count += 1
 
     def refresh_weights(self):
-        """Quantize every weight once per optimizer step (the small-model/fp4torch.py:71-84 scheme)."""
+        """Quantize every weight once per optimizer step (the small-model/fp4torch.py:71-84 scheme).
+        After `capture()` the 2 x 81 launches are one graph replay."""
+        if self.graph_refresh is not None:
+            self.graph_refresh.replay()
+            return
         for projs in self.blocks:
             for p in projs:
                 if p.q is None:
@@ -218,6 +223,10 @@ class LinearStack:
                     store.append(g)
         finally:
             lib.nvfp4_gemm_set_sm_budget(0)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=pool):
+            self.refresh_weights()           # buffers exist already: the in-place form is captured
+        self.graph_refresh = g
         torch.cuda.synchronize()
 
     def kernels_per_microbatch(self):
