@@ -56,19 +56,42 @@ def quant_cols_rht(x, signs, sr=False, seed=0, amax=None):
     return Q(d, s, a, 4.0)
 
 
-def quant_w2d(w):
-    """w fp32 [N, K] -> (Q, Q^T) (llm-1b/fp4ops.py:52-61)."""
+def quant_rows_cols_rht(x, signs, sr=False, seed=0, seed_cols=0, amax=None):
+    """Both operands of one activation / gradient from a single pass over it: what
+    `quant_rows(x, sr, seed, amax)` and `quant_cols_rht(x, signs, sr, seed_cols, amax)` return
+    (llm-1b/fp4ops.py:30-49), bit for bit.  Needs M % 128 == 0 and C % 64 == 0."""
+    L.require_cuda(x)
+    M, C = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and M % 128 == 0 and C % 64 == 0, (M, C)
+    a = amax_of(x) if amax is None else amax
+    dev = x.device
+    dr = torch.empty(M, C // 2, dtype=torch.uint8, device=dev)
+    sr_ = torch.empty(M, C // 16, dtype=torch.uint8, device=dev)
+    dc = torch.empty(C, M // 2, dtype=torch.uint8, device=dev)
+    sc = torch.empty(C, M // 16, dtype=torch.uint8, device=dev)
+    s_r, s_r_dev = L.seed_args(seed)
+    s_c, s_c_dev = L.seed_args(seed_cols)
+    L.check(L.load().nvfp4_quant_tile(L.ptr(x), x.stride(0), M, C, L.ptr(dr), L.ptr(sr_), L.ptr(dc), L.ptr(sc), L.SCALES_LINEAR,
+                                      L.ptr(a), None, None, signs & 0xFFFF, SR_MODE if sr else L.ROUND_NEAREST, s_r, s_c,
+                                      s_r_dev, s_c_dev, L.stream()), "quant_tile")
+    return Q(dr, sr_, a), Q(dc, sc, a, 4.0)
+
+
+def quant_w2d(w, out=None):
+    """w fp32 [N, K] -> (Q, Q^T) (llm-1b/fp4ops.py:52-61).  `out`: a pair returned earlier, rewritten in
+    place (its amax included), so that holders of the buffers see the refreshed weight."""
     L.require_cuda(w)
     N, K = w.shape
     assert w.dtype == torch.float32 and N % 16 == 0 and K % 16 == 0
-    a = amax_of(w)
-    q = torch.empty(N, K // 2, dtype=torch.uint8, device=w.device)
-    s = torch.empty(N, K // 16, dtype=torch.uint8, device=w.device)
-    qt = torch.empty(K, N // 2, dtype=torch.uint8, device=w.device)
-    st = torch.empty(K, N // 16, dtype=torch.uint8, device=w.device)
-    L.check(L.load().nvfp4_quant_w2d(L.ptr(w.contiguous()), L.DTYPE_FP32, N, K, L.ptr(q), L.ptr(s), L.ptr(qt), L.ptr(st),
-                                     L.SCALES_LINEAR, L.ptr(a), None, L.stream()), "quant_w2d")
-    return Q(q, s, a), Q(qt, st, a)
+    if out is None:
+        mk = lambda r, c: torch.empty(r, c, dtype=torch.uint8, device=w.device)
+        a = torch.empty(1, dtype=torch.float32, device=w.device)
+        out = (Q(mk(N, K // 2), mk(N, K // 16), a), Q(mk(K, N // 2), mk(K, N // 16), a))
+    qw, qwt = out
+    qw.amax.copy_(amax_of(w))
+    L.check(L.load().nvfp4_quant_w2d(L.ptr(w.contiguous()), L.DTYPE_FP32, N, K, L.ptr(qw.d), L.ptr(qw.s), L.ptr(qwt.d),
+                                     L.ptr(qwt.s), L.SCALES_LINEAR, L.ptr(qw.amax), None, L.stream()), "quant_w2d")
+    return qw, qwt
 
 
 def gemm(a: Q, b: Q, out=None, splitk=1):

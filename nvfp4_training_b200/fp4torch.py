@@ -1,93 +1,95 @@
-"""The NVFP4 linear layer as torch custom ops (opaque to torch.compile): the `fp4torch` flavour of the
-reference (small-model/fp4torch.py) on this library's `fp4ops`.
+"""The NVFP4 linear layer behind torch custom ops, i.e. the surface small-model/fp4torch.py gives a
+compiled model: `torch.ops.nvfp4.fwd`, `.bwd`, `.linear` (with autograd) and `FP4Weight`.
 
-  fprop : y  = Q_rn(x)  @ Q2d(W)^T                         (nvfp4::fwd,    fp4torch.py:19-23)
-  dgrad : dx = Q_sr(dy) @ Q2d(W)                           (nvfp4::bwd,    fp4torch.py:31-38)
-  wgrad : dW = Q_sr(H dy)^T @ Q_rn(H x), FP32, split-K 16
-  nvfp4::linear(x, w, wd, ws, wtd, wts, wamax) with autograd (fp4torch.py:46-68); `FP4Weight` holds the
-  per-optimizer-step quantized copies of an FP32 master weight (fp4torch.py:71-84).
+Recipe (small-model/fp4torch.py:19-38):  y = Q_rn(x) @ Q2d(W)^T;  dx = Q_sr(dy) @ Q2d(W);
+dW = Q_sr(H dy)^T @ Q_rn(H x) accumulated in FP32 with split-K 16.  Here the two operands of dy come
+from one pass over dy when its shape allows (`fp4ops.quant_rows_cols_rht`), and `FP4Weight.refresh`
+rewrites its buffers in place instead of copying into them.
 
-Seeds follow the reference: a process-wide counter times 2654435761 for stochastic rounding, and a
-fresh 16-bit Hadamard sign vector from Python's `random` per backward call.
+Randomness follows the reference: stochastic-rounding seeds are a process-wide counter times
+2654435761, the 16 Hadamard sign bits come from Python's `random` once per backward call.
 """
+import itertools
 import random
 
 import torch
 
 from . import fp4ops as F
 
-_ctr = [0]
+_LIB = torch.library.Library("nvfp4", "DEF")
+_LIB.define("fwd(Tensor x, Tensor wd, Tensor ws, Tensor wamax) -> Tensor")
+_LIB.define("bwd(Tensor g, Tensor x, Tensor wtd, Tensor wts, Tensor wamax) -> (Tensor, Tensor)")
+_LIB.define("linear(Tensor x, Tensor w, Tensor wd, Tensor ws, Tensor wtd, Tensor wts, Tensor wamax) -> Tensor")
+
+_calls = itertools.count(1)
 
 
-def _seed():
-    _ctr[0] += 1
-    return (_ctr[0] * 2654435761) & 0xFFFFFFFF
+def _next_seed():
+    return (next(_calls) * 2654435761) & 0xFFFFFFFF
 
 
-@torch.library.custom_op("nvfp4::fwd", mutates_args=())
-def fp4_fwd(x: torch.Tensor, wd: torch.Tensor, ws: torch.Tensor, wamax: torch.Tensor) -> torch.Tensor:
-    x2 = x.reshape(-1, x.shape[-1])
-    y = F.gemm(F.quant_rows(x2), F.Q(wd, ws, wamax))
+def _rows(t):
+    """[..., C] -> contiguous [R, C]."""
+    return t.reshape(-1, t.shape[-1]).contiguous()
+
+
+def _fprop(x, wd, ws, wamax):
+    y = F.gemm(F.quant_rows(_rows(x)), F.Q(wd, ws, wamax))
     return y.reshape(*x.shape[:-1], wd.shape[0])
 
 
-@fp4_fwd.register_fake
-def _(x, wd, ws, wamax):
-    return x.new_empty(*x.shape[:-1], wd.shape[0])
-
-
-@torch.library.custom_op("nvfp4::bwd", mutates_args=())
-def fp4_bwd(g: torch.Tensor, x: torch.Tensor, wtd: torch.Tensor, wts: torch.Tensor,
-            wamax: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    g2 = g.reshape(-1, g.shape[-1]).contiguous()
-    x2 = x.reshape(-1, x.shape[-1]).contiguous()
-    dx = F.gemm(F.quant_rows(g2, sr=True, seed=_seed()), F.Q(wtd, wts, wamax))
+def _grads(g, x, wtd, wts, wamax):
+    g2, x2 = _rows(g), _rows(x)
     signs = random.getrandbits(16)
-    dw = F.gemm(F.quant_cols_rht(g2, signs, sr=True, seed=_seed()), F.quant_cols_rht(x2, signs), splitk=16)
-    return dx.reshape(x.shape), dw
+    seed_rows, seed_cols = _next_seed(), _next_seed()
+    if g2.shape[0] % 128 == 0 and g2.shape[1] % 64 == 0:
+        qg, qgt = F.quant_rows_cols_rht(g2, signs, sr=True, seed=seed_rows, seed_cols=seed_cols)
+    else:
+        qg = F.quant_rows(g2, sr=True, seed=seed_rows)
+        qgt = F.quant_cols_rht(g2, signs, sr=True, seed=seed_cols)
+    dx = F.gemm(qg, F.Q(wtd, wts, wamax)).reshape(x.shape)
+    dw = F.gemm(qgt, F.quant_cols_rht(x2, signs), splitk=16)
+    return dx, dw
 
 
-@fp4_bwd.register_fake
-def _(g, x, wtd, wts, wamax):
-    return x.new_empty(x.shape), g.new_empty(g.shape[-1], x.shape[-1], dtype=torch.float32)
+torch.library.impl(_LIB, "fwd", "CUDA")(_fprop)
+torch.library.impl(_LIB, "bwd", "CUDA")(_grads)
+torch.library.impl(_LIB, "linear", "CUDA")(lambda x, w, wd, ws, wtd, wts, wamax: _fprop(x, wd, ws, wamax))
+
+torch.library.register_fake("nvfp4::fwd")(lambda x, wd, ws, wamax: x.new_empty(*x.shape[:-1], wd.shape[0]))
+torch.library.register_fake("nvfp4::bwd")(
+    lambda g, x, wtd, wts, wamax: (x.new_empty(x.shape), g.new_empty(g.shape[-1], x.shape[-1], dtype=torch.float32)))
+torch.library.register_fake("nvfp4::linear")(
+    lambda x, w, wd, ws, wtd, wts, wamax: x.new_empty(*x.shape[:-1], w.shape[0]))
+
+fp4_fwd, fp4_bwd, fp4_linear = torch.ops.nvfp4.fwd, torch.ops.nvfp4.bwd, torch.ops.nvfp4.linear
 
 
-@torch.library.custom_op("nvfp4::linear", mutates_args=())
-def fp4_linear(x: torch.Tensor, w: torch.Tensor, wd: torch.Tensor, ws: torch.Tensor, wtd: torch.Tensor,
-               wts: torch.Tensor, wamax: torch.Tensor) -> torch.Tensor:
-    return fp4_fwd(x, wd, ws, wamax)
-
-
-@fp4_linear.register_fake
-def _(x, w, wd, ws, wtd, wts, wamax):
-    return x.new_empty(*x.shape[:-1], w.shape[0])
-
-
-def _setup(ctx, inputs, output):
-    x, w, wd, ws, wtd, wts, wamax = inputs
+def _save(ctx, inputs, output):
+    x, _w, _wd, _ws, wtd, wts, wamax = inputs
     ctx.save_for_backward(x, wtd, wts, wamax)
 
 
-def _backward(ctx, g):
-    x, wtd, wts, wamax = ctx.saved_tensors
-    dx, dw = fp4_bwd(g.contiguous(), x, wtd, wts, wamax)
-    return dx, dw, None, None, None, None, None
+def _linear_backward(ctx, g):
+    dx, dw = fp4_bwd(g.contiguous(), *ctx.saved_tensors)
+    return (dx, dw) + (None,) * 5
 
 
-torch.library.register_autograd("nvfp4::linear", _backward, setup_context=_setup)
+torch.library.register_autograd("nvfp4::linear", _linear_backward, setup_context=_save)
 
 
 class FP4Weight:
-    """Quantized W / W^T copies of an FP32 master weight, refreshed once per optimizer step."""
+    """Quantized copies of an FP32 master weight and of its transpose, refreshed once per optimizer
+    step (small-model/fp4torch.py:71-84).  Attributes: wd, ws (W), wtd, wts (W^T), amax."""
 
     def __init__(self, w):
         self.w = w
+        self._q = None
         self.refresh()
 
     @torch.no_grad()
     def refresh(self):
-        q, qt = F.quant_w2d(self.w.data)
-        if not hasattr(self, "wd"):
-            self.wd, self.ws, self.wtd, self.wts, self.amax = q.d, q.s, qt.d, qt.s, q.amax
-        else:
-            self.wd.copy_(q.d); self.ws.copy_(q.s); self.wtd.copy_(qt.d); self.wts.copy_(qt.s); self.amax.copy_(q.amax)
+        self._q = F.quant_w2d(self.w.data, out=self._q)      # in place after the first call
+        qw, qwt = self._q
+        self.wd, self.ws, self.wtd, self.wts, self.amax = qw.d, qw.s, qwt.d, qwt.s, qw.amax
+        return self

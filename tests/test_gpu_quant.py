@@ -267,6 +267,24 @@ def test_tile_quantizer_single_outputs_strided_input_and_device_seeds(mods):
     check_nvq(qc, c[0], c[1], c[2], 256, 256)
 
 
+def test_fp4ops_fused_operands_equal_the_separate_calls(mods):
+    """`fp4ops.quant_rows_cols_rht` (row-major scales, fp4k random stream) against `fp4ops.quant_rows` +
+    `fp4ops.quant_cols_rht`, and a weight refreshed in place."""
+    _, fp4ops, _ = mods
+    g = to_dev(make_dy(31, 256, 192))
+    for sr in (False, True):
+        a = fp4ops.quant_rows(g, sr=sr, seed=3)
+        b = fp4ops.quant_cols_rht(g, 0x1234, sr=sr, seed=4)
+        fa, fb = fp4ops.quant_rows_cols_rht(g, 0x1234, sr=sr, seed=3, seed_cols=4)
+        assert torch.equal(fa.d, a.d) and torch.equal(fa.s, a.s) and torch.equal(fb.d, b.d) and torch.equal(fb.s, b.s)
+        assert fb.k == 4.0 and torch.equal(fa.amax, a.amax)
+    w = torch.randn(128, 256, device="cuda")
+    q = fp4ops.quant_w2d(w)
+    ref = fp4ops.quant_w2d(w * 2)
+    same = fp4ops.quant_w2d(w * 2, out=q)
+    assert same[0] is q[0] and torch.equal(q[0].d, ref[0].d) and torch.equal(q[1].s, ref[1].s) and torch.equal(q[0].amax, ref[0].amax)
+
+
 def test_tile_quantizer_rejects_bad_shapes(mods):
     nvq, _, L = mods
     lib = L.load()
