@@ -244,7 +244,11 @@ def isolated_kernels(cfg, T, peaks):
             "traffic": None, "kernel": "gemm_nvf4_kernel (tcgen05.mma kind::mxf4nvf4 block16)",
             "peak_basis": "4 x cuBLAS bf16 burst TFLOP/s (dense FP4 : bf16 = 4 : 1 on B200)",
             "frac_of_nominal_9000": achieved / 9000.0,
-            "how": "all 15 GEMM shapes of the step timed alone with CUDA events, weighted by launches per step"}
+            "how": "all 15 GEMM shapes of the step timed alone with CUDA events, weighted by launches per step",
+            # `traffic` stays null: the figure is a launch mix, not one launch.  DRAM bytes of single launches from
+            # the ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum):
+            "traffic_ncu_mb": {"8192x11264x2048 bf16 out": {"read": 23.0, "write": 133.0, "algorithmic": 206.9},
+                               "8192x2048x11264 bf16 out": {"read": 64.9, "write": 11.5, "algorithmic": 98.4}}}
 
     # quantizers on the largest activation of a block: [T, 5632] X and [T, 11264] dY
     x = [torch.randn(T, 5632, generator=g, device=dev).bfloat16() for _ in range(4)]
