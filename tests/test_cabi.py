@@ -53,6 +53,20 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_gemm(p, p, 64, p, p, 64, p, 1, 128, 128, 128, 100, 0, None, None, 1.0, 1.0, 0, 1, None, None) == -2
     assert lib.nvfp4_gemm_linear(p, p, 64, 8, p, p, 64, 8, p, 1, 128, 128, 128, 128, 0, None, None, 1.0, 1.0, 0, 1,
                                  None, 0, None, None) == -6
+    # tile quantizer and operand emitters
+    assert lib.nvfp4_quant_tile(p, 128, 128, 128, None, None, None, None, 0, p, None, None, 0, 0, 0, 0, None, None, None) == -1
+    assert lib.nvfp4_quant_tile(p, 128, 100, 128, p, p, p, p, 0, p, None, None, 0, 0, 0, 0, None, None, None) == -2
+    assert lib.nvfp4_quant_tile(p, 192, 128, 192, p, p, p, p, 0, p, None, None, 0, 0, 0, 0, None, None, None) == -2   # swizzled: C % 128
+    assert lib.nvfp4_quant_tile(p, 128, 128, 128, p, p, p, p, 0, p, None, None, 0, 7, 0, 0, None, None, None) == -4
+    assert lib.nvfp4_quant_tile(ctypes.c_void_p((1 << 20) + 4), 128, 128, 128, p, p, p, p, 0, p, None, None, 0, 0, 0, 0,
+                                None, None, None) == -3
+    assert lib.nvfp4_quant_tile_status(None, 0) == -1
+    assert lib.nvfp4_emit_rows(p, 384, 128, 384, p, p, p, 0, None, 0, None) == -2          # C % 256
+    assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, p, 1, None, 0, None) == -1          # SR needs the device seed
+    assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, None, 0, None, 0, None) == -1
+    assert lib.nvfp4_emit_cols(p, 128, 128, 128, p, p, p, p, 0, None, 0, None) == -1       # rng carries the sign bits
+    assert lib.nvfp4_emit_cols(p, 192, 128, 192, p, p, p, p, 0, p, 0, None) == -2          # C % 128
+    assert lib.nvfp4_emit_cols(p, 128, 64, 128, p, p, p, p, 0, p, 0, None) == -2           # M % 128
     assert lib.nvfp4_gemm_linear_workspace_bytes(128, 256, 1024) == (128 + 256) * 64
     assert lib.nvfp4_gemm_force_tile_n(64) == -4 and lib.nvfp4_gemm_force_tile_n(448) == 0 and lib.nvfp4_gemm_force_tile_n(0) == 0
 
