@@ -73,9 +73,16 @@ def quant_cols_rht(x, signs, sr=False, seed=0, am=None, sr_mode=None):
     d = torch.empty(C, M // 2, dtype=torch.uint8, device=x.device)
     s = torch.empty(C * M // 16, dtype=torch.uint8, device=x.device)
     gs = _new_gs(am)
-    L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gs),
-                                          signs & 0xFFFF, (sr_mode or SR_MODE) if sr else L.ROUND_NEAREST, *L.seed_args(seed),
-                                          L.stream()), "quant_cols_rht")
+    mode = (sr_mode or SR_MODE) if sr else L.ROUND_NEAREST
+    if M % 128 == 0:
+        # the TMA-staged tile kernel with only the transposed output: same bits, faster than the register-tiled kernel
+        host_seed, dev_seed = L.seed_args(seed)
+        L.check(L.load().nvfp4_quant_tile(L.ptr(x), C, M, C, None, None, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am),
+                                          None, L.ptr(gs), signs & 0xFFFF, mode, 0, host_seed, None, dev_seed, L.stream()),
+                "quant_tile")
+    else:
+        L.check(L.load().nvfp4_quant_cols_rht(L.ptr(x), M, C, L.ptr(d), L.ptr(s), L.SCALES_SWIZZLED, L.ptr(am), L.ptr(gs),
+                                              signs & 0xFFFF, mode, *L.seed_args(seed), L.stream()), "quant_cols_rht")
     return Q(d.view(torch.float4_e2m1fn_x2), s.view(torch.float8_e4m3fn), gs)
 
 
