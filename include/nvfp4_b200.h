@@ -239,7 +239,10 @@ int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, long long ld
  *            rejected with NVFP4_ERR_TOO_LARGE before anything is launched
  *   cost     every GPU on which the library is loaded holds those 8 MiB until the process exits
  *   first call on a device: looks up the array's device address (cudaGetSymbolAddress) with that
- *            device current; make this first call outside any stream capture
+ *            device current; make this first call outside any stream capture.  The first launch of
+ *            each kernel variant a shape selects also makes the CUDA runtime load that kernel and set
+ *            its shared-memory attribute, which may reserve driver memory once: the guarantee of no
+ *            allocation holds from the second call with a given shape class on
  *   sharing  all calls on a device use the same array, which keeps the previous call's bytes (each
  *            call overwrites what it reads, nothing has to start at zero); two calls whose kernels
  *            can overlap on the GPU -- different streams without ordering -- race on it
@@ -251,6 +254,16 @@ int nvfp4_gemm_linear_noalloc(const void* a, const void* sa, long long lda, long
                               void* c, int c_dtype, long long ldc, int M, int N, int K,
                               int alpha_mode, const float* pa, const float* pb, float ka, float kb,
                               int accumulate, int splitk, int* status, void* stream);
+
+/*
+ * Self-test of the bounded waits: launches one CTA that waits on a barrier nobody arrives on, with a
+ * limit of limit_us microseconds (1..1000), and ORs into *status (device int, zeroed by the caller)
+ * bit 0 when the limited wait gave up, bit 1 when the CTA's second warp left through the abort flag,
+ * and in bits 8.. the microseconds the first warp waited.  parked != 0 exercises the sleeping form of
+ * the wait.  The kernel has no copies in flight and always terminates.  No reference counterpart (the
+ * reference kernels have no waits).
+ */
+int nvfp4_selftest_wait_timeout(unsigned limit_us, int parked, int* status, void* stream);
 
 #ifdef __cplusplus
 }

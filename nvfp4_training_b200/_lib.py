@@ -41,6 +41,7 @@ SIGNATURES = {
     "nvfp4_gemm_linear": (_i, [_vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f,
                                _i, _i, _vp, _sz, _vp, _vp]),
     "nvfp4_gemm_linear_noalloc_max_scratch": (_sz, []),
+    "nvfp4_selftest_wait_timeout": (_i, [_u, _i, _vp, _vp]),
     "nvfp4_gemm_linear_noalloc": (_i, [_vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f,
                                        _i, _i, _vp, _vp]),
 }
@@ -107,9 +108,15 @@ def status_word(device):
 
 
 def check_status(device=None):
-    """Synchronising check of the GEMM status word; raises if any CTA gave up waiting."""
+    """Synchronising check of the status words of the GEMM and of the tile quantizer on `device`;
+    raises if any CTA gave up waiting."""
     dev = torch.cuda.current_device() if device is None else device
     code = int(status_word(dev).item())
     if code:
         status_word(dev).zero_()
         raise Nvfp4Error(f"GEMM pipeline wait expired (role code {code})")
+    qcode = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        check(load().nvfp4_quant_tile_status(ctypes.byref(qcode), 1), "quant_tile_status")
+    if qcode.value:
+        raise Nvfp4Error(f"tile quantizer pipeline wait expired (role code {qcode.value})")

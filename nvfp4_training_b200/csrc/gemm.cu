@@ -70,9 +70,6 @@ struct GemmParams {
   int atomic;         // 1: add into C with FP32 atomics
   int splitk;         // number of K slices
   int ktiles_per_split;
-#ifdef NVFP4_GEMM_DEBUG
-  int dbg;            // development switches: 1 no stores, 2 no scale copies, 4 no MMAs, 8 no operand loads
-#endif
 };
 
 // ---------------------------------------------------------------------------------------- PTX wrappers
@@ -215,14 +212,9 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int krem = p.K - kt * kBK;
         const u32 sf_bytes = krem >= kBK ? 2048u : (u32)(krem >> 6) * 512u;
         if (elect_one()) {
-#ifdef NVFP4_GEMM_DEBUG
-          if (p.dbg & 8) mbar_arrive_expect_tx(bar, sf_bytes * (1 + BN / 128)); else
-#endif
-          {
           mbar_arrive_expect_tx(bar, (u32)(C::kABytes + C::kBBytes) + sf_bytes * (1 + BN / 128));
           tma_load_2d(st_addr, &map_a, x, ya, bar);
           tma_load_2d(st_addr + C::kABytes, &map_b, x, yb, bar);
-          }
           bulk_load(st_addr + C::kABytes + C::kBBytes, sfa, sf_bytes, bar);
 #pragma unroll
           for (int h = 0; h < BN / 128; h++)
@@ -263,9 +255,6 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (elect_one()) {
           if (krem >= kBK) {
             // scale tiles of the four K chunks: shared memory -> tensor memory
-#ifdef NVFP4_GEMM_DEBUG
-            if (!((p.dbg & 2) && accum))
-#endif
 #pragma unroll
             for (int j = 0; j < 4; j++) {
               tc_cp_sf(sfa_t + 4 * j, pack64(sfa_lo + 32 * j, kDescHiSF));
@@ -274,13 +263,7 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_cp_sf(sfb_t + (BN / 32) * j + 4 * h, pack64(sfb_lo + 128 * h + 32 * j, kDescHiSF));
             }
             // four MMAs, each 64 FP4 values = 32 bytes further along K inside the 128-byte swizzle row
-#ifdef NVFP4_GEMM_DEBUG
-            if (!((p.dbg & 4) && accum))
-#endif
             tc_mma_nvf4(d_tmem, pack64(a_lo, kDescHiAB), pack64(b_lo, kDescHiAB), idesc, sfa_t, sfb_t, accum);
-#ifdef NVFP4_GEMM_DEBUG
-            if (!(p.dbg & 4))
-#endif
 #pragma unroll
             for (int j = 1; j < 4; j++)
               tc_mma_nvf4(d_tmem, pack64(a_lo + 2 * j, kDescHiAB), pack64(b_lo + 2 * j, kDescHiAB), idesc, sfa_t + 4 * j,
@@ -339,9 +322,6 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
       const long long row = (long long)mt * kBM + quad * 32 + lane;
       const long long col = (long long)nt * BN + half * kEpiCols;
-#ifdef NVFP4_GEMM_DEBUG
-      if (p.dbg & 1) { if (r[0] == 0x12345678u && r[kEpiCols - 1] == 0x9abcdef0u) *static_cast<u32*>(p.c) = r[5]; } else
-#endif
       if (p.c_fp32) {
         float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
         if (p.atomic) {
@@ -500,10 +480,6 @@ struct PairParams {
   int atomic;
   int splitk;
   int ktiles_per_split;
-#ifdef NVFP4_GEMM_DEBUG
-  int dbg;
-  unsigned long long* prof;   // [16] clock64 sums of cluster 0 / leader: see NVFP4_PROF uses
-#endif
 };
 
 // Convert, scale and store the NCOLS accumulator values each lane holds for its row (32 rows per warp,
@@ -580,13 +556,6 @@ __device__ __forceinline__ void staged_store(const u32 (&r)[NCOLS], float alpha,
   }
 }
 
-#ifdef NVFP4_GEMM_DEBUG
-#define NVFP4_PROF_T0() long long _t0 = clock64()
-#define NVFP4_PROF_ADD(slot) { long long _t1 = clock64(); prof_acc[slot] += (unsigned long long)(_t1 - _t0); _t0 = _t1; }
-#else
-#define NVFP4_PROF_T0()
-#define NVFP4_PROF_ADD(slot)
-#endif
 
 // Work item -> (row tile, column tile, K slice) of the pair kernel.  Tiles are walked in bands of
 // kBand tile columns, row by row inside a band: the clusters of one wave then cover a roughly square
@@ -660,10 +629,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     int stage = 0; u32 phase = 0;
     u32 st_addr = smem_base;
     bool ok = true;
-#ifdef NVFP4_GEMM_DEBUG
-    unsigned long long prof_acc[4] = {0, 0, 0, 0};
-#endif
-    NVFP4_PROF_T0();
     for (int w = cid; w < num_work && ok; w += ncl) {
       int mt, nt, z;
       decode_tile(w, tiles_m, tiles_n, mt, nt, z);
@@ -673,7 +638,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int za = mt * 2 + (int)rank, zb = (nt * BN) >> 7;
       for (int kt = kt0; kt < kt1; kt++) {
         if (!__all_sync(0xffffffffu, NVFP4_IDLE_WAIT(empty0 + 8 * stage, phase ^ 1u, abort_flag))) { ok = false; break; }
-        NVFP4_PROF_ADD(0);        // producer: waiting for a free stage
         if (elect_one()) {
           if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * stage, C::kTxBytes);
           const u32 bar = leader_full0 + 8 * stage;
@@ -684,12 +648,8 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
         st_addr += C::kStageBytes;
         if (++stage == kStages) { stage = 0; phase ^= 1u; st_addr = smem_base; }
-        NVFP4_PROF_ADD(1);        // producer: issuing
       }
     }
-#ifdef NVFP4_GEMM_DEBUG
-    if (p.prof && blockIdx.x == 0 && lane == 0) { p.prof[0] = prof_acc[0]; p.prof[1] = prof_acc[1]; }
-#endif
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 11);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -702,10 +662,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       u32 a_lo = a_lo0;
       u32 tile = 0;                                   // tiles done by this cluster
       bool ok = true;
-#ifdef NVFP4_GEMM_DEBUG
-      unsigned long long prof_acc[4] = {0, 0, 0, 0};
-#endif
-      NVFP4_PROF_T0();
       for (int w = cid; w < num_work && ok; w += ncl, tile++) {
         int mt, nt, z;
         decode_tile(w, tiles_m, tiles_n, mt, nt, z);
@@ -722,23 +678,17 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const u32 par = BN == 256 ? ((tile & 1u) ^ 1u) : (((tile >> 1) & 1u) ^ 1u);
           if (!__all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag))) { ok = false; break; }
         }
-        NVFP4_PROF_ADD(0);        // MMA: waiting for the accumulator
         tc_fence_after();
         const u32 d_tmem = tmem_base + (acc ? C::kAccOff1 : 0);
         u32 accum = 0u;
         for (int kt = kt0; kt < kt1; kt++) {
           if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, abort_flag))) { ok = false; break; }
-          NVFP4_PROF_ADD(1);      // MMA: waiting for operands
           const u32 b_lo = a_lo + (C::kABytes >> 4);
           const u32 sfa_lo = (a_lo & 0xFFFFu) + ((C::kABytes + C::kBBytes) >> 4);
           const u32 sfb_lo = sfa_lo + (C::kSFABytes >> 4);
           const int krem = p.K - kt * kBK;
           const int kchunks = krem >= kBK ? 4 : (krem >> 6);
           if (elect_one()) {
-#ifdef NVFP4_GEMM_DEBUG
-            if ((p.dbg & 4) && accum) { tc2_commit(empty0 + 8 * stage); tc2_commit(empty_peer0 + 8 * stage); } else
-#endif
-            {
             if (kchunks == 4) {
 #pragma unroll
               for (int j = 0; j < 4; j++) {
@@ -766,21 +716,16 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             // free the stage in both CTAs once these MMAs have read it
             tc2_commit(empty0 + 8 * stage);
             tc2_commit(empty_peer0 + 8 * stage);
-            }
           }
           accum = 1u;
           a_lo += C::kStageBytes >> 4;
           if (++stage == kStages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
-          NVFP4_PROF_ADD(2);      // MMA: issuing
         }
         if (!ok) break;
         // accumulator complete: tell the epilogues of both CTAs
         const u32 fb = BN == 256 ? 0u : 8u * acc;
         if (elect_one()) { tc2_commit(accf0 + fb); tc2_commit(accf_peer0 + fb); }
       }
-#ifdef NVFP4_GEMM_DEBUG
-      if (p.prof && blockIdx.x == 0 && lane == 0) { p.prof[2] = prof_acc[0]; p.prof[3] = prof_acc[1]; p.prof[4] = prof_acc[2]; }
-#endif
       if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     }
   } else {
@@ -792,10 +737,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const u32 acce_leader0 = map_to_cta(acce0, 0);
     u32 tile = 0;
     bool ok = true;
-#ifdef NVFP4_GEMM_DEBUG
-    unsigned long long prof_acc[4] = {0, 0, 0, 0};
-#endif
-    NVFP4_PROF_T0();
     for (int w = cid; w < num_work && ok; w += ncl, tile++) {
       int mt, nt, zz;
       decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
@@ -805,7 +746,6 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const u32 par = BN == 256 ? (tile & 1u) : ((tile >> 1) & 1u);
         if (!__all_sync(0xffffffffu, NVFP4_IDLE_WAIT(bar, par, abort_flag))) { ok = false; break; }
       }
-      NVFP4_PROF_ADD(0);          // epilogue: waiting for a finished accumulator
       tc_fence_after();
       u32 r[NC];
       const u32 t_row = tmem_base + ((u32)(quad * 32) << 16) + (acc ? (u32)C::kAccOff1 : 0u) + (u32)(half * NC);
@@ -841,11 +781,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #undef NVFP4_LD32
 #undef NVFP4_LD16
 #undef NVFP4_RELEASE_ACC
-      NVFP4_PROF_ADD(1);          // epilogue: draining tensor memory
 
-#ifdef NVFP4_GEMM_DEBUG
-      if (p.dbg & 1) { if (r[0] == 0x12345678u && r[NC - 1] == 0x9abcdef0u) *static_cast<u32*>(p.c) = r[5]; continue; }
-#endif
       float alpha = 1.f;
       if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
@@ -855,11 +791,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                              : static_cast<void*>(static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0);
       staged_store<NC, C::kStageRowBytes>(r, alpha, sw, lane, cbase, p.ldc, p.c_fp32 != 0, p.atomic != 0,
                                           (int)min((long long)NC, (long long)p.N - col0));
-      NVFP4_PROF_ADD(2);          // epilogue: converting and storing
     }
-#ifdef NVFP4_GEMM_DEBUG
-    if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) { p.prof[5] = prof_acc[0]; p.prof[6] = prof_acc[1]; p.prof[7] = prof_acc[2]; p.prof[8] = tile; }
-#endif
     if (!ok && lane == 0 && p.status) atomicExch(p.status, 13);
   }
 
@@ -891,12 +823,6 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-#ifdef NVFP4_GEMM_DEBUG
-static int g_debug = 0;
-static unsigned long long* g_prof = nullptr;
-extern "C" int nvfp4_gemm_prof(unsigned long long* p) { g_prof = p; return 0; }
-extern "C" int nvfp4_gemm_debug(int flags) { g_debug = flags; return 0; }
-#endif
 static int g_sm_budget = 0;  // 0 = all SMs; otherwise the persistent GEMM grids use at most this many (even) SMs
 static int g_pair_bn = 0;    // 0 = heuristic, 128 / 192 / 256 = forced tile width of the CTA-pair kernel
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
@@ -977,7 +903,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   DevInfo* di = dev_info();
   if (!di) return NVFP4_ERR_CUDA;
   int sms = di->sms;
-  if (g_sm_budget > 0 && g_sm_budget < sms) sms = g_sm_budget & ~1;
+  if (g_sm_budget > 0 && g_sm_budget < sms) sms = g_sm_budget >= 2 ? (g_sm_budget & ~1) : 2;
 
   const int ktiles = (K + kBK - 1) / kBK;
   if (splitk > ktiles) splitk = ktiles;
@@ -1021,10 +947,6 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.atomic = (accumulate || splitk > 1) ? 1 : 0;
     pp.splitk = splitk;
     pp.ktiles_per_split = per;
-#ifdef NVFP4_GEMM_DEBUG
-    pp.dbg = g_debug;
-    pp.prof = g_prof;
-#endif
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
     const long long clusters = work < sms / 2 ? work : sms / 2;
     const unsigned grid = (unsigned)(2 * clusters);
@@ -1060,9 +982,6 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   p.atomic = (accumulate || splitk > 1) ? 1 : 0;
   p.splitk = splitk;
   p.ktiles_per_split = per;
-#ifdef NVFP4_GEMM_DEBUG
-  p.dbg = g_debug;
-#endif
   if (wide) return launch_gemm<256>(ma, mb, p, sms, di->attr256, st);
   return launch_gemm<128>(ma, mb, p, sms, di->attr128, st);
 }
@@ -1091,7 +1010,7 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
 }
 
 extern "C" int nvfp4_gemm_set_sm_budget(int sms) {
-  if (sms < 0) return NVFP4_ERR_SHAPE;
+  if (sms < 0 || sms == 1) return NVFP4_ERR_SHAPE;   // the CTA-pair grids need at least one SM pair
   g_sm_budget = sms;
   return NVFP4_OK;
 }
@@ -1118,3 +1037,4 @@ extern "C" const char* nvfp4_error_string(int status) {
     default: return "unknown status";
   }
 }
+

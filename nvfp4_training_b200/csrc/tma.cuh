@@ -34,21 +34,21 @@ __device__ __forceinline__ u64 globaltimer_ns() {
   return t;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one expired).
-__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abort_flag, u64 limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const u64 t0 = globaltimer_ns();
   for (u32 it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 127u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
 }
 
 // Bounded wait for warps that can afford to sleep: the try_wait carries a suspend-time hint, so a
 // waiting warp polls rarely instead of competing for issue slots with the warps that have work.
-__device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile int* abort_flag, u64 limit_ns = kWaitLimitNs) {
   u64 t0 = 0;
   for (u32 it = 1;; ++it) {
     u32 ok;
@@ -62,7 +62,7 @@ __device__ __forceinline__ bool mbar_wait_parked(u32 bar, u32 parity, volatile i
       if (*abort_flag) return false;
       const u64 now = globaltimer_ns();      // the clock is read only once a wait has lasted a while
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+      else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
     }
   }
 }

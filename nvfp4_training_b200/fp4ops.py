@@ -23,6 +23,12 @@ class Q:
 
 
 def amax_of(x):
+    """max|x| as a device fp32 [1] (llm-1b/fp4ops.py:25-26).  bf16 inputs take the one-read amax kernel
+    (same value); other dtypes, e.g. FP32 master weights once per step, the torch reduction."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0 and x.numel() > 0:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+        L.check(L.load().nvfp4_amax_bf16(L.ptr(x), x.numel(), L.ptr(out), L.stream()), "amax")
+        return out
     return x.abs().amax().float().reshape(1)
 
 

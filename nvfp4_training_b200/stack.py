@@ -87,7 +87,10 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None):
+        """`seed` initialises the weights (the same on every rank of a data-parallel job: replicated
+        weights), `input_seed` the synthetic activation / gradient pools (different per rank: each rank
+        holds its own rows of the batch; default seed + 1000)."""
         self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
         self.ar_blocks = max(1, ar_blocks)   # transformer blocks per gradient all-reduce
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
@@ -125,7 +128,7 @@ class LinearStack:
             self.gw_flat.append(flat)
             self.ar_after[grp[0]] = flat           # backward walks the blocks downwards: the group's lowest block is last
         # synthetic pools: X ~ N(0,1) bf16, dY ~ Student-t(3) * 1e-3 bf16, one per projection kind
-        gen_in = torch.Generator(device=self.device).manual_seed(seed + 1000)
+        gen_in = torch.Generator(device=self.device).manual_seed(seed + 1000 if input_seed is None else input_seed)
         self.x_pool, self.gy_pool = {}, {}
         for name, N, K, _ in names + ([("head", cfg.vocab, cfg.d, 0.02)] if cfg.lm_head else []):
             self.x_pool[name] = torch.randn(self.T, K, generator=gen_in, device=self.device).bfloat16()

@@ -338,17 +338,19 @@ def _stream(sr_mode, seed, blk_idx, elt_idx):
     raise ValueError(sr_mode)
 
 
-def quant_rows(x, amax=None, sr_mode=SR_NONE, seed=0):
+def quant_rows(x, amax=None, sr_mode=SR_NONE, seed=0, blk0=0):
     """1x16 blocks along the last dim (small-model/model_ref.py:39-47 `nvfp4_1d`; kernel
     llm-1b/nvq.cu:93-116).  x: [R, C] float32 holding bf16 values.
     Returns (packed codes [R, C/2], scale bytes [R, C/16] row-major, gs float32).
-    SR block index = r*(C/16)+c (nvq.cu:113); fp4k element index = 16 * that (fp4k.cu:84)."""
+    SR block index = r*(C/16)+c (nvq.cu:113); fp4k element index = 16 * that (fp4k.cu:84).
+    `blk0`: index of x's first block when x is a band of rows r0.. of a larger tensor
+    (r0*(C/16)); with `amax` of the whole tensor the band then quantizes as it does inside it."""
     x = np.asarray(x, dtype=np.float32)
     R, C = x.shape
     assert C % 16 == 0
     am = amax_f32(x) if amax is None else np.float32(amax)
     gs = global_scale(am)
-    blk = np.arange(R * (C // 16), dtype=np.uint64).reshape(R, C // 16)
+    blk = np.arange(R * (C // 16), dtype=np.uint64).reshape(R, C // 16) + np.uint64(blk0)
     rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
     codes, sbyte = _quant_blocks(x.reshape(R, C // 16, 16), gs, inv_global_scale(am), sr_mode, rnd)
     return pack_codes(codes.reshape(R, C)), sbyte, gs
@@ -376,16 +378,17 @@ def rht16_cols(x, signs):
     return (v * np.float32(0.25)).astype(np.float32)
 
 
-def quant_cols_rht(x, signs, amax=None, sr_mode=SR_NONE, seed=0):
+def quant_cols_rht(x, signs, amax=None, sr_mode=SR_NONE, seed=0, blk0=0):
     """Quantize x^T along tokens after the RHT16 (llm-1b/nvq.cu:122-158): global scale from
     4*amax(x).  Returns (packed codes [C, M/2], scale bytes [C, M/16], gs float32 incl. the x4).
-    SR block index = c*(M/16)+mb (nvq.cu:155); fp4k element index = c*M + mb*16 (fp4k.cu:114)."""
+    SR block index = c*(M/16)+mb (nvq.cu:155); fp4k element index = c*M + mb*16 (fp4k.cu:114).
+    `blk0`: index of the first block when x is a band of columns c0.. of a larger tensor (c0*(M/16))."""
     x = np.asarray(x, dtype=np.float32)
     M, C = x.shape
     am = amax_f32(x) if amax is None else np.float32(amax)
     gs = global_scale(am, 4.0)
     t = rht16_cols(x, signs)
-    blk = np.arange(C * (M // 16), dtype=np.uint64).reshape(C, M // 16)
+    blk = np.arange(C * (M // 16), dtype=np.uint64).reshape(C, M // 16) + np.uint64(blk0)
     rnd = _stream(sr_mode, seed, blk.astype(np.uint32), (blk * 16).astype(np.uint32))
     codes, sbyte = _quant_blocks(t, gs, inv_global_scale(am, 4.0), sr_mode, rnd)
     return pack_codes(codes.reshape(C, M)), sbyte, gs

@@ -69,6 +69,13 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_emit_cols(p, 128, 64, 128, p, p, p, p, 0, p, 0, None) == -2           # M % 128
     assert lib.nvfp4_gemm_linear_workspace_bytes(128, 256, 1024) == (128 + 256) * 64
     assert lib.nvfp4_gemm_force_tile_n(64) == -4 and lib.nvfp4_gemm_force_tile_n(448) == 0 and lib.nvfp4_gemm_force_tile_n(0) == 0
+    # an SM budget of one SM cannot hold a CTA pair; negative budgets are refused too
+    assert lib.nvfp4_gemm_set_sm_budget(1) == -2 and lib.nvfp4_gemm_set_sm_budget(-4) == -2
+    assert lib.nvfp4_gemm_set_sm_budget(2) == 0 and lib.nvfp4_gemm_set_sm_budget(0) == 0
+    # the wait self-test accepts 1..1000 microseconds only
+    assert lib.nvfp4_selftest_wait_timeout(100, 0, None, None) == -1
+    assert lib.nvfp4_selftest_wait_timeout(0, 0, p, None) == -7
+    assert lib.nvfp4_selftest_wait_timeout(5000, 0, p, None) == -7
 
 
 def test_python_wrappers_refuse_cpu_tensors():

@@ -1,0 +1,96 @@
+"""GPU check of `LinearStack`, the data-parallel workload the benchmark times: a tiny architecture
+(2 blocks + head, d = 256) run for one step of two microbatches
+
+  * with CUDA graphs and without: the FP32 weight gradients must be bit-equal (the first microbatch
+    stores dW, the second adds once, so the order of operations is fixed), which covers capture and
+    replay, the device-side stochastic-rounding seeds, the `overwrite=first` path, the flat per-block
+    gradient buffers and the weight-refresh graph;
+  * against the oracle's whole-layer restatement with the same seeds (hardware stochastic rounding
+    model), summed over the two microbatches: relative Frobenius error <= 1e-4 for FP32 dW, <= 4e-3
+    for the bf16 y and dX of one eager block pass.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from tests.gpu_util import rel_fro
+
+pytestmark = pytest.mark.gpu
+
+
+def f32(t):
+    return t.float().cpu().numpy()
+
+
+def tiny_stack(use_graphs, seed=3):
+    from nvfp4_training_b200.stack import LinearStack, StackConfig
+    cfg = StackConfig(vocab=512, d=256, layers=2, heads=2, kv_heads=1, ff=384, lm_head=True)
+    st = LinearStack(cfg, 256, torch.device("cuda"), seed=seed, use_graphs=use_graphs)
+    if use_graphs:
+        st.capture()
+    return st
+
+
+def test_stack_graphs_equal_eager_and_oracle():
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.linear import _RHT_SIGNS
+    a, b = tiny_stack(True), tiny_stack(False)
+    assert a.graphs_fwd is not None and b.graphs_fwd is None
+    for pa, pb in zip([p for blk in a.blocks for p in blk], [p for blk in b.blocks for p in blk]):
+        assert torch.equal(pa.w, pb.w)
+    first_micro = a.micro_count
+    assert first_micro == b.micro_count
+    for st in (a, b):
+        st.step(2, do_allreduce=False)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for pa, pb in zip([p for blk in a.blocks for p in blk], [p for blk in b.blocks for p in blk]):
+        assert torch.equal(pa.gw, pb.gw), pa.name
+        assert pa.gw.abs().max().item() > 0
+    # a second step replays the same graphs with new seeds: still equal, and different from the first
+    g0 = a.blocks[0][2].gw.clone()
+    for st in (a, b):
+        st.step(2, do_allreduce=False)
+    torch.cuda.synchronize()
+    for pa, pb in zip([p for blk in a.blocks for p in blk], [p for blk in b.blocks for p in blk]):
+        assert torch.equal(pa.gw, pb.gw), pa.name
+    assert not torch.equal(g0, a.blocks[0][2].gw)
+
+    # oracle: dW of three projections over the two microbatches of the FIRST step of a fresh stack
+    c = tiny_stack(True)
+    c.step(2, do_allreduce=False)
+    torch.cuda.synchronize()
+    for p in (c.blocks[0][0], c.blocks[1][3], c.blocks[2][0]):
+        x, w, gy = f32(c.x_pool[p.name]), f32(p.w), f32(c.gy_pool[p.name])
+        want = 0.0
+        for m in (first_micro, first_micro + 1):
+            seed = (p.lid * 7919 + m * 1000003) & 0xFFFFFFFF
+            _, _, gw = O.linear_fwd_bwd(x, w, gy, _RHT_SIGNS, seed=seed, sr_mode=O.SR_HW)
+            want = want + gw.astype(np.float64)
+        assert rel_fro(f32(p.gw), want) <= 1e-4, (p.name, rel_fro(f32(p.gw), want))
+    # y and dX of one eager block pass with the seeds now in device memory
+    projs = b.blocks[1]
+    b._fwd_block(projs, keep=True)
+    b._bwd_block(projs, keep=True, first=True)
+    torch.cuda.synchronize()
+    seeds = b.seeds.cpu().numpy().astype(np.int64) & 0xFFFFFFFF
+    for p in projs:
+        x, w, gy = f32(b.x_pool[p.name]), f32(p.w), f32(b.gy_pool[p.name])
+        assert int(seeds[p.lid, 1]) == int(seeds[p.lid, 0]) ^ 0x5BD1E995
+        y, gx, gw = O.linear_fwd_bwd(x, w, gy, _RHT_SIGNS, seed=int(seeds[p.lid, 0]), sr_mode=O.SR_HW)
+        assert rel_fro(f32(p.y), y) <= 4e-3 and rel_fro(f32(p.gx), gx) <= 4e-3, p.name
+        assert rel_fro(f32(p.gw), gw) <= 1e-4, p.name
+    _lib.check_status()
+
+
+def test_stack_separate_weight_and_input_seeds():
+    """Ranks of a data-parallel job share the weight seed and differ in the input seed: same weights,
+    different activations."""
+    from nvfp4_training_b200.stack import LinearStack, StackConfig
+    cfg = StackConfig(vocab=512, d=256, layers=1, heads=2, kv_heads=1, ff=384, lm_head=False)
+    a = LinearStack(cfg, 128, torch.device("cuda"), seed=0, input_seed=10, use_graphs=False)
+    b = LinearStack(cfg, 128, torch.device("cuda"), seed=0, input_seed=11, use_graphs=False)
+    for pa, pb in zip(a.blocks[0], b.blocks[0]):
+        assert torch.equal(pa.w, pb.w)
+    assert not torch.equal(a.x_pool["qkv"], b.x_pool["qkv"])

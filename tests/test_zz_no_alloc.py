@@ -40,6 +40,19 @@ def test_noalloc_matches_workspace_entry_point_twice():
                                               K // 2, K // 16, out.data_ptr(), L.DTYPE_FP32, N, M, N, K, L.ALPHA_AMAX,
                                               pa.data_ptr(), pb.data_ptr(), 1.0, 4.0, 0, 1, None, st), "noalloc")
     torch.cuda.synchronize()
+    # The claim itself: once every kernel variant these shapes select has been launched (above), further
+    # calls take no device memory -- neither from the driver (free memory as cudaMemGetInfo reports it
+    # does not drop) nor from torch's caching allocator.
+    free0 = torch.cuda.mem_get_info()[0]
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(2):
+        for M, N, K, a, sa, b, sb, pa, pb, ref, out in cases:
+            L.check(lib.nvfp4_gemm_linear_noalloc(a.data_ptr(), sa.data_ptr(), K // 2, K // 16, b.data_ptr(), sb.data_ptr(),
+                                                  K // 2, K // 16, out.data_ptr(), L.DTYPE_FP32, N, M, N, K, L.ALPHA_AMAX,
+                                                  pa.data_ptr(), pb.data_ptr(), 1.0, 4.0, 0, 1, None, st), "noalloc")
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free0
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == (alloc0, reserved0)
     for M, N, K, a, sa, b, sb, pa, pb, ref, out in cases:
         r, o = ref.cpu().numpy().astype(np.float64), out.cpu().numpy().astype(np.float64)
         assert np.isfinite(o).all() and np.abs(r).max() > 0
