@@ -307,6 +307,260 @@ def isolated_kernels(cfg, T, peaks):
     return roof, detail
 
 
+# ------------------------------------------------------------------------------------------ self-check
+def _deq_rows(q, rows):
+    """float64 [len(rows), C] block-scaled values (without the tensor scale) of rows of a packed operand, decoded
+    with the package's pure-torch decoders (the reference's own test decoders, llm-1b/nvq.py:99-117)."""
+    import torch
+    from nvfp4_training_b200 import nvq
+    R, C = q.d.shape[0], q.d.shape[1] * 2
+    d = q.d.view(torch.uint8)[rows]
+    sc = nvq.unswizzle(q.s, R, C // 16)[rows].contiguous().view(torch.float8_e4m3fn).double()
+    tab = nvq._E2M1.to(device=d.device, dtype=torch.float64)
+    v = torch.stack([tab[(d & 15).long()], tab[(d >> 4).long()]], -1).reshape(d.shape[0], C)
+    return v * sc.repeat_interleave(16, 1)
+
+
+def _gemm_rows_err(c, qa, qb, rows):
+    """max over the sampled rows of |C - Y| / (tol_rel |Y| + 1e-6 max|Y|) and the relative Frobenius error, Y = FP64
+    product of the dequantized operand bytes.  tol_rel = 1e-4 (FP32 out) or 2^-8 (bf16 out): <= 1 passes."""
+    import torch
+    all_rows = torch.arange(qb.d.shape[0], device=c.device)
+    y = _deq_rows(qa, rows) @ _deq_rows(qb, all_rows).t() * (qa.gs.double() * qb.gs.double())
+    got = c[rows].double()
+    rel = 1e-4 if c.dtype == torch.float32 else 2.0 ** -8
+    worst = ((got - y).abs() / (rel * y.abs() + 1e-6 * y.abs().max())).max().item()
+    fro = ((got - y).norm() / y.norm()).item()
+    return worst, fro
+
+
+def verify_step(stack, n_micro, world, rank):
+    """Checks of the timed workload's results, after the timed region:
+      kernels   y / dX / dW of one projection (down, 5632 -> 2048) at the step's own shapes, on 256 sampled rows each,
+                against the FP64 product of their own dequantized operands (tolerances of the GPU tests);
+      stack     the weight gradient the graph-replayed step leaves for that projection is bit-equal to an eager
+                recomputation with the same device seeds (first microbatch stores, later ones add once);
+      allreduce (N > 1) a slice of the all-reduced dW equals the sum of the ranks' local slices.
+    Returns a dict with `ok`."""
+    import torch
+    import torch.distributed as dist
+    from nvfp4_training_b200 import _lib, nvq
+    from nvfp4_training_b200.linear import _RHT_SIGNS, linear_bwd, linear_fwd
+    dev = stack.device
+    out = {}
+    p = stack.blocks[0][3]
+    x, gy = stack.x_pool[p.name], stack.gy_pool[p.name]
+    T = x.shape[0]
+    g = torch.Generator(device=dev).manual_seed(5)
+    rows_t = torch.sort(torch.randperm(T, generator=g, device=dev)[:256]).values
+    rows_n = torch.sort(torch.randperm(p.N, generator=g, device=dev)[:256]).values
+    am, ag = nvq.amax(x), nvq.amax(gy)
+    qx, qxt = nvq.quant_rows_cols_rht(x, _RHT_SIGNS, am=am)
+    qg, qgt = nvq.quant_rows_cols_rht(gy, _RHT_SIGNS, sr=True, seed=11, seed_cols=12, am=ag, sr_mode=stack.sr_mode)
+    errs = {"y": _gemm_rows_err(nvq.mm(qx, p.q), qx, p.q, rows_t),
+            "dx": _gemm_rows_err(nvq.mm(qg, p.qt), qg, p.qt, rows_t),
+            "dw": _gemm_rows_err(nvq.mm(qgt, qxt, out_dtype=torch.float32), qgt, qxt, rows_n)}
+    out["kernels"] = {k: {"worst_over_bound": v[0], "rel_fro": v[1]} for k, v in errs.items()}
+    ok = all(v[0] <= 1.0 for v in errs.values())
+    del qx, qxt, qg, qgt
+
+    # stack result against an eager recomputation with the same seeds
+    mc = stack.micro_count
+    stack.step(n_micro, do_allreduce=False)
+    local = p.gw.clone()
+    local_head = stack.blocks[-1][0].gw.view(-1)[:65536].clone()
+    stack.micro_count = mc
+    gw = torch.empty_like(p.gw)
+    for m in range(n_micro):
+        stack._bump_seeds()
+        sd = stack.seeds[p.lid]
+        _, am_x, qxt = linear_fwd(x, p.q, keep_xt=True, signs=_RHT_SIGNS)
+        linear_bwd(None, am_x, gy, p.qt, sd[0:1], sd[1:2], gw_out=gw, signs=_RHT_SIGNS, sr_mode=stack.sr_mode,
+                   overwrite=(m == 0), qxt=qxt)
+    out["stack_equals_eager"] = bool(torch.equal(gw, local))
+    ok = ok and out["stack_equals_eager"]
+
+    if world > 1:
+        stack.micro_count = mc
+        stack.step(n_micro, do_allreduce=True)
+        torch.cuda.synchronize()
+        sl = slice(0, 65536)
+        mine = torch.stack([local.view(-1)[sl], local_head])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        want = torch.stack(gathered).double().sum(0)
+        got = torch.stack([p.gw.view(-1)[sl], stack.blocks[-1][0].gw.view(-1)[:65536]]).double()
+        err = ((got - want).abs().max() / want.abs().max()).item()
+        out["allreduce_max_err_over_max"] = err
+        ok = ok and err <= 1e-6
+    torch.cuda.synchronize()
+    _lib.check_status()
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    out["ok"] = bool(flag.item() == 1.0)
+    return out
+
+
+def comm_breakdown(stack, n_micro, steps):
+    """Where the time of a data-parallel step goes: the step with the all-reduce switched off, and the block-by-block
+    all-reduces of all gradient buffers timed alone (CUDA events, this rank; the caller takes the max over ranks)."""
+    import torch
+    from nvfp4_training_b200.stack import allreduce_sum_
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.distributed.barrier()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    stack.step(n_micro, False)
+    ms_noar = timed(lambda: stack.step(n_micro, False), steps)
+
+    def only_ar():
+        for flat in reversed(stack.gw_flat):
+            allreduce_sum_([flat], stack.group)
+    only_ar()
+    ms_ar = timed(only_ar, max(2, steps // 2))
+    nbytes = sum(f.numel() * 4 for f in stack.gw_flat)
+    return ms_noar, ms_ar, nbytes
+
+
+# ------------------------------------------------------------------------------------------ configuration sweeps
+def config_sweeps(cfg, peaks):
+    """The other benchmark configurations, each timed with CUDA events on one GPU (rotating operand sets larger than
+    L2 where one set would fit):
+      config2   every projection of one block at T = 4096: the whole layer (quantizers + 3 GEMMs, weights cached) and
+                its three GEMMs alone
+      config3   wgrad stress: dY [16384, 5632] stochastic + X [16384, 2048] nearest, RHT16 on both, FP32 dW
+      config5   GEMM M = N = K in {4096, 8192, 16384}, M = 4096 with N, K in {2048, 5632, 49152} (with the library FP4
+                GEMM behind torch._scaled_mm beside it); quantizers on 16 Mi .. 1 Gi elements, 1x16 / 16x16 / +RHT16 /
+                +stochastic rounding and the one-read kernel that emits both operands
+    """
+    import torch
+    from nvfp4_training_b200 import _lib, nvq
+    from nvfp4_training_b200.linear import _RHT_SIGNS, linear_bwd, linear_fwd
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(11)
+    HW = _lib.ROUND_SR_HW
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    res = {"config2": {}, "config3": {}, "config5_gemm": {}, "config5_quant": {}}
+
+    def rnd(r, c, scale=1.0):
+        t = torch.randn(r, c, generator=g, device=dev, dtype=torch.bfloat16)
+        return t if scale == 1.0 else (t.float() * scale).bfloat16()
+
+    def gemm_time(M, N, K, fp32=False, lib=False):
+        nset = max(2, min(6, int(300e6 // ((M + N) * K * 0.5625 + M * N * (4 if fp32 else 2))) + 1))
+        ops = []
+        for _ in range(nset):
+            ops.append((nvq.quant_rows(rnd(M, K)), nvq.quant_rows(rnd(N, K)),
+                        torch.empty(M, N, dtype=torch.float32 if fp32 else torch.bfloat16, device=dev)))
+        it = [0]
+
+        def run():
+            a, b, o = ops[it[0] % nset]
+            it[0] += 1
+            nvq.mm(a, b, out_dtype=o.dtype, out=o)
+
+        def run_lib():
+            a, b, _ = ops[it[0] % nset]
+            it[0] += 1
+            torch._scaled_mm(a.d, b.d.t(), a.s.view(-1), b.s.view(-1), out_dtype=torch.bfloat16)
+        t = time_events(run, iters=max(8, 2 * nset))
+        out = {"M": M, "N": N, "K": K, "us": t * 1e6, "tflops": 2.0 * M * N * K / t / 1e12,
+               "frac_of_4x_bf16": 2.0 * M * N * K / t / 1e12 / fp4_peak}
+        if lib and not fp32:
+            try:
+                tl = time_events(run_lib, iters=max(8, 2 * nset))
+                out["scaled_mm_tflops"] = 2.0 * M * N * K / tl / 1e12
+            except Exception as e:
+                out["scaled_mm_error"] = repr(e)[:100]
+        return out
+
+    # ---- config 2
+    T = 4096
+    projs = [("qkv", 3072, 2048), ("o_3072_to_2048", 2048, 3072), ("o_2048_to_2048", 2048, 2048),
+             ("gate_up", 11264, 2048), ("down", 2048, 5632)]
+    for name, N, K in projs:
+        nset = 4
+        xs = [rnd(T, K) for _ in range(nset)]
+        gys = [rnd(T, N, 1e-3) for _ in range(nset)]
+        q, qt = nvq.quant_w2d(rnd(N, K, 0.02))
+        gw = torch.zeros(N, K, device=dev)
+        it = [0]
+
+        def layer():
+            i = it[0] % nset
+            it[0] += 1
+            _, am, qxt = linear_fwd(xs[i], q, keep_xt=True)
+            linear_bwd(None, am, gys[i], qt, 1, 2, gw_out=gw, sr_mode=HW, overwrite=True, qxt=qxt)
+        t = time_events(layer, iters=12)
+        fl = 6.0 * T * N * K
+        res["config2"][name] = {"T": T, "N": N, "K": K, "layer_us": t * 1e6, "layer_tflops": fl / t / 1e12,
+                                "layer_frac_of_4x_bf16": fl / t / 1e12 / fp4_peak,
+                                "fprop": gemm_time(T, N, K, lib=True), "dgrad": gemm_time(T, K, N, lib=True),
+                                "wgrad": gemm_time(N, K, T, fp32=True)}
+        del xs, gys
+    # ---- config 3
+    T, N, K = 16384, 5632, 2048
+    gy, x = rnd(T, N, 1e-3), rnd(T, K)
+    dw = torch.empty(N, K, device=dev)
+    am_g, am_x = nvq.amax(gy), nvq.amax(x)
+
+    def wgrad():
+        qgt = nvq.quant_cols_rht(gy, _RHT_SIGNS, sr=True, seed=3, am=am_g, sr_mode=HW)
+        qxt = nvq.quant_cols_rht(x, _RHT_SIGNS, am=am_x)
+        nvq.mm(qgt, qxt, out_dtype=torch.float32, out=dw)
+    t = time_events(wgrad, iters=12)
+    res["config3"] = {"T": T, "N": N, "K": K, "quant_plus_gemm_us": t * 1e6, "tflops": 2.0 * T * N * K / t / 1e12,
+                      "gemm_alone": gemm_time(N, K, T, fp32=True)}
+    exact = gy.double().t() @ x.double()
+    res["config3"]["rel_err_vs_exact"] = ((dw.double() - exact).norm() / exact.norm()).item()
+    del gy, x, dw, exact
+    # ---- config 5: GEMM
+    for n in (4096, 8192, 16384):
+        res["config5_gemm"][f"square_{n}"] = gemm_time(n, n, n, lib=True)
+    for N in (2048, 5632, 49152):
+        for K in (2048, 5632, 49152):
+            res["config5_gemm"][f"M4096_N{N}_K{K}"] = gemm_time(4096, N, K, lib=True)
+    # ---- config 5: quantizers
+    hbm = peaks["hbm_gbs"]
+    for label, R in (("16Mi", 2048), ("64Mi", 8192), ("256Mi", 32768), ("1Gi", 131072)):
+        C = 8192
+        n = R * C
+        nset = max(1, min(8, int(300e6 // (n * 2)) + 1))
+        xs = [rnd(R, C) for _ in range(nset)]
+        am = nvq.amax(xs[0])
+        it = [0]
+
+        def t_of(fn, bpe):
+            def run():
+                it[0] += 1
+                fn(xs[it[0] % nset])
+            t = time_events(run, iters=max(6, 2 * nset))
+            return {"us": t * 1e6, "gbs": n * bpe / t / 1e9, "frac_hbm": n * bpe / t / 1e9 / hbm}
+        res["config5_quant"][label] = {
+            "elements": n,
+            "amax": t_of(lambda t: nvq.amax(t), 2.0),
+            "rows_1x16_rn": t_of(lambda t: nvq.quant_rows(t, am=am), 2.5625),
+            "rows_1x16_sr": t_of(lambda t: nvq.quant_rows(t, sr=True, seed=1, am=am, sr_mode=HW), 2.5625),
+            "cols_rht16_rn": t_of(lambda t: nvq.quant_cols_rht(t, _RHT_SIGNS, am=am), 2.5625),
+            "cols_rht16_sr": t_of(lambda t: nvq.quant_cols_rht(t, _RHT_SIGNS, sr=True, seed=1, am=am, sr_mode=HW), 2.5625),
+            "both_operands_rn": t_of(lambda t: nvq.quant_rows_cols_rht(t, _RHT_SIGNS, am=am), 3.125),
+            "both_operands_sr": t_of(lambda t: nvq.quant_rows_cols_rht(t, _RHT_SIGNS, sr=True, seed=1, seed_cols=2, am=am, sr_mode=HW), 3.125),
+            "w2d_16x16": t_of(lambda t: nvq.quant_w2d(t, am=am), 3.125),
+        }
+        del xs
+        torch.cuda.empty_cache()
+    _lib.check_status()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist

@@ -105,9 +105,15 @@ int nvfp4_quant_cols_rht(const void* x, int M, int C, void* codes, void* scales,
  * needs from an activation or a gradient: the row operand of `nvfp4_quant_rows` (codes_r, scales_r,
  * gs_r_out) and the transposed RHT16 operand of `nvfp4_quant_cols_rht` (codes_c, scales_c, gs_c_out),
  * bit-identical to those two calls with seeds seed_r / seed_c (seed_*_dev: device words that
- * replace them).  Either output pair may be null to skip it.  The tensor is read from HBM once
- * (TMA tiles of 128 tokens x 64 columns in a shared-memory ring).  Fuses the reference's pair of
- * launches `quant_rows(gy)` + `quant_cols_rht(gy)` (llm-1b/model.py:62-66, llm-1b/nvq.py:46-70).
+ * replace them).  Either output pair may be null to skip it.  The tensor is read from HBM once.
+ * Fuses the reference's pair of launches `quant_rows(gy)` + `quant_cols_rht(gy)` (llm-1b/model.py:62-66,
+ * llm-1b/nvq.py:46-70).  Two kernels stand behind it:
+ *   - tensor-core fed (M % 128 == 0, C % 128 == 0, codes 16-byte and scales 4-byte aligned): TMA tiles of
+ *     128 x 128, tcgen05.mma with 0/+-1 matrices converts / transposes / sign-flips the tile exactly into
+ *     tensor memory, the quantizing warps read it with tcgen05.ld.  One documented difference: an input
+ *     that is exactly -0 gives code 0x0 (the scalar kernels and the reference's convert give 0x8);
+ *   - scalar (any other accepted shape): TMA tiles of 128 x 64 in a shared-memory ring, read by the
+ *     quantizing warps.
  * Requires M % 128 == 0, C % 64 == 0 (C % 128 == 0 with SWIZZLED scales and codes_c), ldx % 8 == 0,
  * x and codes_c 16-byte aligned, codes_r and scales_c 8-byte aligned.  A wait that expires inside the kernel (1 s) is reported by nvfp4_quant_tile_status.
  */
@@ -116,8 +122,13 @@ int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void* codes_r, 
                      unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
                      const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
 
+/* Tuning / test hook: 0 = nvfp4_quant_tile picks the tensor-core-fed kernel where it applies (default),
+ * 1 = always the scalar tile kernel.  Process-wide.  No reference counterpart. */
+int nvfp4_quant_tile_set_path(int path);
+
 /* Reads (synchronously) the status word of nvfp4_quant_tile launches on the current device:
- * 0, or the role whose wait expired first (1 producer, 2 consumer); `reset` != 0 clears it. */
+ * 0, or the role whose wait expired first (scalar kernel: 1 producer, 2 consumer; tensor-core-fed kernel:
+ * 17 producer, 18 consumer, 19 MMA issuer); `reset` != 0 clears it. */
 int nvfp4_quant_tile_status(int* out, int reset);
 
 /*

@@ -29,6 +29,7 @@ SIGNATURES = {
     "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp, _vp]),
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),
     "nvfp4_quant_tile_status": (_i, [_vp, _i]),
+    "nvfp4_quant_tile_set_path": (_i, [_i]),
     "nvfp4_emit_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp, _u, _vp]),
     "nvfp4_emit_cols": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _u, _vp]),
     "nvfp4_quant_w2d": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
@@ -64,6 +65,9 @@ def load():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
+        # tuning knob: NVFP4_TILE_PATH=1 keeps nvfp4_quant_tile on its scalar kernel
+        if os.environ.get("NVFP4_TILE_PATH"):
+            lib.nvfp4_quant_tile_set_path(int(os.environ["NVFP4_TILE_PATH"]))
         _lib = lib
     return _lib
 

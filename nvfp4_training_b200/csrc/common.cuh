@@ -154,6 +154,16 @@ __device__ __forceinline__ u64 f2_ndiv(u64 a, u64 b, u64 nrb) {
   return f2_fma(f2_fma(m, b, a), nrb, m);
 }
 
+// t / bs for a block scale bs (an E4M3 value: at most 4 significant bits), from the negated reciprocal split in two
+// words, nrh = -RN(1/bs) and nrl = -RN(1/bs - RN(1/bs)):  RN(t*nrh + RN(t*nrl)).  The quotient feeds a
+// round-to-E2M1 whose result only depends on how t/bs compares with the seven rounding boundaries b (0.25 .. 5).
+// RN(t/bs) < b, = b, > b exactly when t < c, = c, > c for c = b*bs (exactly representable), and this form --
+// accurate to 2^-46, against 0.03 ulp between the nearest t/bs and a rounding midpoint next to b -- maps
+// pred(c), c, succ(c) below, onto and above b for every scale byte and boundary (checked exhaustively by
+// tests/test_division_model.py); it is monotone in t, so the codes equal those of the correctly rounded division.
+// Like ndiv() it takes the NEGATED numerator and returns the quotient with the original sign, zeros included.
+__device__ __forceinline__ u64 f2_div_bs(u64 nt, u64 nrh, u64 nrl) { return f2_fma(nt, nrh, f2_mul(nt, nrl)); }
+
 // Per-tensor constants of a quantizer launch.
 struct TensorScale {
   float gs;      // max(k*amax/2688, 1e-30)/pre: the FP32 tensor scale the values are divided by
@@ -164,7 +174,7 @@ struct TensorScale {
 
 constexpr int kLutFloats = 256;
 
-// Fill the per-CTA table: for round to nearest  lut[sb] = {-RN(1/bs), bs},  for stochastic rounding
+// Fill the per-CTA table: for round to nearest  lut[sb] = {-RN(1/bs), -RN(1/bs - RN(1/bs))} (see f2_div_bs),  for stochastic rounding
 // lut[sb] = {inv_gs/bs, bs}  (the exact multiplier of the reference kernels).  `pre` is a power of
 // two that the caller's values still have to be multiplied by (0.25 after the Hadamard butterflies,
 // else 1): it is folded into gs, which changes no quotient.  Ends with a block barrier.
@@ -183,9 +193,18 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
     const float bsf = e4m3_dec(threadIdx.x);
     // entry 0 (underflowed block): -0 / +0 make every scaled value a zero with the input's sign
     float m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -0.f : 0.f;
-    if (threadIdx.x >= 1 && threadIdx.x <= 126)
-      m = (ROUNDING == NVFP4_ROUND_NEAREST) ? -__frcp_rn(bsf) : __fdiv_rn(t.inv_gs, bsf);   // emit modes: inv/bs too
-    reinterpret_cast<float2*>(lut)[threadIdx.x] = make_float2(m, bsf);
+    float second = (ROUNDING == NVFP4_ROUND_NEAREST) ? -0.f : bsf;
+    if (threadIdx.x >= 1 && threadIdx.x <= 126) {
+      if (ROUNDING == NVFP4_ROUND_NEAREST) {
+        const float rh = __frcp_rn(bsf);
+        const float res = __fmaf_rn(-rh, bsf, 1.f);        // exact: 1 - rh*bs has few significant bits
+        m = -rh;
+        second = -__fmul_rn(res, rh);                       // -(1/bs - rh) to 2^-24 of itself
+      } else {
+        m = __fdiv_rn(t.inv_gs, bsf);                       // emit modes: inv/bs too
+      }
+    }
+    reinterpret_cast<float2*>(lut)[threadIdx.x] = make_float2(m, second);
   }
   __syncthreads();
   return t;
@@ -253,8 +272,9 @@ __device__ __forceinline__ u32 round8(float (&y)[8], u32& key, u32 seed, u32 elt
 // Quantize one block of 16 values that share a scale.
 //   v      the 16 values (x, or the Hadamard-transformed x before its power-of-two factor)
 //   sb     the block's scale byte (block_scale_byte of max |v| over everything that shares the scale)
-// Round to nearest:  y = (v/gs)/bs, the torch path's operation order, each division correctly
-//   rounded by f2_ndiv() (three packed FMA-pipe instructions per two values, no branch).
+// Round to nearest:  y = (v/gs)/bs, the torch path's operation order: v/gs correctly rounded by f2_ndiv()
+//   (three packed FMA-pipe instructions per two values), the division by the block scale by f2_div_bs()
+//   (two), which gives the same codes as a correctly rounded one; no branch.
 // Stochastic rounding:  y = v * (inv_gs / bs), the reference kernels' form (llm-1b/nvq.cu:50,54) in
 //   IEEE arithmetic; the torch path draws torch.rand and so defines no bit-level result.
 // A block whose scale byte is 0 needs no branch: table entry 0 turns every value into a zero with
@@ -272,7 +292,7 @@ __device__ __forceinline__ uint2 quant_block16(const u64 (&P)[8], u32 sb, const 
     float y[8];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[4 * h + j], G, NRG), B, K) : f2_mul(P[4 * h + j], K);
+      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_div_bs(f2_ndiv(P[4 * h + j], G, NRG), K, B) : f2_mul(P[4 * h + j], K);
       y[2 * j] = f2_lo(r); y[2 * j + 1] = f2_hi(r);
     }
     w[h] = round8<ROUNDING>(y, key, seed, elt_idx, h);
@@ -304,7 +324,7 @@ __device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const Tensor
     float y0[8], y1[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_ndiv(f2_ndiv(P[8 * h + j], G, NRG), B, K) : f2_mul(P[8 * h + j], K);
+      const u64 r = (ROUNDING == NVFP4_ROUND_NEAREST) ? f2_div_bs(f2_ndiv(P[8 * h + j], G, NRG), K, B) : f2_mul(P[8 * h + j], K);
       y0[j] = f2_lo(r); y1[j] = f2_hi(r);
     }
     w0[h] = round8<ROUNDING>(y0, key0, seed, blk0 * 16u, h);

@@ -229,11 +229,11 @@ __global__ void __launch_bounds__(256) quant_w2d_kernel(const T* __restrict__ w,
       const u32 sb = block_scale_byte(bmax, ts);
       sbs[j] = sb;
       const float2 kf = lut_entry(ts, sb);
-      const u64 B = f2_pack(kf.y, kf.y), NRB = f2_pack(kf.x, kf.x);
+      const u64 NRH = f2_pack(kf.x, kf.x), NRL = f2_pack(kf.y, kf.y);
       float y[8];
 #pragma unroll
       for (int i = 0; i < 8; i += 2) {
-        const u64 t = f2_ndiv(f2_ndiv(f2_pack(v[j][i], v[j][i + 1]), G, NRG), B, NRB);
+        const u64 t = f2_div_bs(f2_ndiv(f2_pack(v[j][i], v[j][i + 1]), G, NRG), NRH, NRL);
         y[i] = f2_lo(t); y[i + 1] = f2_hi(t);
       }
       const u32 word = e2m1x8_rn(y);

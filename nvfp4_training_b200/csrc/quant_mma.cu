@@ -1,0 +1,440 @@
+// One-read NVFP4 quantizer for sm_100a, tensor-core fed: the row operand (1x16 blocks along the
+// columns) and the transposed RHT16 operand (16-token blocks per column) of a bf16 [M, C] tensor
+// from a single pass over HBM.
+//
+// What the quantizer's threads spend their issue slots on is not the arithmetic of the format but
+// getting values into the right thread in FP32: unpacking bf16 pairs, and for the transposed operand
+// walking a shared-memory tile column-wise and staging the outputs back into rows.  Here the tensor
+// core does that data movement, exactly:
+//   * TMA streams 128-token x 128-column tiles (two 128 x 64 boxes, 128-byte swizzle) into a ring;
+//   * one thread issues tcgen05.mma kind::f16 (bf16 in, FP32 out) with tiny 0/+-1 matrices as the B
+//     operand.  Row operand: D1[token, col] = X * I (K-major A): the tile converted to FP32, one
+//     token per tensor-memory lane.  Transposed operand: D2[col, slot] = X^T * P (MN-major A straight
+//     from the same tile, no transpose in shared memory): one column per lane, and P both applies
+//     the Hadamard sign vector and interleaves two 16-token blocks (slot 2k = token k of the first
+//     block, 2k+1 = token k of the second), so that the butterflies run on packed FP32 pairs.
+//     Every output is ONE product +-1 * x plus exact zeros, so D holds the bf16 values bit for bit
+//     whatever the accumulation order;
+//   * eight consumer warps read their lane quadrant with tcgen05.ld (16 values of a 1x16 block, or 32
+//     values of two 16-token blocks, per instruction), quantize, and store 32 contiguous bytes of
+//     codes per thread for each operand: no staging, no shared-memory traffic in the consumers.
+// One difference to the scalar kernels: an input that is exactly -0 arrives as +0 (an IEEE sum of
+// signed zeros), so its code is 0x0 where the scalar kernels and the reference's convert give 0x8; the
+// dequantized value is the same.  Inf/NaN inputs poison their 16-value group (0 * Inf), as they
+// poison the tensor's amax in every implementation.
+//
+// Two CTAs per SM, each with 256 tensor-memory columns (D1 and D2 of one tile); while the consumers
+// finish a tile's last values the next tile's MMAs already run.  Every mbarrier wait is bounded: on
+// expiry the CTA raises an abort flag, stores a role code in the quantizer status word, lets copies
+// in flight land, frees its tensor memory and returns.
+#include "tma.cuh"
+
+namespace nvfp4 {
+
+constexpr int kQTok = 128;                    // tokens per tile
+constexpr int kQCol = 128;                    // columns per tile (two TMA boxes of 64)
+constexpr int kQBoxBytes = kQTok * 64 * 2;    // 16 KB
+constexpr int kQTileBytes = 2 * kQBoxBytes;
+constexpr int kQStages = 3;
+constexpr int kQConsumerWarps = 8;
+constexpr int kQThreads = 32 * (2 + kQConsumerWarps);
+constexpr int kQI16Bytes = 16 * 128, kQPermBytes = 32 * 128;
+constexpr int kQSmem = kQStages * kQTileBytes + 1024 /*I16, padded*/ + 1024 + 2 * kQPermBytes + 1024 /*alignment slack*/;
+constexpr int kQTmemCols = 256;               // D1 at columns 0..127, D2 at 128..255
+
+__device__ int g_quant_tc_status;             // 0, or the role code of the first wait that expired
+
+struct TcParams {
+  unsigned char* codes_r; unsigned char* scales_r;    // row operand [M, C/2], scales [M, C/16]
+  unsigned char* codes_c; unsigned char* scales_c;    // transposed operand [C, M/2], scales [C, M/16]
+  const float* amax;
+  float* gs_r_out; float* gs_c_out;
+  int M, C, linear;
+  u32 signs;
+  u32 seed_r, seed_c;
+  const u32* seed_r_dev; const u32* seed_c_dev;
+};
+
+// ---- tcgen05 wrappers (cta_group::1)
+__device__ __forceinline__ void q_tmem_alloc(u32 smem_dst, u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void q_tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void q_tmem_dealloc(u32 taddr, u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void q_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void q_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void q_commit(u32 bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void q_mma_bf16(u32 d_tmem, u64 adesc, u64 bdesc, u32 idesc, u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void q_ld32(u32 taddr, u32 (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void q_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ u64 q_pack64(u32 lo, u32 hi) {
+  u64 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// Shared-memory matrix descriptors (tcgen05): start address >> 4 in bits 0..13, leading byte offset >> 4 in
+// bits 16..29, stride byte offset >> 4 in bits 32..45, version 1 at bit 46, 128-byte swizzle (2) in bits 61..63.
+//   K-major operand (rows of 128 bytes along K): stride offset = 1024 B between 8-row groups, leading offset unused (1)
+//   MN-major operand (rows of 128 bytes along M, one row per K index): leading offset = distance between 64-element
+//   groups along M (the two TMA boxes, 16 KB apart), stride offset = 1024 B between 8-row (8 K index) groups
+constexpr u32 kQDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ u64 q_desc_k(u32 saddr) { return q_pack64(((saddr & 0x3FFFFu) >> 4) | (1u << 16), kQDescHi); }
+__device__ __forceinline__ u64 q_desc_mn(u32 saddr) {
+  return q_pack64(((saddr & 0x3FFFFu) >> 4) | ((u32)(kQBoxBytes >> 4) << 16), kQDescHi);
+}
+// Instruction descriptor, kind::f16: FP32 accumulator (1 at bit 4), A and B bf16 (1 at bits 7 and 10), A major at
+// bit 15 (1 = MN-major), B K-major, N / 8 at bit 17, M / 16 at bit 24.
+__host__ __device__ constexpr u32 q_idesc(int n, bool a_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((u32)(n >> 3) << 17) | ((u32)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void q_settle_copies() {
+  const u64 t0 = globaltimer_ns();
+  while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+}
+
+// Walks the tiles of one CTA in (token tile, column tile) coordinates without a division per tile.
+struct TcWalk {
+  int mt, ct, dq, dr, nct, nmt;
+  __device__ __forceinline__ TcWalk(int M, int C) {
+    nct = C / kQCol; nmt = M / kQTok;
+    mt = (int)blockIdx.x / nct; ct = (int)blockIdx.x - mt * nct;
+    dq = (int)gridDim.x / nct; dr = (int)gridDim.x - dq * nct;
+  }
+  __device__ __forceinline__ bool valid() const { return mt < nmt; }
+  __device__ __forceinline__ void next() { mt += dq; ct += dr; if (ct >= nct) { ct -= nct; mt++; } }
+};
+
+template <int ROUNDING, bool ROWS, bool COLS>
+__global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) float lut_r[kLutFloats];
+  __shared__ __align__(8) float lut_c[kLutFloats];
+  __shared__ __align__(8) u64 bars[2 * kQStages + 2];
+  __shared__ u32 tmem_slot;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const u32 tiles0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const u32 i16_s = tiles0 + kQStages * kQTileBytes;            // 16 rows x 128 B, then padding to 1024
+  const u32 p1_s = i16_s + 2048, p2_s = p1_s + kQPermBytes;     // 32 rows x 128 B each (1024-byte aligned)
+  const u32 full0 = smem_u32(bars), empty0 = full0 + 8 * kQStages;
+  const u32 tfull = empty0 + 8 * kQStages, tempty = tfull + 8;
+
+  // ---- constants of the MMAs: identity and the two sign/interleave matrices, in the K-major 128-byte-swizzle
+  // layout (row n at n * 128 bytes, its 16-byte chunk j at position j ^ (n & 7)); only K columns 0..15 are read
+  for (u32 i = threadIdx.x; i < (2048u + 2u * kQPermBytes) / 4u; i += kQThreads)
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(i16_s + 4u * i), "r"(0u) : "memory");
+  __syncthreads();
+  if (threadIdx.x < 16) {
+    const u32 n = threadIdx.x;                                  // I16: row n has 1.0 at K index n
+    const u32 off = n * 128u + ((((n >> 3) ^ (n & 7u)) << 4) | ((n & 7u) << 1));
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(i16_s + off), "h"((unsigned short)0x3F80) : "memory");
+  } else if (threadIdx.x >= 32 && threadIdx.x < 64) {
+    // P1 row 2k and P2 row 2k+1 hold s_k at K index k: slot 2k = token k of the first 16-token block, slot 2k+1 =
+    // token k of the second; bit k of `signs` negates token k
+    const u32 n = threadIdx.x - 32u, k = n >> 1;
+    const unsigned short v = ((p.signs >> k) & 1u) ? (unsigned short)0xBF80 : (unsigned short)0x3F80;
+    const u32 off = n * 128u + ((((k >> 3) ^ (n & 7u)) << 4) | ((k & 7u) << 1));
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(((n & 1u) ? p2_s : p1_s) + off), "h"(v) : "memory");
+  }
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kQStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(tfull, 1);
+    mbar_init(tempty, kQConsumerWarps);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // the tensor core reads shared memory through the asynchronous proxy
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    q_tmem_alloc(smem_u32(&tmem_slot), kQTmemCols);
+    q_tmem_relinquish();
+  }
+  const float amax = __ldg(p.amax);
+  const bool first = blockIdx.x == 0 && threadIdx.x == 0;
+  TensorScale ts_r, ts_c;
+  if (ROWS) ts_r = make_tensor_scale<ROUNDING>(amax, 1.f, lut_r, first ? p.gs_r_out : nullptr);
+  // the x0.25 that follows the butterflies is folded into the tensor scale (a power of two)
+  if (COLS) ts_c = make_tensor_scale<ROUNDING>(amax, 4.f, lut_c, first ? p.gs_c_out : nullptr, 0.25f);
+  q_fence_before();
+  __syncthreads();
+  q_fence_after();
+  const u32 tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    u32 stage = 0, phase = 0;
+    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(empty0 + 8 * stage, phase ^ 1u, abort_flag))) {
+        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 1);
+        break;
+      }
+      if (elect_one()) {
+        const u32 bar = full0 + 8 * stage, dst = tiles0 + stage * kQTileBytes;
+        mbar_arrive_expect_tx(bar, kQTileBytes);
+        tma_load_2d(dst, &map, tw.ct * kQCol, tw.mt * kQTok, bar);
+        tma_load_2d(dst + kQBoxBytes, &map, tw.ct * kQCol + 64, tw.mt * kQTok, bar);
+      }
+      __syncwarp();
+      if (++stage == kQStages) { stage = 0; phase ^= 1u; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr u32 idesc_row = q_idesc(16, false), idesc_col = q_idesc(32, true);
+    const u64 b_i16 = q_desc_k(i16_s), b_p1 = q_desc_k(p1_s), b_p2 = q_desc_k(p2_s);
+    u32 stage = 0, phase = 0, tile_par = 0;
+    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
+      // tensor memory free (the consumers have read the previous tile), then the tile's bytes have landed
+      bool ok = mbar_wait(tempty, tile_par ^ 1u, abort_flag);
+      ok = ok && mbar_wait(full0 + 8 * stage, phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 3);
+        break;
+      }
+      q_fence_after();
+      if (elect_one()) {
+        const u32 tile = tiles0 + stage * kQTileBytes;
+        if (ROWS) {
+          // D1[token, 64 b + 16 kk + n] = sum_k X[token, 64 b + 16 kk + k] * I[n, k]
+#pragma unroll
+          for (int b = 0; b < 2; b++)
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+              q_mma_bf16(tmem_base + (u32)(64 * b + 16 * kk), q_desc_k(tile + b * kQBoxBytes + kk * 32), b_i16, idesc_row, 0u);
+        }
+        if (COLS) {
+          // D2[col, 32 pr + 2 k + j] = s_k * X[32 pr + 16 j + k, col]   (j = 0: first K = 16 step, j = 1: second)
+#pragma unroll
+          for (int pr = 0; pr < 4; pr++) {
+            q_mma_bf16(tmem_base + (u32)(128 + 32 * pr), q_desc_mn(tile + (32 * pr) * 128), b_p1, idesc_col, 0u);
+            q_mma_bf16(tmem_base + (u32)(128 + 32 * pr), q_desc_mn(tile + (32 * pr + 16) * 128), b_p2, idesc_col, 1u);
+          }
+        }
+        q_commit(empty0 + 8 * stage);      // the stage is free once the MMAs have read it
+        q_commit(tfull);                   // and the consumers may read tensor memory
+      }
+      __syncwarp();
+      tile_par ^= 1u;
+      if (++stage == kQStages) { stage = 0; phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers (warps 2..9)
+    const int quad = warp & 3;                      // tensor-memory lanes 32 * quad .. + 31 (fixed by the warp index)
+    const int half = (warp - 2) >> 2;               // columns 64 * half .. + 63 of D1 / of D2
+    u32 seed_r = p.seed_r, seed_c = p.seed_c;
+    if (ROUNDING != NVFP4_ROUND_NEAREST) {
+      if (p.seed_r_dev) seed_r = __ldg(p.seed_r_dev);
+      if (p.seed_c_dev) seed_c = __ldg(p.seed_c_dev);
+    }
+    const int nblk = p.C >> 4;                      // 16-column blocks per row
+    const int nmb = p.M >> 4;                       // 16-token blocks per column
+    const u32 t_lane = tmem_base + ((u32)(quad * 32) << 16);
+    u32 tile_par = 0;
+    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
+      const int mt = tw.mt, ct = tw.ct;
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(tfull, tile_par, abort_flag))) {
+        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
+        break;
+      }
+      tile_par ^= 1u;
+      q_fence_after();
+
+      if (ROWS) {
+        // lane = token; this warp's 64 columns = four 1x16 blocks, two per tensor-memory load
+        const long long tok = (long long)mt * kQTok + quad * 32 + lane;
+        const int blk0 = ct * (kQCol / 16) + half * 4;
+        uint2 o[4]; u32 sbs = 0u;
+#pragma unroll
+        for (int jj = 0; jj < 2; jj++) {
+          u32 r[32];
+          q_ld32(t_lane + (u32)(64 * half + 32 * jj), r);
+          q_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 2; j++) {
+            u64 P[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) P[i] = q_pack64(r[16 * j + 2 * i], r[16 * j + 2 * i + 1]);
+            const u32 sb = block_scale_byte(absmax16(P), ts_r);
+            const long long b = tok * nblk + blk0 + 2 * jj + j;
+            o[2 * jj + j] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)b * 16u);
+            sbs |= sb << (8 * (2 * jj + j));
+          }
+        }
+        if (!COLS) {
+          // nothing else reads this tile: hand tensor memory back before storing
+          q_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty);
+        }
+        unsigned char* dst = p.codes_r + tok * (p.C >> 1) + ct * (kQCol / 2) + half * 32;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[2].x, o[2].y, o[3].x, o[3].y);
+        // the four scale bytes are neighbours in both layouts
+        const long long so = p.linear ? tok * nblk + blk0
+                                      : ((long long)mt * (nblk >> 2) + ct * 2 + half) * 512 + lane * 16 + quad * 4;
+        *reinterpret_cast<u32*>(p.scales_r + so) = sbs;
+      }
+
+      if (COLS) {
+        // lane = column; this warp's 64 slots = four 16-token blocks, two (interleaved) per tensor-memory load
+        const long long col = (long long)ct * kQCol + quad * 32 + lane;
+        const int mb0 = mt * (kQTok / 16) + half * 4;
+        uint2 o[4]; u32 sbs = 0u;
+#pragma unroll
+        for (int pp = 0; pp < 2; pp++) {
+          u32 r[32];
+          q_ld32(t_lane + (u32)(128 + 64 * half + 32 * pp), r);
+          q_wait_ld();
+          if (pp == 1) {
+            // the last values of this tile are in registers: the next tile's MMAs may overwrite tensor memory
+            q_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty);
+          }
+          u64 P[16];
+#pragma unroll
+          for (int i = 0; i < 16; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
+#pragma unroll
+          for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+              if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
+          const u32 b0 = (u32)(col * nmb + mb0 + 2 * pp), b1 = b0 + 1u;
+          u32 sb0, sb1;
+          quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, block_key<ROUNDING>(seed_c, b0), block_key<ROUNDING>(seed_c, b1),
+                                    o[2 * pp], o[2 * pp + 1], sb0, sb1);
+          sbs |= (sb0 | (sb1 << 8)) << (16 * pp);
+        }
+        unsigned char* dst = p.codes_c + (col * nmb + mb0) * 8;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[2].x, o[2].y, o[3].x, o[3].y);
+        const long long so = p.linear ? col * nmb + mb0
+                                      : ((long long)ct * (nmb >> 2) + mt * 2 + half) * 512 + lane * 16 + quad * 4;
+        *reinterpret_cast<u32*>(p.scales_c + so) = sbs;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_flag) q_settle_copies();
+  q_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    q_fence_after();
+    q_tmem_dealloc(tmem_base, kQTmemCols);
+  }
+}
+
+static bool make_tc_map(CUtensorMap* map, const void* x, long long M, long long C, long long ldx) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ldx * 2)};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)kQTok};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int ROUNDING, bool ROWS, bool COLS>
+static int launch_tc(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t st) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return NVFP4_ERR_CUDA;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(quant_tc_kernel<ROUNDING, ROWS, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmem) != cudaSuccess)
+      return NVFP4_ERR_CUDA;
+    configured[dev] = true;
+  }
+  quant_tc_kernel<ROUNDING, ROWS, COLS><<<grid, kQThreads, kQSmem, st>>>(map, p);
+  NVFP4_LAUNCH_CHECK();
+  return NVFP4_OK;
+}
+
+template <int ROUNDING>
+static int launch_tc_mode(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t st) {
+  if (p.codes_r && p.codes_c) return launch_tc<ROUNDING, true, true>(map, p, grid, st);
+  if (p.codes_c) return launch_tc<ROUNDING, false, true>(map, p, grid, st);
+  return launch_tc<ROUNDING, true, false>(map, p, grid, st);
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+// Whether the tensor-core-fed kernel takes this call (shape and alignment); otherwise the scalar tile kernel runs.
+bool nvfp4_quant_tc_accepts(const void* x, long long ldx, int M, int C, const void* codes_r, const void* scales_r,
+                            const void* codes_c, const void* scales_c) {
+  if (M <= 0 || C <= 0 || (M % kQTok) || (C % kQCol) || ldx < C) return false;
+  return !((reinterpret_cast<uintptr_t>(x) & 15u) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes_r) & 15u) ||
+           (reinterpret_cast<uintptr_t>(codes_c) & 15u) || (reinterpret_cast<uintptr_t>(scales_r) & 3u) ||
+           (reinterpret_cast<uintptr_t>(scales_c) & 3u));
+}
+
+// Arguments as nvfp4_quant_tile, already validated by it.
+int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* codes_r, void* scales_r, void* codes_c,
+                          void* scales_c, int scale_layout, const float* amax, float* gs_r_out, float* gs_c_out,
+                          unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
+                          const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap map;
+  if (!make_tc_map(&map, x, M, C, ldx)) return NVFP4_ERR_CUDA;
+  TcParams p = {};
+  p.codes_r = static_cast<unsigned char*>(codes_r); p.scales_r = static_cast<unsigned char*>(scales_r);
+  p.codes_c = static_cast<unsigned char*>(codes_c); p.scales_c = static_cast<unsigned char*>(scales_c);
+  p.amax = amax; p.gs_r_out = gs_r_out; p.gs_c_out = gs_c_out;
+  p.M = M; p.C = C; p.linear = scale_layout == NVFP4_SCALES_LINEAR;
+  p.signs = signs & 0xFFFFu;
+  p.seed_r = seed_r; p.seed_c = seed_c; p.seed_r_dev = seed_r_dev; p.seed_c_dev = seed_c_dev;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
+  }
+  const long long ntiles = (long long)(M / kQTok) * (C / kQCol);
+  int grid = 2 * sms;
+  if (ntiles < grid) grid = (int)ntiles;
+  switch (rounding) {
+    case NVFP4_ROUND_NEAREST: return launch_tc_mode<NVFP4_ROUND_NEAREST>(map, p, grid, st);
+    case NVFP4_ROUND_SR_DITHER: return launch_tc_mode<NVFP4_ROUND_SR_DITHER>(map, p, grid, st);
+    case NVFP4_ROUND_SR_DITHER_K: return launch_tc_mode<NVFP4_ROUND_SR_DITHER_K>(map, p, grid, st);
+    default: return launch_tc_mode<NVFP4_ROUND_SR_HW>(map, p, grid, st);
+  }
+}
+
+// Status word of the tensor-core-fed kernel on the current device (merged into nvfp4_quant_tile_status).
+int nvfp4_quant_tc_status(int* out, int reset) {
+  if (cudaMemcpyFromSymbol(out, g_quant_tc_status, sizeof(int)) != cudaSuccess) return NVFP4_ERR_CUDA;
+  if (reset) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_quant_tc_status, &zero, sizeof(int)) != cudaSuccess) return NVFP4_ERR_CUDA;
+  }
+  return NVFP4_OK;
+}

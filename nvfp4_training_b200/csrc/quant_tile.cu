@@ -304,6 +304,23 @@ static int launch_tile_mode(const CUtensorMap& map, const TileParams& p, int gri
 
 using namespace nvfp4;
 
+// the tensor-core-fed kernel (quant_mma.cu)
+bool nvfp4_quant_tc_accepts(const void* x, long long ldx, int M, int C, const void* codes_r, const void* scales_r,
+                            const void* codes_c, const void* scales_c);
+int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* codes_r, void* scales_r, void* codes_c,
+                          void* scales_c, int scale_layout, const float* amax, float* gs_r_out, float* gs_c_out,
+                          unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
+                          const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
+int nvfp4_quant_tc_status(int* out, int reset);
+
+static int g_tile_path = 0;   // 0 = tensor-core-fed kernel where it applies, 1 = always the scalar tile kernel
+
+extern "C" int nvfp4_quant_tile_set_path(int path) {
+  if (path != 0 && path != 1) return NVFP4_ERR_ENUM;
+  g_tile_path = path;
+  return NVFP4_OK;
+}
+
 extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void* codes_r, void* scales_r, void* codes_c,
                                 void* scales_c, int scale_layout, const float* amax, float* gs_r_out, float* gs_c_out,
                                 unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
@@ -317,6 +334,9 @@ extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void
       (reinterpret_cast<uintptr_t>(codes_c) & 15u) || (reinterpret_cast<uintptr_t>(scales_c) & 7u))
     return NVFP4_ERR_ALIGN;
   if (M == 0 || C == 0) return NVFP4_OK;
+  if (g_tile_path == 0 && nvfp4_quant_tc_accepts(x, ldx, M, C, codes_r, scales_r, codes_c, scales_c))
+    return nvfp4_quant_tc_launch(x, ldx, M, C, codes_r, scales_r, codes_c, scales_c, scale_layout, amax, gs_r_out, gs_c_out,
+                                 signs, rounding, seed_r, seed_c, seed_r_dev, seed_c_dev, stream);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap map;
   if (!make_tile_map(&map, x, M, C, ldx)) return NVFP4_ERR_CUDA;
@@ -378,5 +398,9 @@ extern "C" int nvfp4_quant_tile_status(int* out, int reset) {
     const int zero = 0;
     if (cudaMemcpyToSymbol(g_quant_status, &zero, sizeof(int)) != cudaSuccess) return NVFP4_ERR_CUDA;
   }
+  int tc = 0;
+  const int rc = nvfp4_quant_tc_status(&tc, reset);
+  if (rc != NVFP4_OK) return rc;
+  if (*out == 0 && tc) *out = 16 + tc;    // 17 producer, 18 consumer, 19 MMA issuer of the tensor-core-fed kernel
   return NVFP4_OK;
 }

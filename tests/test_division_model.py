@@ -57,3 +57,47 @@ def test_tensor_scale_never_has_all_ones_significand():
         ams = (top[0] + np.arange(-4, 5)).astype(np.uint32).view(f32)
         gs = (ams / f32(2688)).astype(f32)
         assert not np.any((gs.view(np.uint32) & 0x7FFFFF) == 0x7FFFFF)
+
+
+def _rn32(fr):
+    """Round a Fraction to the nearest-even float32 (normal range)."""
+    from fractions import Fraction as Fr
+    import math
+    if fr == 0:
+        return f32(0)
+    s, a = (-1 if fr < 0 else 1), abs(fr)
+    e = math.floor(math.log2(a))
+    while Fr(2) ** e > a:
+        e -= 1
+    while Fr(2) ** (e + 1) <= a:
+        e += 1
+    q = a / Fr(2) ** (e - 23)
+    n = q.numerator // q.denominator
+    rem = q - n
+    if rem > Fr(1, 2) or (rem == Fr(1, 2) and n % 2 == 1):
+        n += 1
+    return f32(s * float(n) * 2.0 ** (e - 23))
+
+
+def test_two_word_reciprocal_division_by_block_scale_gives_the_same_codes():
+    """The kernels divide by the block scale as RN(t*rh + RN(t*rl)) with rh = RN(1/bs), rl = RN((1 - rh*bs)*rh).
+    A code only depends on how the quotient compares with the seven rounding boundaries b; RN(t/bs) is below,
+    on or above b exactly when t is below, on or above c = b*bs.  Exhaustively (exact rational arithmetic): for
+    every scale byte and boundary the form maps pred(c), c, succ(c) below, onto and above b -- and so does the
+    IEEE division.  Both are monotone in t, hence the same codes for every t."""
+    from fractions import Fraction as Fr
+    bounds = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    for sb in range(1, 127):
+        bs = O.e4m3_decode(np.array([sb], dtype=np.uint8))[0]
+        rh = f32(1.0) / bs
+        res = _rn32(Fr(1) - Fr(float(rh)) * Fr(float(bs)))
+        assert Fr(float(res)) == Fr(1) - Fr(float(rh)) * Fr(float(bs))            # the residual FMA is exact
+        rl = _rn32(Fr(float(res)) * Fr(float(rh)))
+        for b in bounds:
+            c = f32(b * bs)
+            assert Fr(float(c)) == Fr(b) * Fr(float(bs))
+            for t, rel in ((np.nextafter(c, f32(0)), -1), (c, 0), (np.nextafter(c, f32(np.inf)), 1)):
+                w = _rn32(Fr(float(t)) * Fr(float(rl)))
+                y = _rn32(Fr(float(t)) * Fr(float(rh)) + Fr(float(w)))
+                assert np.sign(float(y) - b) == rel, (sb, b, rel)
+                assert np.sign(float(f32(t / bs)) - b) == rel, (sb, b, rel)

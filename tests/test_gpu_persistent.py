@@ -115,10 +115,12 @@ MODES = [("rn", "SR_NONE", "ROUND_NEAREST"), ("dither", "SR_DITHER_NVQ", "ROUND_
          ("dither_k", "SR_DITHER_FP4K", "ROUND_SR_DITHER_K"), ("hw", "SR_HW", "ROUND_SR_HW")]
 
 
+@pytest.mark.parametrize("path", [0, 1], ids=["tensor_core_fed", "scalar"])
 @pytest.mark.parametrize("linear", [False, True])
 @pytest.mark.parametrize("name,omode,lmode", MODES)
-def test_tile_quantizer_many_tiles_per_cta(mods, name, omode, lmode, linear):
-    """[8192, 2048]: 2048 tiles of 128 x 64 over 296 CTAs, so the stage ring wraps and every CTA drains
+def test_tile_quantizer_many_tiles_per_cta(mods, name, omode, lmode, linear, path):
+    """[8192, 2048]: 2048 tiles of 128 x 64 (scalar kernel) or 1024 of 128 x 128 (tensor-core-fed kernel)
+    over 296 CTAs, so the stage ring wraps, the tensor-memory hand-off repeats and the scalar kernel drains
     transposed outputs inside its loop.  Whole-tensor byte equality for round-to-nearest; for the
     stochastic modes 8 row bands (row operand) and 8 column bands (transposed operand), first and last
     included, against the oracle with the bands' block indices."""
@@ -135,9 +137,13 @@ def test_tile_quantizer_many_tiles_per_cta(mods, name, omode, lmode, linear):
     sc = torch.empty(C * M // 16, dtype=torch.uint8, device="cuda")
     gr, gc = torch.empty(1, device="cuda"), torch.empty(1, device="cuda")
     seed_r, seed_c = 0x1234567, 0x89ABCDE
-    L.check(L.load().nvfp4_quant_tile(xd.data_ptr(), C, M, C, dr.data_ptr(), sr.data_ptr(), dc.data_ptr(), sc.data_ptr(),
-                                      L.SCALES_LINEAR if linear else L.SCALES_SWIZZLED, am.data_ptr(), gr.data_ptr(),
-                                      gc.data_ptr(), SIGNS, getattr(L, lmode), seed_r, seed_c, None, None, L.stream()), "tile")
+    assert L.load().nvfp4_quant_tile_set_path(path) == 0
+    try:
+        L.check(L.load().nvfp4_quant_tile(xd.data_ptr(), C, M, C, dr.data_ptr(), sr.data_ptr(), dc.data_ptr(), sc.data_ptr(),
+                                          L.SCALES_LINEAR if linear else L.SCALES_SWIZZLED, am.data_ptr(), gr.data_ptr(),
+                                          gc.data_ptr(), SIGNS, getattr(L, lmode), seed_r, seed_c, None, None, L.stream()), "tile")
+    finally:
+        L.load().nvfp4_quant_tile_set_path(0)
     torch.cuda.synchronize()
     L.check_status()
     codes_r, codes_c = u8(dr), u8(dc)

@@ -219,16 +219,36 @@ def test_cols_rht_sr_dither_bit_exact(mods, signs):
 SR_MODES = {"rn": None, "dither": "SR_DITHER_NVQ", "dither_k": "SR_DITHER_FP4K", "hw": "SR_HW"}
 
 
+def codes_equal_up_to_negative_zero(got, want, x_negzero):
+    """Packed codes equal except that positions whose INPUT was exactly -0 may carry code 0x0 instead of
+    0x8 (the tensor-core-fed kernel's documented difference); magnitudes must agree everywhere."""
+    g, w = O.unpack_codes(got), O.unpack_codes(want)
+    diff = g != w
+    if not diff.any():
+        return True
+    return bool(np.all(x_negzero[diff]) and np.all((g[diff] & 7) == 0) and np.all((w[diff] & 7) == 0))
+
+
+@pytest.fixture(params=[0, 1], ids=["tensor_core_fed", "scalar"])
+def tile_path(request, mods):
+    """Both kernels behind nvfp4_quant_tile: 0 = tensor-core fed where the shape allows, 1 = scalar."""
+    lib = mods[2].load()
+    assert lib.nvfp4_quant_tile_set_path(request.param) == 0
+    yield request.param
+    lib.nvfp4_quant_tile_set_path(0)
+
+
 @pytest.mark.parametrize("mode", ["rn", "dither", "dither_k", "hw"])
 @pytest.mark.parametrize("M,C", [(128, 128), (384, 640), (2048, 256)])
-def test_tile_quantizer_matches_both_oracles(mods, mode, M, C):
+def test_tile_quantizer_matches_both_oracles(mods, tile_path, mode, M, C):
     """The one-read tile kernel gives the row operand and the transposed RHT operand bit for bit,
     in every rounding mode, with separate seeds for the two outputs."""
     nvq, _, L = mods
     signs = 0x9C3A
     x = make_dy(M + C, M, C)
     x[5, :16] = 0.0                 # an all-zero block (scale byte 0)
-    x[16:32, 3] = -0.0
+    if tile_path == 1:
+        x[16:32, 3] = -0.0          # signed zeros: bit-exact in the scalar kernel (the other kernel: next test)
     xd = to_dev(x)
     if mode == "rn":
         r = O.quant_rows(x)
@@ -245,7 +265,35 @@ def test_tile_quantizer_matches_both_oracles(mods, mode, M, C):
     assert nvq.quant_tile_status() == 0
 
 
-def test_tile_quantizer_single_outputs_strided_input_and_device_seeds(mods):
+def test_tile_quantizer_tensor_core_path_negative_zero_inputs(mods):
+    """The tensor-core-fed kernel moves values through an MMA with a 0/1 matrix; an input that is exactly -0
+    comes out as +0, so its code may be 0x0 where the convert instruction gives 0x8.  Everything else --
+    negative values that round to zero included -- keeps its sign; magnitudes and scales are unchanged."""
+    nvq, _, L = mods
+    assert L.load().nvfp4_quant_tile_set_path(0) == 0
+    M, C, signs = 256, 256, 0x9C3A
+    x = make_dy(77, M, C)
+    x[16:32, 3] = -0.0
+    x[40, 64:80] = -0.0             # a whole row block of negative zeros
+    x[:, 200] = -1e-30              # negative and far below every block scale: rounds to -0, sign kept
+    x = bf16_round(x)
+    negz = (x == 0) & np.signbit(x)
+    r = O.quant_rows(x)
+    c = O.quant_cols_rht(x, signs)
+    qr, qc = nvq.quant_rows_cols_rht(to_dev(x), signs)
+    assert np.array_equal(O.unswizzle_scales(u8(qr.s), M, C // 16), r[1]) and qr.gs.item() == float(r[2])
+    assert np.array_equal(O.unswizzle_scales(u8(qc.s), C, M // 16), c[1]) and qc.gs.item() == float(c[2])
+    assert codes_equal_up_to_negative_zero(u8(qr.d), r[0], negz)
+    # transposed operand: a code can only differ where every input of its 16-token block that is not +0 is -0
+    gc, wc = O.unpack_codes(u8(qc.d)), O.unpack_codes(c[0])
+    diff = gc != wc
+    assert np.all((gc[diff] & 7) == 0) and np.all((wc[diff] & 7) == 0)
+    blk_has_negz = negz.T.reshape(C, M // 16, 16).any(-1).repeat(16, axis=1)
+    assert np.all(blk_has_negz[diff])
+    assert np.array_equal(nvq.dequant(qr).cpu().numpy(), O.dequant(r[0], r[1], r[2]))
+
+
+def test_tile_quantizer_single_outputs_strided_input_and_device_seeds(mods, tile_path):
     nvq, _, L = mods
     signs = 0x0F0F
     x = make_x(21, 256, 256)
