@@ -245,11 +245,9 @@ def isolated_kernels(cfg, T, peaks):
             "peak_basis": "4 x cuBLAS bf16 burst TFLOP/s (dense FP4 : bf16 = 4 : 1 on B200)",
             "frac_of_nominal_9000": achieved / 9000.0,
             "how": "all 15 GEMM shapes of the step timed alone with CUDA events, weighted by launches per step",
-            # `traffic` stays null: the figure is a launch mix, not one launch.  DRAM bytes of single launches from
-            # the ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum):
-            "traffic_ncu_mb": {"8192x11264x2048 bf16 out": {"read": 23.0, "write": 133.0, "algorithmic": 206.9},
-                               "8192x2048x11264 bf16 out": {"read": 64.9, "write": 11.5, "algorithmic": 98.4}}}
-
+            # `traffic` stays null: the figure is a launch mix, not one launch; DRAM bytes of single launches are in the
+            # ncu summaries under profiles/ (gemm_*.md)
+            "traffic_note": "launch mix: per-launch DRAM bytes are in profiles/gemm_*.md"}
     # quantizers on the largest activation of a block: [T, 5632] X and [T, 11264] dY
     x = [torch.randn(T, 5632, generator=g, device=dev).bfloat16() for _ in range(4)]
     am = [nvq.amax(t) for t in x]
@@ -639,18 +637,75 @@ def run_ours(args):
     barrier()
     ms_e2e = e0.elapsed_time(e1) / e2e_steps
 
-    t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
+    # ---- where a data-parallel step's time goes (N > 1), and the self-check of the results
+    ms_noar = ms_ar = 0.0
+    ar_bytes = 0
+    if world > 1 and not args.skip_isolated:
+        ms_noar, ms_ar, ar_bytes = comm_breakdown(stack, n_micro, max(2, min(args.steps, 5)))
+    verify = None if args.no_verify else verify_step(stack, n_micro, world, rank)
+
+    t = torch.tensor([ms, ms_e2e, ms_noar, ms_ar], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
+    ms, ms_e2e, ms_noar, ms_ar = t.tolist()
+    comm = None
+    if world > 1 and ms_ar > 0:
+        comm = {"step_without_allreduce_ms": ms_noar, "comm_exposed_ms": ms - ms_noar, "allreduce_alone_ms": ms_ar,
+                "allreduce_bytes": ar_bytes,
+                "allreduce_alone_busbw_gbs": 2.0 * (world - 1) / world * ar_bytes / (ms_ar * 1e-3) / 1e9,
+                "how": "same step with the collective switched off; the block-by-block all-reduces of all gradient "
+                       "buffers alone; CUDA events, max over ranks"}
 
-    roof = detail = cpu = None
-    if rank == 0:
-        del stack
+    roof = detail = cpu = sweeps = mb4096 = emitter = None
+    del stack
+    torch.cuda.empty_cache()
+    if world == 1 and not args.skip_isolated and mb != 4096:
+        # the same step in 4096-row microbatches (the reference's microbatch size): 16x the launches
+        plan2 = shard_plan(world, rank, GLOBAL_TOKENS, 4096)
+        st2 = LinearStack(cfg, plan2["microbatch"], torch.device("cuda", local), seed=0, input_seed=1000 + rank,
+                          use_graphs=not args.no_graphs)
+        if not args.no_graphs:
+            st2.capture()
+        for _ in range(2):
+            st2.step(plan2["n_micro"], False)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            st2.step(plan2["n_micro"], False)
+        e1.record()
+        torch.cuda.synchronize()
+        ms2 = e0.elapsed_time(e1) / 3
+        mb4096 = {"microbatch_tokens": 4096, "microbatches_per_rank": plan2["n_micro"], "ms_per_step": ms2,
+                  "tokens_per_s": GLOBAL_TOKENS / (ms2 * 1e-3)}
+        del st2
         torch.cuda.empty_cache()
+        # the same step through the operand emitters of the reference's trainer (llm-1b/model2.py:430-480): row
+        # operands with exact per-row scales, column operands with delayed per-tensor scales, no amax pass,
+        # rs[row] * gs in the GEMM epilogue.  A second, separately labelled number: a different scaling contract.
+        st3 = LinearStack(cfg, mb, torch.device("cuda", local), seed=0, input_seed=1000 + rank,
+                          use_graphs=not args.no_graphs, mode="emit")
+        if not args.no_graphs:
+            st3.capture()
+        for _ in range(2):
+            st3.step(n_micro, False)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            st3.step(n_micro, False)
+        e1.record()
+        torch.cuda.synchronize()
+        ms3 = e0.elapsed_time(e1) / 3
+        _lib.check_status()
+        emitter = {"contract": "per-row scales (row operands) + delayed per-tensor scales (column operands), no amax pass",
+                   "microbatch_tokens": mb, "ms_per_step": ms3, "tokens_per_s": GLOBAL_TOKENS / (ms3 * 1e-3)}
+        del st3
+        torch.cuda.empty_cache()
+    if rank == 0:
         if not args.skip_isolated:
             roof, detail = isolated_kernels(cfg, mb, peaks)
             roof["peak_source"] = peak_src
+            if world == 1:
+                sweeps = config_sweeps(cfg, peaks)
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             cpu_reference_sample(64, threads)
@@ -678,9 +733,14 @@ def run_ours(args):
             # this library's kernels in the timed region: per microbatch and projection amax + tile quantizer +
             # GEMM (forward) and amax + tile quantizer + 2 GEMMs (backward); per step and weight amax + quant_w2d
             "gpu_launches": args.steps * launches_per_step,
-            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "detail": detail,
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "verify": verify, "comm": comm,
+            "step_with_4096_row_microbatches": mb4096, "step_through_operand_emitters": emitter, "detail": detail,
+            "configs": sweeps,
         }
         print(json.dumps(line))
+        if verify is not None and not verify["ok"]:
+            sys.stderr.write("bench.py: result verification FAILED: " + json.dumps(verify) + "\n")
+            sys.exit(3)
     if world > 1:
         dist.destroy_process_group()
 
@@ -790,7 +850,9 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs left free for NCCL during backward when N > 1 (default: 32 at N >= 8, else 16)")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--skip-isolated", action="store_true", help="skip the isolated-kernel leg (for profiler runs)")
+    ap.add_argument("--skip-isolated", action="store_true",
+                    help="skip the isolated-kernel legs, the configuration sweeps and the communication breakdown (for profiler runs)")
+    ap.add_argument("--no-verify", action="store_true", help="skip the self-check of the results after the timed region")
     ap.add_argument("--case", default=None, choices=["gemm", "quant", "block"],
                     help="run one small single-kernel case instead of the benchmark (for profiler captures)")
     ap.add_argument("--M", type=int, default=8192)

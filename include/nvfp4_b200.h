@@ -56,6 +56,9 @@ extern "C" {
 #define NVFP4_ALPHA_ONE         0  /* alpha = 1                       (llm-1b/nvq.py:94 scale=False)    */
 #define NVFP4_ALPHA_GS          1  /* alpha = *pa * *pb               (llm-1b/nvq.py:93: gsA*gsB)       */
 #define NVFP4_ALPHA_AMAX        2  /* alpha = *pa * *pb * ka*kb/2688^2 (llm-1b/fp4k.cu:261)             */
+#define NVFP4_ALPHA_ROW         3  /* alpha[row] = pa[row] * *pb: per-row scale of the A operand times the
+                                      tensor scale of B, the separate `scale_rows` pass of llm-1b/model2.py:152-154
+                                      done in the epilogue; pa = device FP32 [M] */
 
 /* Library version, major*10000 + minor*100 + patch. */
 int nvfp4_version(void);
@@ -128,20 +131,21 @@ int nvfp4_quant_tile_set_path(int path);
 
 /* Reads (synchronously) the status word of nvfp4_quant_tile launches on the current device:
  * 0, or the role whose wait expired first (scalar kernel: 1 producer, 2 consumer; tensor-core-fed kernel:
- * 17 producer, 18 consumer, 19 MMA issuer); `reset` != 0 clears it. */
+ * 17 / 19 the loading and MMA-issuing warp waiting for a tile / for a free stage, 18 a consumer); `reset` != 0 clears it. */
 int nvfp4_quant_tile_status(int* out, int reset);
 
 /*
  * Row operand with an exact per-row FP32 scale, produced in one launch without a tensor-wide amax
  * pass: x [T, C] bf16 (row stride ldx) -> codes [T, C/2], swizzled block scales for [T, C/16] and
  * rs_out[t] = rowmax * (1/2688); a consumer multiplies the raw GEMM result by rs[t] * (weight scale).
- * Replaces kernel `row_emit` (llm-1b/emit.cu:263-285, and its fixed-width variants :228-260) and
- * launcher `emit.row_emit` (llm-1b/emit.py:72-79).  Arithmetic per row, IEEE FP32: inv = 2688/rowmax;
+ * Replaces launcher `emit.row_emit` (llm-1b/emit.py:62-68) with the kernels it dispatches: `row_emit`
+ * (llm-1b/emit.cu:263-285) and, for C == 11264, `row_emit_11264` (llm-1b/emit.cu:228-260).  Arithmetic per row, IEEE FP32: inv = 2688/rowmax;
  * per 16 values sb = e4m3((max*inv)*(1/6)), k = inv/dec(sb), code = rn(x*k).  sr != 0: stochastic
  * rounding by 11-bit mantissa dither (llm-1b/emit.cu:38-43) with the reference's random sequence:
  * lane l = (column/8) % 32 of row r runs s <- s*1664525+1013904223 from hash32(rng[0] ^ salt ^
- * hash32(r*32+l)) over its 8-column chunks in column order, one step per pair of values.
- * rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0, T % 128 == 0,
+ * hash32(r*32+l)) over its 8-column chunks in column order, one step per pair of values; for C == 11264 the
+ * sequence of `row_emit_11264`: four per lane, sequence s from hash32(rng[0] ^ salt ^ hash32(r*128+s*32+l)) over
+ * the chunks 4 j + s.  rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0, T % 128 == 0,
  * ldx % 8 == 0, x 16-byte aligned.
  */
 int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
@@ -197,7 +201,7 @@ int nvfp4_swizzle_scales(const void* s_linear, long long lds, int R, int C16, vo
  *   a, b      packed codes, row strides lda / ldb BYTES (multiples of 16), 16-byte aligned
  *   sa, sb    scales in the SWIZZLED layout for [M, K/16] and [N, K/16], 16-byte aligned
  *   c         bf16 or fp32 [M, N], row stride ldc ELEMENTS (multiple of 8), 16-byte aligned
- *   pa, pb    device FP32 scalars used by alpha_mode (may be null for NVFP4_ALPHA_ONE)
+ *   pa, pb    device FP32 scalars used by alpha_mode (may be null for NVFP4_ALPHA_ONE); NVFP4_ALPHA_ROW: pa = FP32 [M]
  *   accumulate  0: C = result; 1: C += result (fp32 only, atomic adds)
  *   splitk    >= 1: the K range is cut into that many slices of whole 256-element tiles, each
  *             added atomically into C; needs accumulate = 1 or C zeroed by the caller when > 1

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "libnvfp4_b200.so")
 SCALES_SWIZZLED, SCALES_LINEAR = 0, 1
 DTYPE_BF16, DTYPE_FP32 = 0, 1
 ROUND_NEAREST, ROUND_SR_DITHER, ROUND_SR_DITHER_K, ROUND_SR_HW = 0, 1, 2, 3
-ALPHA_ONE, ALPHA_GS, ALPHA_AMAX = 0, 1, 2
+ALPHA_ONE, ALPHA_GS, ALPHA_AMAX, ALPHA_ROW = 0, 1, 2, 3
 
 _c = ctypes
 _vp, _ll, _i, _u, _f, _sz = _c.c_void_p, _c.c_longlong, _c.c_int, _c.c_uint, _c.c_float, _c.c_size_t

@@ -1,6 +1,7 @@
 // Row-operand emitter with an exact per-row FP32 scale (sm_100a): one launch, no tensor-wide amax
-// pass.  Reference: `row_emit` of llm-1b/emit.cu:263-285 (launcher llm-1b/emit.py:72-79), whose
-// arithmetic (multiplications by reciprocals) and random stream it reproduces bit for bit.
+// pass.  Reference: `row_emit` of llm-1b/emit.cu:263-285 and, for 11264-column rows, `row_emit_11264`
+// (llm-1b/emit.cu:228-260), as the launcher llm-1b/emit.py:62-68 dispatches them; the arithmetic
+// (multiplications by reciprocals, IEEE here) and both random sequences are reproduced bit for bit.
 //
 // One warp per row.  Lane l owns the 8-column chunks 256 j + 8 l of its row: that is the unit the
 // reference's per-lane random sequence is defined on, and a warp-wide load of one chunk index j
@@ -54,8 +55,11 @@ __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg
 }
 
 // KEEP = number of chunks per lane held in registers (C == 256 * KEEP), or 0 for rows of any
-// length that are read twice.
-template <int KEEP, bool SR>
+// length that are read twice.  SUBS = 4 reproduces the random sequence of the kernel the reference's launcher
+// picks for 11264-column rows (`row_emit_11264` = row_reg<4, 11>, llm-1b/emit.cu:228-260, llm-1b/emit.py:64-67): four
+// sequences per lane, sequence s seeded with hash32(seed ^ salt ^ hash32(r*128 + s*32 + lane)) and walking the
+// chunks 4 j + s in order; SUBS = 1 is the generic `row_emit` sequence (one per lane, seeded with r*32 + lane).
+template <int KEEP, bool SR, int SUBS = 1>
 __global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int C,
                                                         u32* __restrict__ codes, unsigned char* __restrict__ scales,
                                                         float* __restrict__ rs_out, int T, const u32* __restrict__ rng,
@@ -81,7 +85,18 @@ __global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __r
   const float am = __uint_as_float(mm << 16);
   const float inv = am > 0.f ? __fdiv_rn(kFp4E4m3, am) : 0.f;
   if (lane == 0) rs_out[r] = __fmul_rn(am, 1.f / kFp4E4m3);
-  u32 lcg = hash32((SR ? __ldg(rng) : 0u) ^ salt ^ hash32((u32)(r * 32 + lane)));
+  const u32 seed = (SR ? __ldg(rng) : 0u) ^ salt;
+  if (SUBS == 4) {
+    u32 lcg4[4];
+#pragma unroll
+    for (int sidx = 0; sidx < 4; sidx++) lcg4[sidx] = hash32(seed ^ hash32((u32)(r * 128 + sidx * 32 + lane)));
+    for (int c = 0; c < C; c += 1024)
+#pragma unroll
+      for (int sidx = 0; sidx < 4; sidx++)
+        emit_chunk<SR>(ld_chunk(row + c + sidx * 256), inv, lcg4[sidx], r, c + sidx * 256 + lane * 8, C, codes, scales, lane);
+    return;
+  }
+  u32 lcg = hash32(seed ^ hash32((u32)(r * 32 + lane)));
   if (KEEP > 0) {
 #pragma unroll
     for (int j = 0; j < NK; j++) emit_chunk<SR>(kept[j], inv, lcg, r, j * 256 + lane * 8, C, codes, scales, lane);
@@ -116,6 +131,10 @@ extern "C" int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void*
     case 8: launch_rows<8>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
     case 12: launch_rows<12>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
     case 22: launch_rows<22>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 44:   // 11264 columns: the reference's launcher switches to its four-sequence kernel here
+      if (sr) emit_rows_kernel<0, true, 4><<<blocks, 256, 0, st>>>(xp, ldx, C, cp, sp, rs_out, T, rng, salt);
+      else emit_rows_kernel<0, false, 1><<<blocks, 256, 0, st>>>(xp, ldx, C, cp, sp, rs_out, T, rng, salt);
+      break;
     default: launch_rows<0>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
   }
   NVFP4_LAUNCH_CHECK();

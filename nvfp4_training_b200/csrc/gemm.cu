@@ -317,10 +317,11 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (lane == 0) mbar_arrive(smem_u32(acc_empty + acc));
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1u; }
 
+      const long long row = (long long)mt * kBM + quad * 32 + lane;
       float alpha = 1.f;
       if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
-      const long long row = (long long)mt * kBM + quad * 32 + lane;
+      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = __ldg(p.pa + row) * __ldg(p.pb);   // this lane's row
       const long long col = (long long)nt * BN + half * kEpiCols;
       if (p.c_fp32) {
         float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
@@ -782,10 +783,11 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #undef NVFP4_LD16
 #undef NVFP4_RELEASE_ACC
 
+      const long long row0 = (long long)mt * 256 + rank * 128 + quad * 32;      // first row of this warp
       float alpha = 1.f;
       if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
-      const long long row0 = (long long)mt * 256 + rank * 128 + quad * 32;      // first row of this warp
+      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = __ldg(p.pa + row0 + lane) * __ldg(p.pb);   // each lane stages its own row
       const long long col0 = (long long)nt * BN + half * NC;
       void* cbase = p.c_fp32 ? static_cast<void*>(static_cast<float*>(p.c) + row0 * p.ldc + col0)
                              : static_cast<void*>(static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0);
@@ -882,7 +884,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
                           void* c, int c_dtype, long long ldc, int M, int N, int K, int alpha_mode, const float* pa,
                           const float* pb, float ka, float kb, int accumulate, int splitk, int* status, void* stream) {
   if (!a || !sa || !b || !sb || !c) return NVFP4_ERR_NULL;
-  if (alpha_mode < NVFP4_ALPHA_ONE || alpha_mode > NVFP4_ALPHA_AMAX) return NVFP4_ERR_ENUM;
+  if (alpha_mode < NVFP4_ALPHA_ONE || alpha_mode > NVFP4_ALPHA_ROW) return NVFP4_ERR_ENUM;
   if (alpha_mode != NVFP4_ALPHA_ONE && (!pa || !pb)) return NVFP4_ERR_NULL;
   if (c_dtype != NVFP4_DTYPE_BF16 && c_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
   if (M < 0 || N < 0 || K < 0 || (M % 128) || (N % 128) || (K % 64) || splitk < 1) return NVFP4_ERR_SHAPE;

@@ -23,8 +23,9 @@
 // dequantized value is the same.  Inf/NaN inputs poison their 16-value group (0 * Inf), as they
 // poison the tensor's amax in every implementation.
 //
-// Two CTAs per SM, each with 256 tensor-memory columns (D1 and D2 of one tile); while the consumers
-// finish a tile's last values the next tile's MMAs already run.  Every mbarrier wait is bounded: on
+// Two CTAs per SM, each with nine warps (one loads tiles and issues the MMAs, eight quantize) and 256
+// tensor-memory columns used as two buffers, so that MMAs into one buffer run while the consumers work on
+// the other; the consumers' tensor-memory loads are software-pipelined.  Every mbarrier wait is bounded: on
 // expiry the CTA raises an abort flag, stores a role code in the quantizer status word, lets copies
 // in flight land, frees its tensor memory and returns.
 #include "tma.cuh"
@@ -37,10 +38,10 @@ constexpr int kQBoxBytes = kQTok * 64 * 2;    // 16 KB
 constexpr int kQTileBytes = 2 * kQBoxBytes;
 constexpr int kQStages = 3;
 constexpr int kQConsumerWarps = 8;
-constexpr int kQThreads = 32 * (2 + kQConsumerWarps);
-constexpr int kQI16Bytes = 16 * 128, kQPermBytes = 32 * 128;
+constexpr int kQThreads = 32 * (1 + kQConsumerWarps);
+constexpr int kQPermBytes = 32 * 128;
 constexpr int kQSmem = kQStages * kQTileBytes + 1024 /*I16, padded*/ + 1024 + 2 * kQPermBytes + 1024 /*alignment slack*/;
-constexpr int kQTmemCols = 256;               // D1 at columns 0..127, D2 at 128..255
+constexpr int kQTmemCols = 256;               // two buffers of 128 columns
 
 __device__ int g_quant_tc_status;             // 0, or the role code of the first wait that expired
 
@@ -87,7 +88,27 @@ __device__ __forceinline__ void q_ld32(u32 taddr, u32 (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void q_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void q_ld16(u32 taddr, u32 (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+// Wait for this thread's tensor-memory loads.  The loaded registers pass through the statement as in/out operands,
+// so that the compiler cannot schedule a use of them before the wait.
+__device__ __forceinline__ void q_wait_ld16(u32 (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]) :: "memory");
+}
+__device__ __forceinline__ void q_wait_ld32(u32 (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) :: "memory");
+}
 
 __device__ __forceinline__ u64 q_pack64(u32 lo, u32 hi) {
   u64 d;
@@ -133,7 +154,7 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) float lut_r[kLutFloats];
   __shared__ __align__(8) float lut_c[kLutFloats];
-  __shared__ __align__(8) u64 bars[2 * kQStages + 2];
+  __shared__ __align__(8) u64 bars[2 * kQStages + 4];
   __shared__ u32 tmem_slot;
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
@@ -143,7 +164,7 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   const u32 i16_s = tiles0 + kQStages * kQTileBytes;            // 16 rows x 128 B, then padding to 1024
   const u32 p1_s = i16_s + 2048, p2_s = p1_s + kQPermBytes;     // 32 rows x 128 B each (1024-byte aligned)
   const u32 full0 = smem_u32(bars), empty0 = full0 + 8 * kQStages;
-  const u32 tfull = empty0 + 8 * kQStages, tempty = tfull + 8;
+  const u32 tfull = empty0 + 8 * kQStages, tempty = tfull + 16;     // two tensor-memory buffers: [2] each
 
   // ---- constants of the MMAs: identity and the two sign/interleave matrices, in the K-major 128-byte-swizzle
   // layout (row n at n * 128 bytes, its 16-byte chunk j at position j ^ (n & 7)); only K columns 0..15 are read
@@ -165,13 +186,12 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   if (threadIdx.x == 0) {
     abort_word = 0;
     for (int s = 0; s < kQStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(tfull, 1);
-    mbar_init(tempty, kQConsumerWarps);
+    for (int b = 0; b < 2; b++) { mbar_init(tfull + 8 * b, 1); mbar_init(tempty + 8 * b, kQConsumerWarps); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // the tensor core reads shared memory through the asynchronous proxy
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  if (warp == 1) {
+  if (warp == 0) {
     q_tmem_alloc(smem_u32(&tmem_slot), kQTmemCols);
     q_tmem_relinquish();
   }
@@ -186,14 +206,18 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   q_fence_after();
   const u32 tmem_base = tmem_slot;
 
+  // Tensor memory holds two buffers of 128 columns, each with its own full / empty barrier.  With both outputs
+  // buffer 0 is D1 (row operand) and buffer 1 is D2 (transposed operand) of the same tile: the consumers hand D1
+  // back after its last load, so the next tile's row MMAs run while they quantize the transposed half, and vice
+  // versa.  With one output the two buffers hold the same kind of result for alternating tiles.
+  constexpr bool BOTH = ROWS && COLS;
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    u32 stage = 0, phase = 0;
-    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(empty0 + 8 * stage, phase ^ 1u, abort_flag))) {
-        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 1);
-        break;
-      }
+    // ------------------------------------------------------------------ TMA producer and MMA issuer (one warp)
+    // Loads run kQStages tiles ahead: the load of tile n + kQStages is issued once the MMAs of tile n have
+    // released their stage.
+    constexpr u32 idesc_row = q_idesc(16, false), idesc_col = q_idesc(32, true);
+    const u64 b_i16 = q_desc_k(i16_s), b_p1 = q_desc_k(p1_s), b_p2 = q_desc_k(p2_s);
+    auto load_tile = [&](const TcWalk& tw, u32 stage) {
       if (elect_one()) {
         const u32 bar = full0 + 8 * stage, dst = tiles0 + stage * kQTileBytes;
         mbar_arrive_expect_tx(bar, kQTileBytes);
@@ -201,51 +225,73 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
         tma_load_2d(dst + kQBoxBytes, &map, tw.ct * kQCol + 64, tw.mt * kQTok, bar);
       }
       __syncwarp();
-      if (++stage == kQStages) { stage = 0; phase ^= 1u; }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    constexpr u32 idesc_row = q_idesc(16, false), idesc_col = q_idesc(32, true);
-    const u64 b_i16 = q_desc_k(i16_s), b_p1 = q_desc_k(p1_s), b_p2 = q_desc_k(p2_s);
-    u32 stage = 0, phase = 0, tile_par = 0;
-    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
-      // tensor memory free (the consumers have read the previous tile), then the tile's bytes have landed
-      bool ok = mbar_wait(tempty, tile_par ^ 1u, abort_flag);
-      ok = ok && mbar_wait(full0 + 8 * stage, phase, abort_flag);
+    };
+    // D[token, 64 b + 16 kk + n] = sum_k X[token, 64 b + 16 kk + k] * I[n, k]
+    auto row_mmas = [&](u32 tile, u32 d) {
+#pragma unroll
+      for (int b = 0; b < 2; b++)
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          q_mma_bf16(d + (u32)(64 * b + 16 * kk), q_desc_k(tile + b * kQBoxBytes + kk * 32), b_i16, idesc_row, 0u);
+    };
+    // D[col, 32 pr + 2 k + j] = s_k * X[32 pr + 16 j + k, col]   (j = 0: first K = 16 step, j = 1: second)
+    auto col_mmas = [&](u32 tile, u32 d) {
+#pragma unroll
+      for (int pr = 0; pr < 4; pr++) {
+        q_mma_bf16(d + (u32)(32 * pr), q_desc_mn(tile + (32 * pr) * 128), b_p1, idesc_col, 0u);
+        q_mma_bf16(d + (u32)(32 * pr), q_desc_mn(tile + (32 * pr + 16) * 128), b_p2, idesc_col, 1u);
+      }
+    };
+    TcWalk ahead(p.M, p.C);
+    for (u32 s = 0; s < (u32)kQStages && ahead.valid(); s++, ahead.next()) load_tile(ahead, s);
+    u32 stage = 0, phase = 0, n = 0;
+    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next(), n++) {
+      // buffers and their parities: with both outputs each buffer is used once per tile, else once per two tiles
+      const u32 buf0 = BOTH ? 0u : (n & 1u), par = BOTH ? (n & 1u) : ((n >> 1) & 1u);
+      bool ok = mbar_wait(full0 + 8 * stage, phase, abort_flag);                 // the tile's bytes have landed
+      ok = ok && mbar_wait(tempty + 8 * buf0, par ^ 1u, abort_flag);             // and the first buffer is free
       if (!__all_sync(0xffffffffu, ok)) {
-        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 3);
+        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 1);
         break;
       }
       q_fence_after();
+      const u32 tile = tiles0 + stage * kQTileBytes;
       if (elect_one()) {
-        const u32 tile = tiles0 + stage * kQTileBytes;
-        if (ROWS) {
-          // D1[token, 64 b + 16 kk + n] = sum_k X[token, 64 b + 16 kk + k] * I[n, k]
-#pragma unroll
-          for (int b = 0; b < 2; b++)
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++)
-              q_mma_bf16(tmem_base + (u32)(64 * b + 16 * kk), q_desc_k(tile + b * kQBoxBytes + kk * 32), b_i16, idesc_row, 0u);
-        }
-        if (COLS) {
-          // D2[col, 32 pr + 2 k + j] = s_k * X[32 pr + 16 j + k, col]   (j = 0: first K = 16 step, j = 1: second)
-#pragma unroll
-          for (int pr = 0; pr < 4; pr++) {
-            q_mma_bf16(tmem_base + (u32)(128 + 32 * pr), q_desc_mn(tile + (32 * pr) * 128), b_p1, idesc_col, 0u);
-            q_mma_bf16(tmem_base + (u32)(128 + 32 * pr), q_desc_mn(tile + (32 * pr + 16) * 128), b_p2, idesc_col, 1u);
-          }
-        }
-        q_commit(empty0 + 8 * stage);      // the stage is free once the MMAs have read it
-        q_commit(tfull);                   // and the consumers may read tensor memory
+        if (ROWS) row_mmas(tile, tmem_base + 128u * buf0); else col_mmas(tile, tmem_base + 128u * buf0);
+        if (!BOTH) q_commit(empty0 + 8 * stage);      // the stage is free once the MMAs have read it
+        q_commit(tfull + 8 * buf0);                   // and the consumers may read this buffer
       }
       __syncwarp();
-      tile_par ^= 1u;
+      if (BOTH) {
+        if (!__all_sync(0xffffffffu, mbar_wait(tempty + 8, par ^ 1u, abort_flag))) {
+          if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 1);
+          break;
+        }
+        q_fence_after();
+        if (elect_one()) {
+          col_mmas(tile, tmem_base + 128u);
+          q_commit(empty0 + 8 * stage);
+          q_commit(tfull + 8);
+        }
+        __syncwarp();
+      }
+      if (ahead.valid()) {
+        // refill this stage as soon as the MMAs just issued have read it
+        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase, abort_flag))) {
+          if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 3);
+          break;
+        }
+        load_tile(ahead, stage);
+        ahead.next();
+      }
       if (++stage == kQStages) { stage = 0; phase ^= 1u; }
     }
   } else {
-    // ------------------------------------------------------------------ consumers (warps 2..9)
+    // ------------------------------------------------------------------ consumers (warps 1..8)
+    // The tensor-memory loads are software-pipelined: while a chunk (a 1x16 block of the row operand, or two
+    // 16-token blocks of the transposed one) is being quantized, the load of the next chunk is in flight.
     const int quad = warp & 3;                      // tensor-memory lanes 32 * quad .. + 31 (fixed by the warp index)
-    const int half = (warp - 2) >> 2;               // columns 64 * half .. + 63 of D1 / of D2
+    const int half = (warp - 1) >> 2;               // columns 64 * half .. + 63 of a buffer
     u32 seed_r = p.seed_r, seed_c = p.seed_c;
     if (ROUNDING != NVFP4_ROUND_NEAREST) {
       if (p.seed_r_dev) seed_r = __ldg(p.seed_r_dev);
@@ -253,89 +299,98 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     }
     const int nblk = p.C >> 4;                      // 16-column blocks per row
     const int nmb = p.M >> 4;                       // 16-token blocks per column
-    const u32 t_lane = tmem_base + ((u32)(quad * 32) << 16);
-    u32 tile_par = 0;
-    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next()) {
+    const u32 t_lane = tmem_base + ((u32)(quad * 32) << 16) + (u32)(64 * half);
+    u32 n = 0;
+    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next(), n++) {
       const int mt = tw.mt, ct = tw.ct;
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(tfull, tile_par, abort_flag))) {
+      const u32 buf0 = BOTH ? 0u : (n & 1u), par = BOTH ? (n & 1u) : ((n >> 1) & 1u);
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(tfull + 8 * buf0, par, abort_flag))) {
         if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
         break;
       }
-      tile_par ^= 1u;
       q_fence_after();
 
+      // lane = token of the row operand / column of the transposed operand
+      const long long tok = (long long)mt * kQTok + quad * 32 + lane;
+      const long long col = (long long)ct * kQCol + quad * 32 + lane;
+      const int blk0 = ct * (kQCol / 16) + half * 4;     // first of this warp's four 1x16 blocks of a row
+      const int mb0 = mt * (kQTok / 16) + half * 4;      // first of this warp's four 16-token blocks of a column
+      uint2 orow[4], ocol[4];
+      u32 sb_row = 0u, sb_col = 0u;
+      u32 ra[16], rb[16], rc[32];
+
+      auto row_block = [&](const u32 (&r)[16], int j) {
+        u64 P[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
+        const u32 sb = block_scale_byte(absmax16(P), ts_r);
+        const long long b = tok * nblk + blk0 + j;
+        orow[j] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)b * 16u);
+        sb_row |= sb << (8 * j);
+      };
+      auto col_pair = [&](const u32 (&r)[32], int pp) {
+        u64 P[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
+#pragma unroll
+        for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+          for (int i = 0; i < 16; i++)
+            if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
+        const u32 b0 = (u32)(col * nmb + mb0 + 2 * pp), b1 = b0 + 1u;
+        u32 sb0, sb1;
+        quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, block_key<ROUNDING>(seed_c, b0), block_key<ROUNDING>(seed_c, b1),
+                                  ocol[2 * pp], ocol[2 * pp + 1], sb0, sb1);
+        sb_col |= (sb0 | (sb1 << 8)) << (16 * pp);
+      };
+      // a buffer has been read completely: the next MMAs into it may start
+      auto release = [&](u32 buf) {
+        q_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty + 8 * buf);
+      };
+
       if (ROWS) {
-        // lane = token; this warp's 64 columns = four 1x16 blocks, two per tensor-memory load
-        const long long tok = (long long)mt * kQTok + quad * 32 + lane;
-        const int blk0 = ct * (kQCol / 16) + half * 4;
-        uint2 o[4]; u32 sbs = 0u;
-#pragma unroll
-        for (int jj = 0; jj < 2; jj++) {
-          u32 r[32];
-          q_ld32(t_lane + (u32)(64 * half + 32 * jj), r);
-          q_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 2; j++) {
-            u64 P[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) P[i] = q_pack64(r[16 * j + 2 * i], r[16 * j + 2 * i + 1]);
-            const u32 sb = block_scale_byte(absmax16(P), ts_r);
-            const long long b = tok * nblk + blk0 + 2 * jj + j;
-            o[2 * jj + j] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)b * 16u);
-            sbs |= sb << (8 * (2 * jj + j));
+        const u32 t = t_lane + 128u * buf0;
+        q_ld16(t, ra);      q_wait_ld16(ra);
+        q_ld16(t + 16, rb); row_block(ra, 0);  q_wait_ld16(rb);
+        q_ld16(t + 32, ra); row_block(rb, 1);  q_wait_ld16(ra);
+        q_ld16(t + 48, rb); row_block(ra, 2);  q_wait_ld16(rb);
+        release(buf0);
+        if (BOTH) {
+          // the transposed half of the same tile: start its first load before the last row block is quantized
+          const bool ok2 = mbar_wait_parked(tfull + 8, par, abort_flag);
+          if (!__all_sync(0xffffffffu, ok2)) {
+            if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
+            break;
           }
+          q_fence_after();
+          q_ld32(t_lane + 128u, rc);
         }
-        if (!COLS) {
-          // nothing else reads this tile: hand tensor memory back before storing
-          q_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tempty);
-        }
+        row_block(rb, 3);
         unsigned char* dst = p.codes_r + tok * (p.C >> 1) + ct * (kQCol / 2) + half * 32;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
-        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[2].x, o[2].y, o[3].x, o[3].y);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(orow[0].x, orow[0].y, orow[1].x, orow[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(orow[2].x, orow[2].y, orow[3].x, orow[3].y);
         // the four scale bytes are neighbours in both layouts
         const long long so = p.linear ? tok * nblk + blk0
                                       : ((long long)mt * (nblk >> 2) + ct * 2 + half) * 512 + lane * 16 + quad * 4;
-        *reinterpret_cast<u32*>(p.scales_r + so) = sbs;
+        *reinterpret_cast<u32*>(p.scales_r + so) = sb_row;
       }
-
       if (COLS) {
-        // lane = column; this warp's 64 slots = four 16-token blocks, two (interleaved) per tensor-memory load
-        const long long col = (long long)ct * kQCol + quad * 32 + lane;
-        const int mb0 = mt * (kQTok / 16) + half * 4;
-        uint2 o[4]; u32 sbs = 0u;
-#pragma unroll
-        for (int pp = 0; pp < 2; pp++) {
-          u32 r[32];
-          q_ld32(t_lane + (u32)(128 + 64 * half + 32 * pp), r);
-          q_wait_ld();
-          if (pp == 1) {
-            // the last values of this tile are in registers: the next tile's MMAs may overwrite tensor memory
-            q_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty);
-          }
-          u64 P[16];
-#pragma unroll
-          for (int i = 0; i < 16; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
-#pragma unroll
-          for (int h = 1; h < 16; h <<= 1)
-#pragma unroll
-            for (int i = 0; i < 16; i++)
-              if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
-          const u32 b0 = (u32)(col * nmb + mb0 + 2 * pp), b1 = b0 + 1u;
-          u32 sb0, sb1;
-          quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, block_key<ROUNDING>(seed_c, b0), block_key<ROUNDING>(seed_c, b1),
-                                    o[2 * pp], o[2 * pp + 1], sb0, sb1);
-          sbs |= (sb0 | (sb1 << 8)) << (16 * pp);
-        }
+        const u32 cbuf = BOTH ? 1u : buf0;
+        const u32 t = t_lane + 128u * cbuf;
+        if (!BOTH) q_ld32(t, rc);
+        q_wait_ld32(rc);
+        col_pair(rc, 0);
+        q_ld32(t + 32, rc); q_wait_ld32(rc);
+        release(cbuf);
+        col_pair(rc, 1);
         unsigned char* dst = p.codes_c + (col * nmb + mb0) * 8;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0].x, o[0].y, o[1].x, o[1].y);
-        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[2].x, o[2].y, o[3].x, o[3].y);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(ocol[0].x, ocol[0].y, ocol[1].x, ocol[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(ocol[2].x, ocol[2].y, ocol[3].x, ocol[3].y);
         const long long so = p.linear ? col * nmb + mb0
                                       : ((long long)ct * (nmb >> 2) + mt * 2 + half) * 512 + lane * 16 + quad * 4;
-        *reinterpret_cast<u32*>(p.scales_c + so) = sbs;
+        *reinterpret_cast<u32*>(p.scales_c + so) = sb_col;
       }
     }
   }
@@ -345,7 +400,7 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   if (*abort_flag) q_settle_copies();
   q_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 0) {
     q_fence_after();
     q_tmem_dealloc(tmem_base, kQTmemCols);
   }

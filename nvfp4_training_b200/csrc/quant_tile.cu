@@ -401,6 +401,6 @@ extern "C" int nvfp4_quant_tile_status(int* out, int reset) {
   int tc = 0;
   const int rc = nvfp4_quant_tc_status(&tc, reset);
   if (rc != NVFP4_OK) return rc;
-  if (*out == 0 && tc) *out = 16 + tc;    // 17 producer, 18 consumer, 19 MMA issuer of the tensor-core-fed kernel
+  if (*out == 0 && tc) *out = 16 + tc;    // tensor-core-fed kernel: 17 / 19 its loading and MMA-issuing warp (waiting for a tile / a free stage), 18 a consumer
   return NVFP4_OK;
 }

@@ -2,7 +2,9 @@
 row operand with an exact per-row FP32 scale, so no tensor-wide amax pass precedes it, and the raw
 block-scaled GEMM whose result the consumer multiplies by `rs[t] * gs`.
 
-Built so far: `RowQ`, `ColQ`, `row_emit`, `col_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`, `mm_col`.
+Built: `RowQ`, `ColQ`, `row_emit`, `col_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`, `mm_col`, `scale_rows`, `dequant`.
+`mm_row_w` / `mm_row_wt` / `mm_col` take `scale=True` to apply `rs[row] * gs` (resp. the two delayed tensor scales) in
+the GEMM epilogue, which the reference does in a separate elementwise pass (`scale_rows`, llm-1b/model2.py:152-154).
 The fused producers (`rms_emit`, `swiglu_emit`) and `mom_acc` are not built.
 """
 import torch
@@ -109,17 +111,51 @@ def mm(ad, as_, bd, bs, out_dtype=torch.bfloat16):
     return nvq.mm(a, b, out_dtype=out_dtype, scale=False)[0]
 
 
-def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32):
+def _gemm(ad, as_, bd, bs, out, alpha_mode, pa, pb, accumulate=False):
+    M, N, K = ad.shape[0], bd.shape[0], ad.shape[1] * 2
+    assert bd.shape[1] * 2 == K and out.shape == (M, N) and out.stride(1) == 1
+    L.require_cuda(ad, bd, out)
+    L.check(L.load().nvfp4_gemm(L.ptr(ad), L.ptr(as_), ad.stride(0), L.ptr(bd), L.ptr(bs), bd.stride(0), L.ptr(out),
+                                L.DTYPE_FP32 if out.dtype == torch.float32 else L.DTYPE_BF16, out.stride(0), M, N, K,
+                                alpha_mode, L.ptr(pa), L.ptr(pb), 1.0, 1.0, int(accumulate), 1,
+                                L.ptr(L.status_word(ad.device)), L.stream()), "gemm")
+    return out
+
+
+def scale_rows(raw, rs, gs):
+    """true = raw * rs[:, None] * gs as bf16: the reference's separate pass (llm-1b/model2.py:152-154)."""
+    return (raw.float() * (rs[:, None] * gs)).to(torch.bfloat16)
+
+
+def dequant(d, s, rs):
+    """Row operand back to FP32 [R, C] (tests; `E.dequant` of llm-1b/test_emit.py)."""
+    R, C = d.shape[0], d.shape[1] * 2
+    return nvq.dequant(nvq.Q(d.view(F4), s.view(F8), _one(d.device))) * rs[:, None]
+
+
+def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32, scale=False, amax_a=None, amax_b=None, out=None, accumulate=False):
     """wgrad: dW_raw = Q(H dy)^T Q(H x) [N, K]; true = raw * gsA * gsB with gs = amax_use/2688
-    (llm-1b/emit.py:148-150)."""
-    return mm(a.d, a.s, b.d, b.s, out_dtype=out_dtype)
+    (llm-1b/emit.py:148-150).  scale=True: the two delayed amax words (device fp32 [1]) are given and
+    the product by gsA * gsB happens in the epilogue; `out` / `accumulate`: in-place FP32 accumulation."""
+    if not scale:
+        return mm(a.d, a.s, b.d, b.s, out_dtype=out_dtype)
+    if out is None:
+        out = torch.empty(a.d.shape[0], b.d.shape[0], dtype=out_dtype, device=a.d.device)
+    return _gemm(a.d, a.s, b.d, b.s, out, L.ALPHA_AMAX, amax_a, amax_b, accumulate)
 
 
-def mm_row_w(q: RowQ, w: WQ):
-    """forward: y_raw = Q(x) @ Q(W)^T; true y = y_raw * q.rs[:, None] * w.gs (llm-1b/emit.py:136-140)."""
-    return mm(q.d, q.s, w.d, w.s)
+def mm_row_w(q: RowQ, w: WQ, scale=False):
+    """forward: y_raw = Q(x) @ Q(W)^T; true y = y_raw * q.rs[:, None] * w.gs (llm-1b/emit.py:136-140).
+    scale=True returns the true y (bf16), scaled per row in the GEMM epilogue."""
+    if not scale:
+        return mm(q.d, q.s, w.d, w.s)
+    out = torch.empty(q.d.shape[0], w.d.shape[0], dtype=torch.bfloat16, device=q.d.device)
+    return _gemm(q.d, q.s, w.d, w.s, out, L.ALPHA_ROW, q.rs, w.gs)
 
 
-def mm_row_wt(q: RowQ, w: WQ):
+def mm_row_wt(q: RowQ, w: WQ, scale=False):
     """dgrad: dx_raw = Q(dy) @ Q(W); true = raw * q.rs[:, None] * w.gs (llm-1b/emit.py:143-145)."""
-    return mm(q.d, q.s, w.td, w.ts)
+    if not scale:
+        return mm(q.d, q.s, w.td, w.ts)
+    out = torch.empty(q.d.shape[0], w.td.shape[0], dtype=torch.bfloat16, device=q.d.device)
+    return _gemm(q.d, q.s, w.td, w.ts, out, L.ALPHA_ROW, q.rs, w.gs)

@@ -19,8 +19,10 @@ from dataclasses import dataclass
 
 import torch
 
-from . import _lib, nvq
+from . import _lib, emit, nvq
 from .linear import _RHT_SIGNS, linear_bwd, linear_fwd
+
+EMIT_MARGIN = 2.0      # delayed column scales use the last observed amax times this (llm-1b/model2.py:13,497-499)
 
 
 @dataclass
@@ -76,7 +78,7 @@ def allreduce_sum_(tensors, group=None):
 
 
 class _Proj:
-    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx", "qxt")
+    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx", "qxt", "wq", "cx")
 
 
 def student_t(shape, gen, device, df=3):
@@ -87,10 +89,16 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor"):
         """`seed` initialises the weights (the same on every rank of a data-parallel job: replicated
         weights), `input_seed` the synthetic activation / gradient pools (different per rank: each rank
-        holds its own rows of the batch; default seed + 1000)."""
+        holds its own rows of the batch; default seed + 1000).
+        `mode`: "tensor" = the per-tensor-scale contract of llm-1b/model.py (amax pass + one-read quantizer);
+        "emit" = the operand emitters of the reference's trainer (llm-1b/model2.py:430-480): row operands with exact
+        per-row scales, column operands with delayed per-tensor scales, no amax pass, `rs[row] * gs` applied in the
+        GEMM epilogue."""
+        assert mode in ("tensor", "emit")
+        self.mode = mode
         self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
         self.ar_blocks = max(1, ar_blocks)   # transformer blocks per gradient all-reduce
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
@@ -136,6 +144,12 @@ class LinearStack:
         # per-projection SR seeds in device memory: [n_proj, 2] = (seed, seed ^ 0x5bd1e995) (llm-1b/model.py:59,66)
         self.seeds = torch.zeros(self.n_proj, 2, dtype=torch.int32, device=self.device)
         self._lids = torch.arange(self.n_proj, dtype=torch.int64, device=self.device) * 7919
+        # emitter mode: delayed amax of the two column operands of every projection (x, gy), the observed
+        # values of the running microbatch, and the device words the emitters read (seed, Hadamard signs)
+        self.amax_use = torch.full((self.n_proj, 2), 1e9, dtype=torch.float32, device=self.device)
+        self.amax_cur = torch.zeros(self.n_proj, 2, dtype=torch.int32, device=self.device)
+        self.rng = torch.tensor([0, _RHT_SIGNS], dtype=torch.int32, device=self.device)
+        self._calibrated = False
         self.micro_count = 0
         self._bump_seeds()
         self.comm_stream = torch.cuda.Stream(device=self.device)
@@ -150,7 +164,7 @@ class LinearStack:
         torch.nn.init.trunc_normal_(w, std=std, a=-3 * std, b=3 * std, generator=gen)
         p.w = w.bfloat16()
         p.gw = None      # a view of the block's flat gradient buffer, set by the constructor
-        p.q = p.qt = p.am_x = p.y = p.gx = None
+        p.q = p.qt = p.am_x = p.y = p.gx = p.qxt = p.wq = p.cx = None
         return p
 
     # ------------------------------------------------------------------ per-step pieces
@@ -159,7 +173,14 @@ class LinearStack:
         s = (self._lids + self.micro_count * 1000003) & 0xFFFFFFFF
         both = torch.stack([s, s ^ 0x5BD1E995], 1)
         self.seeds.copy_(torch.where(both >= 2 ** 31, both - 2 ** 32, both).to(torch.int32))
+        self.rng[0] = (self.micro_count * 1000003 + 12345) % (2 ** 31)
         self.micro_count += 1
+
+    def roll_amax(self):
+        """Delayed scaling: this microbatch's observed RHT-domain amax (x margin) scales the next one
+        (llm-1b/model2.py:497-499)."""
+        torch.mul(self.amax_cur.view(torch.float32).clamp(min=1e-30), EMIT_MARGIN, out=self.amax_use)
+        self.amax_cur.zero_()
 
     def refresh_weights(self):
         """Quantize every weight once per optimizer step (the small-model/fp4torch.py:71-84 scheme).
@@ -179,7 +200,33 @@ class LinearStack:
             for p in projs:
                 p.gw.zero_()
 
+    def _fwd_block_emit(self, projs, keep=False):
+        T = self.T
+        for p in projs:
+            x = self.x_pool[p.name]
+            if p.wq is None or p.wq.q is not p.q:
+                p.wq = emit.WQ(p.N, p.K)
+                p.wq.q, p.wq.qt = p.q, p.qt
+            rq = emit.row_emit(x, emit.RowQ(T, p.K, self.device), None)
+            p.cx = emit.col_emit(x, emit.ColQ(T, p.K, self.device), self.amax_use[p.lid, 0:1], self.amax_cur[p.lid, 0:1], self.rng)
+            y = emit.mm_row_w(rq, p.wq, scale=True)
+            p.y = y if keep else None
+
+    def _bwd_block_emit(self, projs, keep=False, first=False):
+        T = self.T
+        for p in reversed(projs):
+            gy = self.gy_pool[p.name]
+            use_x, use_g = self.amax_use[p.lid, 0:1], self.amax_use[p.lid, 1:2]
+            rq = emit.row_emit(gy, emit.RowQ(T, p.N, self.device), self.rng, sr=True, salt=p.lid * 8 + 1)
+            cg = emit.col_emit(gy, emit.ColQ(T, p.N, self.device), use_g, self.amax_cur[p.lid, 1:2], self.rng, sr=True,
+                               salt=p.lid * 8 + 2)
+            gx = emit.mm_row_wt(rq, p.wq, scale=True)
+            emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
+            p.gx = gx if keep else None
+
     def _fwd_block(self, projs, keep=False):
+        if self.mode == "emit":
+            return self._fwd_block_emit(projs, keep)
         for p in projs:
             y, p.am_x, p.qxt = linear_fwd(self.x_pool[p.name], p.q, keep_xt=True, signs=_RHT_SIGNS)
             p.y = y if keep else None
@@ -187,22 +234,40 @@ class LinearStack:
     def _bwd_block(self, projs, keep=False, first=False):
         """`first`: the step's first microbatch overwrites dW instead of adding to it, so the
         gradients need no clearing pass."""
+        if self.mode == "emit":
+            return self._bwd_block_emit(projs, keep, first)
         for p in reversed(projs):
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(None, p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
                                gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt)
             p.gx = gx if keep else None
 
+    def calibrate(self):
+        """Emitter mode: two passes over all projections so that the delayed column scales come from observed
+        amax values instead of the initial placeholder."""
+        self.refresh_weights()
+        for _ in range(2):
+            for projs in self.blocks:
+                self._fwd_block(projs)
+            for projs in reversed(self.blocks):
+                self._bwd_block(projs)
+            self.roll_amax()
+        self._calibrated = True
+
     def capture(self):
         """Capture each block's forward and backward into CUDA graphs sharing one memory pool."""
         self.refresh_weights()
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):          # warm-up outside capture
-            for projs in self.blocks:
-                self._fwd_block(projs)
-            for projs in reversed(self.blocks):
-                self._bwd_block(projs)
+        with torch.cuda.stream(s):          # warm-up outside capture (emitter mode: calibrates the delayed scales)
+            for _ in range(2 if self.mode == "emit" else 1):
+                for projs in self.blocks:
+                    self._fwd_block(projs)
+                for projs in reversed(self.blocks):
+                    self._bwd_block(projs)
+                if self.mode == "emit":
+                    self.roll_amax()
+        self._calibrated = True
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         pool = torch.cuda.graph_pool_handle()
@@ -234,7 +299,7 @@ class LinearStack:
 
     def kernels_per_microbatch(self):
         """Kernels of this library launched per microbatch: fwd amax + tile quantizer + gemm;
-        bwd amax + tile quantizer + 2 gemm."""
+        bwd amax + tile quantizer + 2 gemm (emitter mode: two emitters in place of amax + quantizer)."""
         return self.n_proj * (3 + 4)
 
     def microbatch(self, last, do_allreduce, first=False):
@@ -261,12 +326,16 @@ class LinearStack:
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ev)
                     allreduce_sum_([self.ar_after[nblk - 1 - i]], self.group)
+        if self.mode == "emit":
+            self.roll_amax()
         return works
 
     def step(self, n_micro, do_allreduce):
         """One optimizer step's worth of this path: re-quantize weights, clear dW, n_micro
         microbatches (the first overwrites dW, the others add), all-reduce.  Leaves the summed FP32
         gradients in `p.gw`."""
+        if self.mode == "emit" and not self._calibrated:
+            self.calibrate()
         self.refresh_weights()
         for m in range(n_micro):
             self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce, first=(m == 0))

@@ -219,14 +219,18 @@ _SR_HW_MULT = (0x9E3779B1, 0x85EBCA77, 0xC2B2AE3D, 0x27D4EB2F)
 
 def sr_words_hw(seed, blk_idx):
     """Counter-based stream of this library for the hardware-SR mode: one 32-bit word per group of
-    four consecutive elements.  key = hash32(seed ^ blk * 0x9E3779B9); word g = x ^ (x >> 16) with
-    x = key * mult[g] (four odd constants), all mod 2^32.  Returns [..., 4] words."""
+    four consecutive elements.  t = blk * 0x9E3779B9 ^ hash32(seed); t ^= t >> 16; t *= 0x7feb352d;
+    t ^= t >> 15 (mod 2^32); word g = lo ^ hi of the 64-bit product t * mult[g] (four odd constants).
+    Returns [..., 4] words."""
     blk_idx = np.asarray(blk_idx, dtype=np.uint32)
-    key = hash32(np.uint32(seed & 0xFFFFFFFF) ^ (blk_idx * np.uint32(0x9E3779B9)))
+    t = (blk_idx * np.uint32(0x9E3779B9)) ^ hash32(np.uint32(seed & 0xFFFFFFFF))
+    t = t ^ (t >> np.uint32(16))
+    t = t * np.uint32(0x7FEB352D)
+    t = t ^ (t >> np.uint32(15))
     out = np.empty(blk_idx.shape + (4,), dtype=np.uint32)
     for g in range(4):
-        x = key * np.uint32(_SR_HW_MULT[g])
-        out[..., g] = x ^ (x >> np.uint32(16))
+        p = t.astype(np.uint64) * np.uint64(_SR_HW_MULT[g])
+        out[..., g] = (p & np.uint64(0xFFFFFFFF)).astype(np.uint32) ^ (p >> np.uint64(32)).astype(np.uint32)
     return out
 
 
@@ -459,7 +463,10 @@ def emit_rows(x, seed=0, sr=False, salt=0):
     bytes [T, C/16] row-major, rs [T] float32).  Arithmetic per row: inv = 2688/rowmax (0 for a
     zero row), rs = rowmax * (1/2688); per 16 values: sb = e4m3((m*inv)*(1/6)), k = inv/dec(sb)
     (0 when the byte is 0), code = rn(x*k).  SR: lane l = (column/8) % 32 of row r starts an LCG at
-    hash32(seed ^ salt ^ hash32(r*32 + l)) and walks its 8-column chunks in column order."""
+    hash32(seed ^ salt ^ hash32(r*32 + l)) and walks its 8-column chunks in column order.  For C == 11264
+    the reference's launcher (llm-1b/emit.py:62-68) runs `row_emit_11264` = row_reg<4, 11> (llm-1b/emit.cu:228-260)
+    instead: four sequences per lane, sequence s seeded with hash32(seed ^ salt ^ hash32(r*128 + s*32 + l)) and
+    walking the chunks 4 j + s, j = 0..10."""
     x = np.asarray(x, dtype=np.float32)
     T, C = x.shape
     assert C % 256 == 0
@@ -477,11 +484,16 @@ def emit_rows(x, seed=0, sr=False, salt=0):
     codes = np.empty((T, C), dtype=np.uint8)
     rows = np.arange(T, dtype=np.uint32)[:, None]
     lanes = np.arange(32, dtype=np.uint32)[None, :]
-    state = hash32(np.uint32((seed if sr else 0) & 0xFFFFFFFF) ^ np.uint32(salt & 0xFFFFFFFF) ^ hash32(rows * np.uint32(32) + lanes))
+    key = np.uint32((seed if sr else 0) & 0xFFFFFFFF) ^ np.uint32(salt & 0xFFFFFFFF)
+    subs = 4 if (C == 11264 and sr) else 1
+    if subs == 1:
+        states = [hash32(key ^ hash32(rows * np.uint32(32) + lanes))]
+    else:
+        states = [hash32(key ^ hash32(rows * np.uint32(128) + np.uint32(32 * sidx) + lanes)) for sidx in range(4)]
     for j in range(C // 256):                      # chunk j of lane l covers columns 256 j + 8 l .. + 8
         v8 = x[:, 256 * j:256 * (j + 1)].reshape(T, 32, 8)
         kk = np.repeat(k[:, 16 * j:16 * (j + 1)], 2, axis=1)          # lanes 2b, 2b+1 share block b
-        c8, state = _emit_pack8(v8, kk, sr, state)
+        c8, states[j % subs] = _emit_pack8(v8, kk, sr, states[j % subs])
         codes[:, 256 * j:256 * (j + 1)] = c8.reshape(T, 256)
     return pack_codes(codes), sbyte, rs
 
@@ -562,3 +574,24 @@ def linear_fwd_bwd(x, w, gy, signs, seed=0, sr_mode=SR_DITHER_NVQ):
     qxt = quant_cols_rht(x, signs)
     gw = gemm_dequant(qgt[0], qgt[1], qgt[2], qxt[0], qxt[1], qxt[2])
     return y, gx, gw
+
+
+# ----------------------------------------------------------------------------- per-row-scale torch emulation
+def qref_rows(x):
+    """The reference's torch emulation of row quantization with an exact per-row scale, `q_rows` of
+    small-model/qref.py:15-31 (whole-row chunk, no column permutation), in FP32 numpy: per row gs = rowmax/2688
+    (clamp 1e-30), xb = x/gs, bs = e4m3(max16|xb| / 6), q = fp4_round(xb / max(bs, 1e-30)).  It is the DIVISION form
+    of what the emitter kernels (llm-1b/emit.cu:81-91) compute with multiplications by reciprocals, so the two
+    agree except where a last-bit difference crosses a rounding boundary: a tolerance cross-check, not bit-equality.
+    Returns (codes [T, C] uint8 with the sign in bit 3, scale bytes [T, C/16], gs [T] float32)."""
+    x = np.asarray(x, dtype=np.float32)
+    T, C = x.shape
+    gs = (np.abs(x).max(axis=1) / np.float32(FP4_E4M3)).astype(np.float32)
+    xb = (x / np.maximum(gs, TINY)[:, None]).astype(np.float32).reshape(T, C // 16, 16)
+    sbyte = e4m3_encode((np.abs(xb).max(axis=2) / FP4_MAX).astype(np.float32))
+    bs = e4m3_decode(sbyte)
+    y = (xb / np.maximum(bs, TINY)[..., None]).astype(np.float32)
+    codes = e2m1_rn_code(y)
+    zero = np.broadcast_to((sbyte == 0)[..., None], codes.shape)
+    codes = np.where(zero, np.signbit(xb).astype(np.uint8) << 3, codes).astype(np.uint8)
+    return codes.reshape(T, C), sbyte, gs

@@ -83,6 +83,13 @@ def main():
     x = inputs_1d()["student_t"]
     out["rows_gamax_dq"] = model_ref.nvfp4_1d(x, gamax=x.float().abs().max() * 4).numpy()
 
+    # ---- 1x16 quantization with an exact PER-ROW scale (the contract of the operand emitters, llm-1b/emit.cu, and of
+    # `q_rows` in small-model/qref.py:15-31, which is this formula row by row): each row is its own tensor
+    xr = torch.cat([inputs_1d()["normal_outliers"][:24], inputs_1d()["student_t"][:24, :192].repeat(1, 2)[:, :256] * 1e3])
+    xr[5] = 0
+    out["rowscale_x"] = bf16_bits(xr)
+    out["rowscale_dq"] = torch.cat([model_ref.nvfp4_1d(xr[r:r + 1]) for r in range(xr.shape[0])]).numpy()
+
     # ---- 16x16 weight quantization (bf16 weights as in llm-1b, fp32 as in small-model)
     g = torch.Generator().manual_seed(2)
     w = (torch.randn(128, 192, generator=g) * 0.02).bfloat16()

@@ -148,3 +148,105 @@ def test_row_emit_rejects_bad_arguments(emit):
     assert lib.nvfp4_emit_rows(*a(64, 256, 0, None)) == -2         # T % 128
     assert lib.nvfp4_emit_rows(*a(128, 256, 1, None)) == -1        # SR needs the device seed
     assert lib.nvfp4_emit_rows(*a(0, 256, 0, None)) == 0
+
+
+# ---------------------------------------------------------------------------------------- pins and the fused epilogue
+def test_row_emit_against_the_reference_torch_emulation(emit):
+    """Cross-check against `q_rows` of small-model/qref.py:15-31 (restated as `O.qref_rows`, itself bit-exact against
+    the reference's `model_ref.nvfp4_1d` row by row): the kernel multiplies by reciprocals where the emulation divides,
+    so codes / scale bytes may differ where a last-bit difference crosses a rounding boundary.  Stated bound: at most
+    2e-3 of the codes and of the scale bytes, never by more than one step; dequantized tensors within 1e-2."""
+    for seed, (T, C) in enumerate([(256, 2048), (128, 5632), (128, 11264)]):
+        x = make_x(seed, T, C) if seed != 1 else make_dy(seed, T, C)
+        q = emit.row_emit(to_dev(x), emit.RowQ(T, C), None)
+        qc, qs, gs = O.qref_rows(x)
+        cu = O.unpack_codes(u8(q.d))
+        sb = O.unswizzle_scales(u8(q.s), T, C // 16)
+        diff = cu != qc
+        assert diff.mean() <= 2e-3 and (sb != qs).mean() <= 2e-3, (diff.mean(), (sb != qs).mean())
+        assert np.abs((cu & 7).astype(int) - (qc & 7).astype(int))[diff].max(initial=0) <= 1
+        assert np.abs(sb.astype(int) - qs.astype(int)).max() <= 1
+        ref = (O.E2M1_TABLE[qc] * np.repeat(O.e4m3_decode(qs), 16, axis=1)) * gs[:, None]
+        assert rel_fro(emit.dequant(q.d, q.s, q.rs).cpu().numpy(), ref) < 1e-2
+
+
+def test_reference_emit_checks_with_stated_bounds(emit):
+    """The quantities llm-1b/test_emit.py:31-46 prints, on its shapes scaled down 8x in tokens, each with a bound:
+    row_emit RN error < 0.12 and SR mean(32) error < 0.4 x RN; wgrad from two column operands with a calibrated
+    delayed amax (x2 margin) < 0.2 of exact; forward and dgrad GEMMs with per-row scales < 0.15 of exact."""
+    T, D, F = 1024, 2048, 5632
+    g0 = torch.Generator(device="cuda").manual_seed(0)
+    rng = torch.tensor([12345, 0b1011001110001101], dtype=torch.int32, device="cuda")
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    g = torch.randn(T, D, generator=g0, device="cuda").bfloat16()
+    qg = emit.RowQ(T, D)
+    acc = torch.zeros(T, D, device="cuda")
+    for i in range(32):
+        rng[0] = i * 7919 + 1
+        emit.row_emit(g, qg, rng, sr=True)
+        acc += emit.dequant(qg.d, qg.s, qg.rs)
+    emit.row_emit(g, qg, rng, sr=False)
+    e_rn, e_sr = rel(emit.dequant(qg.d, qg.s, qg.rs), g), rel(acc / 32, g)
+    assert e_rn < 0.12 and e_sr < 0.4 * e_rn, (e_rn, e_sr)
+    # col_emit + wgrad GEMM, delayed amax calibrated by a first pass
+    gg = (torch.randn(T, F, generator=g0, device="cuda") * 1e-3).bfloat16()
+    aa = torch.randn(T, D, generator=g0, device="cuda").bfloat16()
+    cu = torch.ones(2, device="cuda") * 1e9
+    cc = torch.zeros(2, dtype=torch.int32, device="cuda")
+    qc1, qc2 = emit.ColQ(T, F), emit.ColQ(T, D)
+    emit.col_emit(gg, qc1, cu[0:1], cc[0:1], rng, sr=True)
+    emit.col_emit(aa, qc2, cu[1:2], cc[1:2], rng)
+    cu.copy_(cc.view(torch.float32) * 2.0)
+    cc.zero_()
+    emit.col_emit(gg, qc1, cu[0:1], cc[0:1], rng, sr=True, salt=3)
+    emit.col_emit(aa, qc2, cu[1:2], cc[1:2], rng)
+    dW = emit.mm_col(qc1, qc2).float() * (cu[0] / 2688) * (cu[1] / 2688)
+    ref = gg.float().t() @ aa.float()
+    assert rel(dW, ref) < 0.2, rel(dW, ref)
+    # the same product with the two scales applied in the epilogue, accumulated in place
+    dW2 = torch.zeros(F, D, device="cuda")
+    emit.mm_col(qc1, qc2, scale=True, amax_a=cu[0:1], amax_b=cu[1:2], out=dW2, accumulate=True)
+    assert rel(dW2, dW) < 1e-6
+    # weights: forward and dgrad with per-row scales
+    W = (torch.randn(F, D, generator=g0, device="cuda") * 0.02).bfloat16()
+    wq = emit.WQ(F, D).refresh(W)
+    x = torch.randn(T, D, generator=g0, device="cuda").bfloat16()
+    hq = emit.row_emit(x, emit.RowQ(T, D), None)
+    yraw = emit.mm_row_w(hq, wq)
+    yv = yraw.float() * hq.rs[:, None] * wq.gs
+    assert rel(yv, x.float() @ W.float().t()) < 0.15
+    dq = emit.row_emit(gg, emit.RowQ(T, F), rng, sr=True)
+    dx = emit.mm_row_wt(dq, wq).float() * dq.rs[:, None] * wq.gs
+    assert rel(dx, gg.float() @ W.float()) < 0.15
+    # fused row-scale epilogue == the reference's separate scale_rows pass up to one bf16 rounding of the raw product
+    y_fused = emit.mm_row_w(hq, wq, scale=True)
+    assert y_fused.dtype == torch.bfloat16 and rel(y_fused, yv) < 3e-3
+    assert rel(y_fused, emit.scale_rows(yraw, hq.rs, wq.gs)) < 5e-3
+    dx_fused = emit.mm_row_wt(dq, wq, scale=True)
+    assert rel(dx_fused, dx) < 3e-3
+
+
+@pytest.mark.parametrize("tile", [0, 128, 256, 512, 448, 384])
+def test_gemm_row_scale_epilogue(emit, tile):
+    """alpha[row] = rs[row] * gs in the epilogue of every GEMM variant (one-CTA and CTA-pair kernels, bf16 and FP32,
+    accumulate): against the FP64 product of the dequantized operands with the scales applied per row."""
+    from nvfp4_training_b200 import _lib as L
+    M, N, K = 512, 768, 1024
+    x, w = make_x(5, M, K), make_w(6, N, K)
+    q = emit.row_emit(to_dev(x), emit.RowQ(M, K), None)
+    wq = emit.WQ(N, K).refresh(to_dev(w))
+    codes, sbyte, rs = O.emit_rows(x)
+    wc, ws, _, _, wgs = O.quant_w2d(w)
+    want = O.gemm_unit(codes, sbyte, wc, ws) * rs.astype(np.float64)[:, None] * float(wgs)
+    L.load().nvfp4_gemm_force_tile_n(tile)
+    try:
+        y = emit.mm_row_w(q, wq, scale=True).float().cpu().numpy()
+        assert rel_fro(y, want) <= 4e-3
+        out = torch.full((M, N), 1.0, device="cuda")
+        emit._gemm(q.d, q.s, wq.d, wq.s, out, L.ALPHA_ROW, q.rs, wq.gs, accumulate=True)
+        got = out.cpu().numpy().astype(np.float64)
+        assert rel_fro(got, want + 1.0) <= 1e-5
+        assert (np.abs(got - want - 1.0) <= 1e-4 * np.abs(want) + 1e-5).all()
+    finally:
+        L.load().nvfp4_gemm_force_tile_n(0)
+    L.check_status()

@@ -94,3 +94,50 @@ def test_stack_separate_weight_and_input_seeds():
     for pa, pb in zip(a.blocks[0], b.blocks[0]):
         assert torch.equal(pa.w, pb.w)
     assert not torch.equal(a.x_pool["qkv"], b.x_pool["qkv"])
+
+
+def test_stack_emitter_mode_graphs_equal_eager_and_oracle():
+    """The emitter mode of the stack (row operands with per-row scales, column operands with delayed scales,
+    scales applied in the GEMM epilogues): graph replay equals eager bit for bit, the delayed amax settles at
+    margin x observed, and dW of one projection equals the oracle's restatement of the emitters (FP64 product of the
+    dequantized operands) within 1e-4."""
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.linear import _RHT_SIGNS
+    from nvfp4_training_b200.stack import EMIT_MARGIN, LinearStack, StackConfig
+    cfg = StackConfig(vocab=512, d=256, layers=2, heads=2, kv_heads=1, ff=512, lm_head=True)
+    a = LinearStack(cfg, 256, torch.device("cuda"), seed=3, use_graphs=True, mode="emit")
+    a.capture()
+    b = LinearStack(cfg, 256, torch.device("cuda"), seed=3, use_graphs=False, mode="emit")
+    b.calibrate()
+    assert torch.equal(a.amax_use, b.amax_use)
+    for st in (a, b):
+        st.step(2, do_allreduce=False)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for pa, pb in zip([p for blk in a.blocks for p in blk], [p for blk in b.blocks for p in blk]):
+        assert torch.equal(pa.gw, pb.gw), pa.name
+        assert pa.gw.abs().max().item() > 0
+    # oracle for one projection and ONE microbatch (eager, first = overwrite)
+    p = b.blocks[0][2]
+    x, gy = f32(b.x_pool[p.name]), f32(b.gy_pool[p.name])
+    use = b.amax_use.cpu().numpy()
+    obs_x = np.float32(np.abs(O.rht16_cols(x, _RHT_SIGNS)).max())
+    assert use[p.lid, 0] == np.float32(obs_x * np.float32(EMIT_MARGIN))
+    seed = int(b.rng[0].item())
+    b._fwd_block(b.blocks[0], keep=True)
+    b._bwd_block(b.blocks[0], keep=True, first=True)
+    torch.cuda.synchronize()
+    cx, sx, _ = O.emit_cols(x, _RHT_SIGNS, use[p.lid, 0])
+    cg, sg, _ = O.emit_cols(gy, _RHT_SIGNS, use[p.lid, 1], seed=seed, sr=True, salt=p.lid * 8 + 2)
+    want = O.gemm_unit(cg, sg, cx, sx) * (float(use[p.lid, 1]) / 2688.0) * (float(use[p.lid, 0]) / 2688.0)
+    assert rel_fro(f32(p.gw), want) <= 1e-4
+    # forward y and dgrad of the same projection: per-row scales in the epilogue
+    w = f32(p.w)
+    rc, rsb, rs = O.emit_rows(x)
+    wc, ws, wct, wst, wgs = O.quant_w2d(w)
+    y = O.gemm_unit(rc, rsb, wc, ws) * rs.astype(np.float64)[:, None] * float(wgs)
+    assert rel_fro(f32(p.y), y) <= 4e-3
+    gc, gsb, grs = O.emit_rows(gy, seed=seed, sr=True, salt=p.lid * 8 + 1)
+    gx = O.gemm_unit(gc, gsb, wct, wst) * grs.astype(np.float64)[:, None] * float(wgs)
+    assert rel_fro(f32(p.gx), gx) <= 4e-3
+    _lib.check_status()

@@ -1,5 +1,9 @@
-"""CPU checks of the oracle's restatement of the operand emitters (llm-1b/emit.cu): internal
-consistency only -- the reference holds no CPU implementation or fixture for these kernels."""
+"""CPU checks of the oracle's restatement of the operand emitters (llm-1b/emit.cu).  The reference holds no CPU
+implementation of these kernels; what pins them here is (a) the reference's torch emulation of per-row-scale
+quantization, `q_rows` of small-model/qref.py:15-31, restated as `qref_rows` and itself checked bit for bit against a
+fixture made with the reference's `model_ref.nvfp4_1d` row by row, and (b) a stated cross-check between the two forms:
+the kernels multiply by reciprocals where the emulation divides, so codes and scale bytes may differ where a last-bit
+difference crosses a rounding boundary -- at most 2e-3 of them, never by more than one code step / one scale step."""
 import numpy as np
 
 from oracle import nvfp4_oracle as O
@@ -51,3 +55,51 @@ def test_lcg_and_dither_primitives():
     v = np.array([0.3, 0.74, 1.4, 2.9, 5.9, -0.3, 7.5], dtype=np.float32)
     assert np.array_equal(O.sr2(v, np.uint32(0)), np.array([0.0, 0.5, 1.0, 2.0, 4.0, -0.0, 6.0], dtype=np.float32))
     assert np.array_equal(O.sr2(v, np.uint32(0x3FF800)), np.array([0.5, 1.0, 1.5, 3.0, 6.0, -0.5, 6.0], dtype=np.float32))
+
+
+def test_qref_rows_equals_the_reference_fake_quant_row_by_row(golden):
+    """`qref_rows` (restatement of small-model/qref.py:15-31) dequantizes to exactly what the reference's own
+    `model_ref.nvfp4_1d` gives when each row is quantized as a tensor of its own (fixture `rowscale_*`)."""
+    x = O.bf16_bits_to_f32(golden["rowscale_x"])
+    codes, sbyte, gs = O.qref_rows(x)
+    deq = (O.E2M1_TABLE[codes] * np.repeat(O.e4m3_decode(sbyte), 16, axis=1)).astype(np.float32) * gs[:, None]
+    assert np.array_equal(deq.astype(np.float32), golden["rowscale_dq"])
+
+
+def test_emit_rows_against_the_division_form_within_the_stated_mismatch():
+    for seed, (T, C) in enumerate([(256, 2048), (256, 3072), (128, 5632)]):
+        x = make_x(seed, T, C) if seed != 1 else make_dy(seed, T, C)
+        codes, sbyte, rs = O.emit_rows(x)
+        qc, qs, gs = O.qref_rows(x)
+        cu = O.unpack_codes(codes)
+        diff = cu != qc
+        assert diff.mean() <= 2e-3 and (sbyte != qs).mean() <= 2e-3
+        assert np.abs((cu & 7).astype(int) - (qc & 7).astype(int))[diff].max(initial=0) <= 1
+        assert np.abs(sbyte.astype(int) - qs.astype(int)).max() <= 1
+        assert np.max(np.abs(gs - rs) / np.maximum(gs, 1e-30)) <= 2.0 ** -23         # am * (1/2688) vs am / 2688
+        assert rel_fro(O.emit_rows_dequant(codes, sbyte, rs), (O.E2M1_TABLE[qc] * np.repeat(O.e4m3_decode(qs), 16, axis=1)) * gs[:, None]) < 1e-2
+
+
+def test_emit_rows_11264_columns_uses_the_four_sequence_stream():
+    """For C == 11264 the reference's launcher runs `row_emit_11264` (row_reg<4, 11>, llm-1b/emit.cu:228-260): checked
+    against a scalar walk of that kernel's loop for one row -- sequence s of lane l starts at
+    hash32(seed ^ salt ^ hash32(r*128 + s*32 + l)) and handles the chunks 4 j + s."""
+    rng = np.random.default_rng(3)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits((rng.standard_normal((2, 11264)) * 1e-3).astype(np.float32)))
+    seed, salt, r = 77, 5, 1
+    codes, sbyte, rs = O.emit_rows(x, seed=seed, sr=True, salt=salt)
+    am = np.abs(x[r]).max().astype(np.float32)
+    inv = np.float32(np.float32(2688.0) / am)
+    got = O.unpack_codes(codes)[r]
+    for sub in (0, 3):
+        for lane in (0, 17):
+            st = O.hash32(np.uint32(seed) ^ np.uint32(salt) ^ O.hash32(np.uint32(r * 128 + sub * 32 + lane)))
+            for j in range(11):
+                col = (j * 4 + sub) * 256 + lane * 8
+                blk = x[r, col & ~15:(col & ~15) + 16]
+                m = np.abs(blk).max().astype(np.float32)
+                sb = O.e4m3_encode(np.float32(np.float32(m * inv) * np.float32(np.float32(1) / np.float32(6))))
+                sd = O.e4m3_decode(sb)
+                k = np.float32(inv / sd) if sd > 0 else np.float32(0)
+                c8, st = O._emit_pack8(x[r, col:col + 8][None, :], np.array([k], dtype=np.float32), True, st)
+                assert np.array_equal(np.asarray(c8).reshape(-1), got[col:col + 8]), (sub, lane, j)
