@@ -126,7 +126,12 @@ int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void* codes_r, 
                      const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
 
 /* Tuning / test hook: 0 = nvfp4_quant_tile picks the tensor-core-fed kernel where it applies (default),
- * 1 = always the scalar tile kernel.  Process-wide.  No reference counterpart. */
+ * 1 = always the scalar tile kernel, 2 = the tensor-core-fed kernel with the 16-point Hadamard transform of the
+ * transposed operand computed by the MMA itself (B operand = rows of H diag(signs)) instead of FP32 butterflies, as
+ * the reference's fused backward does on mma.sync (small-model/fused_bwd.cu:33-64 `emit_wg`, small-model/wg16.cu:41-103).
+ * Mode 2 is not bit-exact: the tensor core sums a block's 16 signed values in its own order; results equal the
+ * butterflies' whenever every partial sum is representable in FP32 and may differ in the last bit otherwise.
+ * Process-wide. */
 int nvfp4_quant_tile_set_path(int path);
 
 /* Reads (synchronously) the status word of nvfp4_quant_tile launches on the current device:

@@ -155,7 +155,9 @@ __device__ __forceinline__ u64 f2_ndiv(u64 a, u64 b, u64 nrb) {
 }
 
 // t / bs for a block scale bs (an E4M3 value: at most 4 significant bits), from the negated reciprocal split in two
-// words, nrh = -RN(1/bs) and nrl = -RN(1/bs - RN(1/bs)):  RN(t*nrh + RN(t*nrl)).  The quotient feeds a
+// words, nrh = -RD(1/bs) (rounded DOWN, so that the remainder 1/bs - RD(1/bs) is never negative and both words
+// have the same sign: a zero numerator then keeps its sign through the sum) and nrl = -RN(1/bs - RD(1/bs)):
+// RN(t*nrh + RN(t*nrl)).  The quotient feeds a
 // round-to-E2M1 whose result only depends on how t/bs compares with the seven rounding boundaries b (0.25 .. 5).
 // RN(t/bs) < b, = b, > b exactly when t < c, = c, > c for c = b*bs (exactly representable), and this form --
 // accurate to 2^-46, against 0.03 ulp between the nearest t/bs and a rounding midpoint next to b -- maps
@@ -174,7 +176,7 @@ struct TensorScale {
 
 constexpr int kLutFloats = 256;
 
-// Fill the per-CTA table: for round to nearest  lut[sb] = {-RN(1/bs), -RN(1/bs - RN(1/bs))} (see f2_div_bs),  for stochastic rounding
+// Fill the per-CTA table: for round to nearest  lut[sb] = {-RD(1/bs), -RN(1/bs - RD(1/bs))} (see f2_div_bs),  for stochastic rounding
 // lut[sb] = {inv_gs/bs, bs}  (the exact multiplier of the reference kernels).  `pre` is a power of
 // two that the caller's values still have to be multiplied by (0.25 after the Hadamard butterflies,
 // else 1): it is folded into gs, which changes no quotient.  Ends with a block barrier.
@@ -196,8 +198,8 @@ __device__ __forceinline__ TensorScale make_tensor_scale(float amax, float k, fl
     float second = (ROUNDING == NVFP4_ROUND_NEAREST) ? -0.f : bsf;
     if (threadIdx.x >= 1 && threadIdx.x <= 126) {
       if (ROUNDING == NVFP4_ROUND_NEAREST) {
-        const float rh = __frcp_rn(bsf);
-        const float res = __fmaf_rn(-rh, bsf, 1.f);        // exact: 1 - rh*bs has few significant bits
+        const float rh = __frcp_rd(bsf);
+        const float res = __fmaf_rn(-rh, bsf, 1.f);        // exact and >= +0: 1 - rh*bs has few significant bits
         m = -rh;
         second = -__fmul_rn(res, rh);                       // -(1/bs - rh) to 2^-24 of itself
       } else {

@@ -23,6 +23,12 @@
 // dequantized value is the same.  Inf/NaN inputs poison their 16-value group (0 * Inf), as they
 // poison the tensor's amax in every implementation.
 //
+// Optional mode (nvfp4_quant_tile_set_path(2)): the 16-point Hadamard transform itself in the MMA -- P then holds
+// the rows of H diag(s) instead of a signed permutation and the consumers skip the butterflies.  The tensor core
+// sums the 16 signed bf16 values of a block in FP32 in its own order, so the result equals the butterflies' whenever
+// the exact sum is representable (all values of a block within 2^12 of its largest: every partial sum then fits 24
+// bits) and can differ in the last bit otherwise: not the bit-exact default.
+//
 // Two CTAs per SM, each with nine warps (one loads tiles and issues the MMAs, eight quantize) and 256
 // tensor-memory columns used as two buffers, so that MMAs into one buffer run while the consumers work on
 // the other; the consumers' tensor-memory loads are software-pipelined.  Every mbarrier wait is bounded: on
@@ -54,6 +60,7 @@ struct TcParams {
   u32 signs;
   u32 seed_r, seed_c;
   const u32* seed_r_dev; const u32* seed_c_dev;
+  int tc_rht;       // 1: the 16-point Hadamard transform itself runs in the MMA (B = signed Hadamard rows), see below
 };
 
 // ---- tcgen05 wrappers (cta_group::1)
@@ -149,7 +156,7 @@ struct TcWalk {
   __device__ __forceinline__ void next() { mt += dq; ct += dr; if (ct >= nct) { ct -= nct; mt++; } }
 };
 
-template <int ROUNDING, bool ROWS, bool COLS>
+template <int ROUNDING, bool ROWS, bool COLS, bool TCRHT>
 __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) float lut_r[kLutFloats];
@@ -179,9 +186,21 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     // P1 row 2k and P2 row 2k+1 hold s_k at K index k: slot 2k = token k of the first 16-token block, slot 2k+1 =
     // token k of the second; bit k of `signs` negates token k
     const u32 n = threadIdx.x - 32u, k = n >> 1;
-    const unsigned short v = ((p.signs >> k) & 1u) ? (unsigned short)0xBF80 : (unsigned short)0x3F80;
-    const u32 off = n * 128u + ((((k >> 3) ^ (n & 7u)) << 4) | ((k & 7u) << 1));
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(((n & 1u) ? p2_s : p1_s) + off), "h"(v) : "memory");
+    const u32 base = (n & 1u) ? p2_s : p1_s;
+    if (!TCRHT) {
+      const unsigned short v = ((p.signs >> k) & 1u) ? (unsigned short)0xBF80 : (unsigned short)0x3F80;
+      const u32 off = n * 128u + ((((k >> 3) ^ (n & 7u)) << 4) | ((k & 7u) << 1));
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(base + off), "h"(v) : "memory");
+    } else {
+      // Hadamard in the MMA: row 2k (+1) holds row k of H diag(s), H[k][i] = (-1)^popcount(k & i) (Sylvester order,
+      // the order the butterflies of strides 1, 2, 4, 8 produce); slot 2k + j = transformed value k of block j
+#pragma unroll
+      for (u32 i = 0; i < 16; i++) {
+        const u32 neg = (__popc(k & i) ^ (p.signs >> i)) & 1u;
+        const u32 off = n * 128u + ((((i >> 3) ^ (n & 7u)) << 4) | ((i & 7u) << 1));
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(base + off), "h"(neg ? (unsigned short)0xBF80 : (unsigned short)0x3F80) : "memory");
+      }
+    }
   }
   if (threadIdx.x == 0) {
     abort_word = 0;
@@ -288,8 +307,9 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     }
   } else {
     // ------------------------------------------------------------------ consumers (warps 1..8)
-    // The tensor-memory loads are software-pipelined: while a chunk (a 1x16 block of the row operand, or two
-    // 16-token blocks of the transposed one) is being quantized, the load of the next chunk is in flight.
+    // The tensor-memory loads are software-pipelined, also across tiles: while a chunk (a 1x16 block of the row
+    // operand, or two 16-token blocks of the transposed one) is being quantized, the load of the next chunk is in
+    // flight, and the first chunk of the next tile is requested before the last chunk of this one is quantized.
     const int quad = warp & 3;                      // tensor-memory lanes 32 * quad .. + 31 (fixed by the warp index)
     const int half = (warp - 1) >> 2;               // columns 64 * half .. + 63 of a buffer
     u32 seed_r = p.seed_r, seed_c = p.seed_c;
@@ -300,97 +320,129 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     const int nblk = p.C >> 4;                      // 16-column blocks per row
     const int nmb = p.M >> 4;                       // 16-token blocks per column
     const u32 t_lane = tmem_base + ((u32)(quad * 32) << 16) + (u32)(64 * half);
+    // per-thread output positions of tile (0, 0); a tile adds a multiple of its coordinates
+    const long long tok0 = quad * 32 + lane, col0 = quad * 32 + lane;
+    const long long row_code_stride = (long long)kQTok * (p.C >> 1), col_code_stride = (long long)kQCol * nmb * 8;
+    const long long row_sc0 = p.linear ? tok0 * nblk + half * 4 : (long long)half * 512 + lane * 16 + quad * 4;
+    const long long col_sc0 = p.linear ? col0 * nmb + half * 4 : (long long)half * 512 + lane * 16 + quad * 4;
+
+    bool alive = true;
+    // wait for buffer `buf` to be full; false (for the whole warp) when the CTA is aborting
+    auto wait_full = [&](u32 buf, u32 par) {
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(tfull + 8 * buf, par, abort_flag))) {
+        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
+        alive = false;
+      } else {
+        q_fence_after();
+      }
+      return alive;
+    };
+    // a buffer has been read completely: the next MMAs into it may start
+    auto release = [&](u32 buf) {
+      q_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty + 8 * buf);
+    };
+
+    TcWalk tw(p.M, p.C);
     u32 n = 0;
-    for (TcWalk tw(p.M, p.C); tw.valid(); tw.next(), n++) {
+    u32 first16[16], first32[32];                   // the first chunk of the current tile (loaded one tile ahead)
+    if (tw.valid() && wait_full(0u, 0u)) {
+      if (ROWS) q_ld16(t_lane, first16); else q_ld32(t_lane, first32);
+    }
+    for (; alive && tw.valid(); n++) {
       const int mt = tw.mt, ct = tw.ct;
       const u32 buf0 = BOTH ? 0u : (n & 1u), par = BOTH ? (n & 1u) : ((n >> 1) & 1u);
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(tfull + 8 * buf0, par, abort_flag))) {
-        if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
-        break;
-      }
-      q_fence_after();
+      tw.next();
+      const bool more = tw.valid();
+      const u32 nbuf = BOTH ? 0u : ((n + 1u) & 1u), npar = BOTH ? ((n + 1u) & 1u) : (((n + 1u) >> 1) & 1u);
 
-      // lane = token of the row operand / column of the transposed operand
-      const long long tok = (long long)mt * kQTok + quad * 32 + lane;
-      const long long col = (long long)ct * kQCol + quad * 32 + lane;
-      const int blk0 = ct * (kQCol / 16) + half * 4;     // first of this warp's four 1x16 blocks of a row
-      const int mb0 = mt * (kQTok / 16) + half * 4;      // first of this warp's four 16-token blocks of a column
+      const long long tok = (long long)mt * kQTok + tok0;      // lane = token of the row operand
+      const long long col = (long long)ct * kQCol + col0;      // lane = column of the transposed operand
+      const int blk0 = ct * (kQCol / 16) + half * 4;           // first of this warp's four 1x16 blocks of a row
+      const int mb0 = mt * (kQTok / 16) + half * 4;            // first of this warp's four 16-token blocks of a column
       uint2 orow[4], ocol[4];
       u32 sb_row = 0u, sb_col = 0u;
-      u32 ra[16], rb[16], rc[32];
 
       auto row_block = [&](const u32 (&r)[16], int j) {
         u64 P[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
         const u32 sb = block_scale_byte(absmax16(P), ts_r);
-        const long long b = tok * nblk + blk0 + j;
-        orow[j] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, (u32)b, (u32)b * 16u);
+        const u32 b = (u32)(tok * nblk + blk0 + j);
+        orow[j] = quant_block16<ROUNDING>(P, sb, ts_r, seed_r, b, b * 16u);
         sb_row |= sb << (8 * j);
       };
       auto col_pair = [&](const u32 (&r)[32], int pp) {
         u64 P[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) P[i] = q_pack64(r[2 * i], r[2 * i + 1]);
+        if (!TCRHT) {
 #pragma unroll
-        for (int h = 1; h < 16; h <<= 1)
+          for (int h = 1; h < 16; h <<= 1)
 #pragma unroll
-          for (int i = 0; i < 16; i++)
-            if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
+            for (int i = 0; i < 16; i++)
+              if (!(i & h)) { const u64 a = P[i], b = P[i + h]; P[i] = f2_add(a, b); P[i + h] = f2_sub(a, b); }
+        }
         const u32 b0 = (u32)(col * nmb + mb0 + 2 * pp), b1 = b0 + 1u;
         u32 sb0, sb1;
         quant_block16x2<ROUNDING>(P, ts_c, seed_c, b0, b1, block_key<ROUNDING>(seed_c, b0), block_key<ROUNDING>(seed_c, b1),
                                   ocol[2 * pp], ocol[2 * pp + 1], sb0, sb1);
         sb_col |= (sb0 | (sb1 << 8)) << (16 * pp);
       };
-      // a buffer has been read completely: the next MMAs into it may start
-      auto release = [&](u32 buf) {
-        q_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty + 8 * buf);
+      auto store_rows = [&]() {
+        unsigned char* dst = p.codes_r + (long long)mt * row_code_stride + tok0 * (p.C >> 1) + ct * (kQCol / 2) + half * 32;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(orow[0].x, orow[0].y, orow[1].x, orow[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(orow[2].x, orow[2].y, orow[3].x, orow[3].y);
+        // the four scale bytes are neighbours in both layouts
+        const long long so = p.linear ? (long long)mt * kQTok * nblk + ct * (kQCol / 16) + row_sc0
+                                      : ((long long)mt * (nblk >> 2) + ct * 2) * 512 + row_sc0;
+        *reinterpret_cast<u32*>(p.scales_r + so) = sb_row;
+      };
+      auto store_cols = [&]() {
+        unsigned char* dst = p.codes_c + (long long)ct * col_code_stride + (col0 * nmb + mb0) * 8;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(ocol[0].x, ocol[0].y, ocol[1].x, ocol[1].y);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(ocol[2].x, ocol[2].y, ocol[3].x, ocol[3].y);
+        const long long so = p.linear ? (long long)ct * kQCol * nmb + mt * (kQTok / 16) + col_sc0
+                                      : ((long long)ct * (nmb >> 2) + mt * 2) * 512 + col_sc0;
+        *reinterpret_cast<u32*>(p.scales_c + so) = sb_col;
       };
 
       if (ROWS) {
         const u32 t = t_lane + 128u * buf0;
-        q_ld16(t, ra);      q_wait_ld16(ra);
-        q_ld16(t + 16, rb); row_block(ra, 0);  q_wait_ld16(rb);
-        q_ld16(t + 32, ra); row_block(rb, 1);  q_wait_ld16(ra);
-        q_ld16(t + 48, rb); row_block(ra, 2);  q_wait_ld16(rb);
+        u32 r1[16], r2[16], r3[16];
+        q_wait_ld16(first16);
+        q_ld16(t + 16, r1); row_block(first16, 0); q_wait_ld16(r1);
+        q_ld16(t + 32, r2); row_block(r1, 1);      q_wait_ld16(r2);
+        q_ld16(t + 48, r3); row_block(r2, 2);      q_wait_ld16(r3);
         release(buf0);
         if (BOTH) {
           // the transposed half of the same tile: start its first load before the last row block is quantized
-          const bool ok2 = mbar_wait_parked(tfull + 8, par, abort_flag);
-          if (!__all_sync(0xffffffffu, ok2)) {
-            if (lane == 0) atomicCAS(&g_quant_tc_status, 0, 2);
-            break;
-          }
-          q_fence_after();
-          q_ld32(t_lane + 128u, rc);
+          if (!wait_full(1u, par)) break;
+          q_ld32(t_lane + 128u, first32);
+        } else if (more) {
+          if (!wait_full(nbuf, npar)) break;
+          q_ld16(t_lane + 128u * nbuf, first16);
         }
-        row_block(rb, 3);
-        unsigned char* dst = p.codes_r + tok * (p.C >> 1) + ct * (kQCol / 2) + half * 32;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(orow[0].x, orow[0].y, orow[1].x, orow[1].y);
-        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(orow[2].x, orow[2].y, orow[3].x, orow[3].y);
-        // the four scale bytes are neighbours in both layouts
-        const long long so = p.linear ? tok * nblk + blk0
-                                      : ((long long)mt * (nblk >> 2) + ct * 2 + half) * 512 + lane * 16 + quad * 4;
-        *reinterpret_cast<u32*>(p.scales_r + so) = sb_row;
+        row_block(r3, 3);
+        store_rows();
       }
       if (COLS) {
         const u32 cbuf = BOTH ? 1u : buf0;
         const u32 t = t_lane + 128u * cbuf;
-        if (!BOTH) q_ld32(t, rc);
-        q_wait_ld32(rc);
-        col_pair(rc, 0);
-        q_ld32(t + 32, rc); q_wait_ld32(rc);
+        u32 c1[32];
+        q_wait_ld32(first32);
+        q_ld32(t + 32, c1);
+        col_pair(first32, 0);
+        q_wait_ld32(c1);
         release(cbuf);
-        col_pair(rc, 1);
-        unsigned char* dst = p.codes_c + (col * nmb + mb0) * 8;
-        *reinterpret_cast<uint4*>(dst) = make_uint4(ocol[0].x, ocol[0].y, ocol[1].x, ocol[1].y);
-        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(ocol[2].x, ocol[2].y, ocol[3].x, ocol[3].y);
-        const long long so = p.linear ? col * nmb + mb0
-                                      : ((long long)ct * (nmb >> 2) + mt * 2 + half) * 512 + lane * 16 + quad * 4;
-        *reinterpret_cast<u32*>(p.scales_c + so) = sb_col;
+        if (more) {
+          // first chunk of the next tile, requested before this tile's last chunk is quantized
+          if (!wait_full(nbuf, npar)) break;
+          if (ROWS) q_ld16(t_lane + 128u * nbuf, first16); else q_ld32(t_lane + 128u * nbuf, first32);
+        }
+        col_pair(c1, 1);
+        store_cols();
       }
     }
   }
@@ -418,23 +470,27 @@ static bool make_tc_map(CUtensorMap* map, const void* x, long long M, long long 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int ROUNDING, bool ROWS, bool COLS>
+template <int ROUNDING, bool ROWS, bool COLS, bool TCRHT = false>
 static int launch_tc(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t st) {
   static bool configured[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return NVFP4_ERR_CUDA;
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(quant_tc_kernel<ROUNDING, ROWS, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(quant_tc_kernel<ROUNDING, ROWS, COLS, TCRHT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQSmem) != cudaSuccess)
       return NVFP4_ERR_CUDA;
     configured[dev] = true;
   }
-  quant_tc_kernel<ROUNDING, ROWS, COLS><<<grid, kQThreads, kQSmem, st>>>(map, p);
+  quant_tc_kernel<ROUNDING, ROWS, COLS, TCRHT><<<grid, kQThreads, kQSmem, st>>>(map, p);
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;
 }
 
 template <int ROUNDING>
 static int launch_tc_mode(const CUtensorMap& map, const TcParams& p, int grid, cudaStream_t st) {
+  if (p.tc_rht && p.codes_c) {
+    if (p.codes_r) return launch_tc<ROUNDING, true, true, true>(map, p, grid, st);
+    return launch_tc<ROUNDING, false, true, true>(map, p, grid, st);
+  }
   if (p.codes_r && p.codes_c) return launch_tc<ROUNDING, true, true>(map, p, grid, st);
   if (p.codes_c) return launch_tc<ROUNDING, false, true>(map, p, grid, st);
   return launch_tc<ROUNDING, true, false>(map, p, grid, st);
@@ -453,6 +509,10 @@ bool nvfp4_quant_tc_accepts(const void* x, long long ldx, int M, int C, const vo
            (reinterpret_cast<uintptr_t>(scales_c) & 3u));
 }
 
+static int g_tc_rht = 0;
+// 1: the Hadamard transform of the transposed operand runs inside the MMA instead of FP32 butterflies
+void nvfp4_quant_tc_set_rht(int on) { g_tc_rht = on ? 1 : 0; }
+
 // Arguments as nvfp4_quant_tile, already validated by it.
 int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* codes_r, void* scales_r, void* codes_c,
                           void* scales_c, int scale_layout, const float* amax, float* gs_r_out, float* gs_c_out,
@@ -468,6 +528,7 @@ int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* code
   p.M = M; p.C = C; p.linear = scale_layout == NVFP4_SCALES_LINEAR;
   p.signs = signs & 0xFFFFu;
   p.seed_r = seed_r; p.seed_c = seed_c; p.seed_r_dev = seed_r_dev; p.seed_c_dev = seed_c_dev;
+  p.tc_rht = g_tc_rht;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) {
     int n = 0;

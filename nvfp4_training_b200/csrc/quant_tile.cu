@@ -312,12 +312,16 @@ int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* code
                           unsigned signs, int rounding, unsigned seed_r, unsigned seed_c,
                           const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
 int nvfp4_quant_tc_status(int* out, int reset);
+void nvfp4_quant_tc_set_rht(int on);
 
-static int g_tile_path = 0;   // 0 = tensor-core-fed kernel where it applies, 1 = always the scalar tile kernel
+// 0 = tensor-core-fed kernel where it applies, 1 = always the scalar tile kernel, 2 = tensor-core-fed kernel with the
+// Hadamard transform inside the MMA
+static int g_tile_path = 0;
 
 extern "C" int nvfp4_quant_tile_set_path(int path) {
-  if (path != 0 && path != 1) return NVFP4_ERR_ENUM;
+  if (path < 0 || path > 2) return NVFP4_ERR_ENUM;
   g_tile_path = path;
+  nvfp4_quant_tc_set_rht(path == 2);
   return NVFP4_OK;
 }
 
@@ -334,7 +338,7 @@ extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void
       (reinterpret_cast<uintptr_t>(codes_c) & 15u) || (reinterpret_cast<uintptr_t>(scales_c) & 7u))
     return NVFP4_ERR_ALIGN;
   if (M == 0 || C == 0) return NVFP4_OK;
-  if (g_tile_path == 0 && nvfp4_quant_tc_accepts(x, ldx, M, C, codes_r, scales_r, codes_c, scales_c))
+  if (g_tile_path != 1 && nvfp4_quant_tc_accepts(x, ldx, M, C, codes_r, scales_r, codes_c, scales_c))
     return nvfp4_quant_tc_launch(x, ldx, M, C, codes_r, scales_r, codes_c, scales_c, scale_layout, amax, gs_r_out, gs_c_out,
                                  signs, rounding, seed_r, seed_c, seed_r_dev, seed_c_dev, stream);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

