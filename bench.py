@@ -246,6 +246,8 @@ def isolated_kernels(cfg, T, peaks):
     detail["emit_rows_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     t = q(lambda t, a: emit.row_emit(t, rq, rng, sr=True))
     detail["emit_rows_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: emit.row_emit(t, rq, rng, sr="hw"))
+    detail["emit_rows_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     # column operand with a delayed scale: RHT16 + quantization in one read, records the next amax
     cq = emit.ColQ(T, 5632)
     use = torch.full((1,), 16.0, dtype=torch.float32, device=dev)
@@ -254,6 +256,8 @@ def isolated_kernels(cfg, T, peaks):
     detail["emit_cols_rn"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     t = q(lambda t, a: emit.col_emit(t, cq, use, cur, rng, sr=True))
     detail["emit_cols_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    t = q(lambda t, a: emit.col_emit(t, cq, use, cur, rng, sr="hw"))
+    detail["emit_cols_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     w = [torch.randn(11264, 2048, generator=g, device=dev).bfloat16() for _ in range(4)]
     it = [0]
 

@@ -136,7 +136,8 @@ int nvfp4_quant_tile_set_path(int path);
 
 /* Reads (synchronously) the status word of nvfp4_quant_tile launches on the current device:
  * 0, or the role whose wait expired first (scalar kernel: 1 producer, 2 consumer; tensor-core-fed kernel:
- * 17 / 19 the loading and MMA-issuing warp waiting for a tile / for a free stage, 18 a consumer); `reset` != 0 clears it. */
+ * 17 / 19 the loading and MMA-issuing warp waiting for a tile / for a free stage, 18 a consumer; row emitter's ring
+ * kernel: 33 producer, 34 consumer); `reset` != 0 clears it. */
 int nvfp4_quant_tile_status(int* out, int reset);
 
 /*
@@ -150,11 +151,19 @@ int nvfp4_quant_tile_status(int* out, int reset);
  * lane l = (column/8) % 32 of row r runs s <- s*1664525+1013904223 from hash32(rng[0] ^ salt ^
  * hash32(r*32+l)) over its 8-column chunks in column order, one step per pair of values; for C == 11264 the
  * sequence of `row_emit_11264`: four per lane, sequence s from hash32(rng[0] ^ salt ^ hash32(r*128+s*32+l)) over
- * the chunks 4 j + s.  rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0, T % 128 == 0,
- * ldx % 8 == 0, x 16-byte aligned.
+ * the chunks 4 j + s.  sr == 2: hardware stochastic convert (cvt.rs.satfinite.e2m1x4.f32) with this library's
+ * counter-based words, key from rng[0] ^ salt and the block index r*(C/16) + block (no reference counterpart; rows
+ * of at most 11776 columns).  rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0,
+ * T % 128 == 0, ldx % 8 == 0, x 16-byte aligned.  Two kernels stand behind it: rows of at most 11776 columns travel
+ * as whole rows through a shared-memory ring fed by bulk copies (cp.async.bulk) and are quantized from there;
+ * longer rows take a warp-per-row kernel that re-reads them through L2.  Same bytes from both.
  */
 int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
                     int sr, const unsigned* rng, unsigned salt, void* stream);
+
+/* Tuning / test hook: 0 = nvfp4_emit_rows picks the ring kernel where it applies (default), 1 = always the
+ * warp-per-row kernel.  Process-wide.  No reference counterpart. */
+int nvfp4_emit_rows_set_path(int path);
 
 /*
  * Column operand with a delayed per-tensor scale: x [M, C] bf16 (row stride ldx) -> x^T quantized
@@ -165,7 +174,9 @@ int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, voi
  * and launcher `emit.col_emit` (llm-1b/emit.py:82-85).  rng: device words, rng[0] = SR seed, rng[1] =
  * Hadamard sign bits (required).  sr != 0: 11-bit mantissa dither with the reference's random
  * sequence (the thread of column c and 64-token group g starts at hash32(rng[0] ^ salt ^ hash32(c*4099+g))
- * and takes its four 16-token blocks in order, one LCG step per pair of values).
+ * and takes its four 16-token blocks in order, one LCG step per pair of values).  sr == 2: hardware stochastic convert
+ * with this library's counter-based words (key from rng[0] ^ salt and the block index c*(M/16) + block; no reference
+ * counterpart).
  * Requires M % 128 == 0, C % 128 == 0, ldx % 8 == 0, x and codes 16-byte aligned, scales 8-byte aligned.
  */
 int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void* codes, void* scales,

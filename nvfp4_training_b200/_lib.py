@@ -31,6 +31,7 @@ SIGNATURES = {
     "nvfp4_quant_tile_status": (_i, [_vp, _i]),
     "nvfp4_quant_tile_set_path": (_i, [_i]),
     "nvfp4_emit_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp, _u, _vp]),
+    "nvfp4_emit_rows_set_path": (_i, [_i]),
     "nvfp4_emit_cols": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _u, _vp]),
     "nvfp4_quant_w2d": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
     "nvfp4_e2m1x4_sr": (_i, [_vp, _vp, _vp, _ll, _vp]),
@@ -61,7 +62,8 @@ def load():
         if not os.path.exists(LIB_PATH):
             raise Nvfp4Error(f"{LIB_PATH} not found: build it with `python -m nvfp4_training_b200.build` "
                              "(there is no fallback path)")
-        lib = ctypes.CDLL(LIB_PATH)
+        # NVFP4_LIB_PATH: load another build of the same library (A/B timing of kernel variants)
+        lib = ctypes.CDLL(os.environ.get("NVFP4_LIB_PATH") or LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args

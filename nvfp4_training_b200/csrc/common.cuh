@@ -86,6 +86,7 @@ __device__ __forceinline__ float sr_dither(float v, u32 rnd) {
 // multiplications, no exact divisions); not part of the public rounding enum.
 #define NVFP4_EMIT_NEAREST 4   /* y = v * (inv/bs), round to nearest */
 #define NVFP4_EMIT_SR      5   /* same, 11-bit mantissa dither driven by a per-thread LCG */
+#define NVFP4_EMIT_SR_HW   6   /* same scaling, hardware cvt.rs with this library's counter-based words */
 
 // dither with bits already in place (11 random bits at positions 11..21), truncate to the E2M1
 // grid, clamp to 6, restore the sign (llm-1b/emit.cu:38-43)
@@ -265,7 +266,7 @@ __device__ __forceinline__ u32 round8(float (&y)[8], u32& key, u32 seed, u32 elt
     }
     return e2m1x8_rn(y);
   }
-  if (ROUNDING == NVFP4_ROUND_SR_HW)
+  if (ROUNDING == NVFP4_ROUND_SR_HW || ROUNDING == NVFP4_EMIT_SR_HW)
     return e2m1x4_rs(y[0], y[1], y[2], y[3], sr_hw_word(key, 2 * h)) | (e2m1x4_rs(y[4], y[5], y[6], y[7], sr_hw_word(key, 2 * h + 1)) << 16);
   if (ROUNDING == NVFP4_ROUND_SR_DITHER || ROUNDING == NVFP4_ROUND_SR_DITHER_K) {
 #pragma unroll
@@ -317,7 +318,7 @@ template <int ROUNDING>
 __device__ __forceinline__ void quant_block16x2(const u64 (&P)[16], const TensorScale& ts, u32 seed, u32 blk0, u32 blk1,
                                                 u32 key0, u32 key1, uint2& o0, uint2& o1, u32& sb0, u32& sb1,
                                                 float* bmax_out = nullptr) {
-  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR;
+  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR || ROUNDING == NVFP4_EMIT_SR_HW;
   float m0 = absmax3(f2_lo(P[0]), f2_lo(P[1]), f2_lo(P[2])), m1 = absmax3(f2_hi(P[0]), f2_hi(P[1]), f2_hi(P[2]));
 #pragma unroll
   for (int i = 3; i < 15; i += 2) { m0 = absmax3(m0, f2_lo(P[i]), f2_lo(P[i + 1])); m1 = absmax3(m1, f2_hi(P[i]), f2_hi(P[i + 1])); }

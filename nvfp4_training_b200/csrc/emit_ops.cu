@@ -116,12 +116,29 @@ static void launch_rows(bool sr, unsigned blocks, cudaStream_t st, const __nv_bf
 
 using namespace nvfp4;
 
+// the TMA-fed kernel (emit_rows_ring.cu)
+bool nvfp4_emit_rows_ring_accepts(const void* x, long long ldx, int T, int C, const void* codes);
+int nvfp4_emit_rows_ring_launch(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
+                                int sr, const unsigned* rng, unsigned salt, void* stream);
+
+static int g_emit_rows_path = 0;   // 0 = TMA-fed kernel where it applies, 1 = always the warp-per-row kernel
+
+extern "C" int nvfp4_emit_rows_set_path(int path) {
+  if (path != 0 && path != 1) return NVFP4_ERR_ENUM;
+  g_emit_rows_path = path;
+  return NVFP4_OK;
+}
+
 extern "C" int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void* codes, void* scales, float* rs_out,
                                int sr, const unsigned* rng, unsigned salt, void* stream) {
   if (!x || !codes || !scales || !rs_out || (sr && !rng)) return NVFP4_ERR_NULL;
   if (T < 0 || C < 0 || (C & 255) || ldx < C || (T & 127)) return NVFP4_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes) & 3u)) return NVFP4_ERR_ALIGN;
+  if (sr < 0 || sr > 2) return NVFP4_ERR_ENUM;
   if (T == 0 || C == 0) return NVFP4_OK;
+  if (g_emit_rows_path == 0 && nvfp4_emit_rows_ring_accepts(x, ldx, T, C, codes))
+    return nvfp4_emit_rows_ring_launch(x, ldx, T, C, codes, scales, rs_out, sr, rng, salt, stream);
+  if (sr == 2) return NVFP4_ERR_ENUM;      // the hardware-convert mode exists in the TMA-fed kernel only
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned blocks = (unsigned)((T + 7) / 8);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);

@@ -745,7 +745,11 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       {
         const u32 bar = BN == 256 ? accf0 : accf0 + 8 * acc;
         const u32 par = BN == 256 ? (tile & 1u) : ((tile >> 1) & 1u);
-        if (!__all_sync(0xffffffffu, NVFP4_IDLE_WAIT(bar, par, abort_flag))) { ok = false; break; }
+        // BN = 256: the warps that own the 48 columns the two accumulators share are on the critical path of the
+        // next tile's first MMA (it waits for their hand-back), so they poll instead of sleeping
+        const bool critical = BN == 256 && ((acc && half == 0) || (!acc && half == 1));
+        const bool got = critical ? mbar_wait(bar, par, abort_flag) : NVFP4_IDLE_WAIT(bar, par, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       }
       tc_fence_after();
       u32 r[NC];

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   if (ROWS) ts_r = make_tensor_scale<ROUNDING>(amax, 1.f, lut_r, first ? p.gs_r_out : nullptr);
   // the x0.25 that follows the butterflies is folded into the tensor scale (a power of two); the
   // emitter's delayed amax is already an RHT-domain value (no factor 4)
-  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR;
+  constexpr bool EMIT = ROUNDING == NVFP4_EMIT_NEAREST || ROUNDING == NVFP4_EMIT_SR || ROUNDING == NVFP4_EMIT_SR_HW;
   if (COLS) ts_c = make_tensor_scale<ROUNDING>(amax, EMIT ? 1.f : 4.f, lut_c, first ? p.gs_c_out : nullptr, 0.25f);
   __syncthreads();
 
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
   u32 signs = p.signs;
   float seen = 0.f;                              // emitter: largest transformed magnitude this thread met
   if (EMIT) {
-    seed_c = (ROUNDING == NVFP4_EMIT_SR ? __ldg(p.rng) : 0u) ^ p.salt;
+    seed_c = (ROUNDING != NVFP4_EMIT_NEAREST ? __ldg(p.rng) : 0u) ^ p.salt;
     if (p.rng) signs = __ldg(p.rng + 1) & 0xFFFFu;
   }
   const int nblk = p.C >> 4;                     // 16-column blocks per row
@@ -207,7 +207,10 @@ __global__ void __launch_bounds__(kTileThreads, 2) quant_tile_kernel(const __gri
       uint2 o0, o1; u32 sb0, sb1;
       u32 key0, key1;
       float bmax = 0.f;
-      if (EMIT) {
+      if (ROUNDING == NVFP4_EMIT_SR_HW) {
+        key0 = sr_hw_block_key(seed_c, b0);
+        key1 = sr_hw_block_key(seed_c, b1);
+      } else if (EMIT) {
         // the reference's thread of (column, 64-token group) walks its four blocks in order: jump to block mb & 3
         const u32 c = (u32)(ct * kTileCol + 2 * lane), mb = (u32)(mt * (kTileTok / 16) + cw);
         key0 = hash32(seed_c ^ hash32(c * 4099u + (mb >> 2)));
@@ -313,6 +316,7 @@ int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* code
                           const unsigned* seed_r_dev, const unsigned* seed_c_dev, void* stream);
 int nvfp4_quant_tc_status(int* out, int reset);
 void nvfp4_quant_tc_set_rht(int on);
+int nvfp4_emit_rows_ring_status(int* out, int reset);
 
 // 0 = tensor-core-fed kernel where it applies, 1 = always the scalar tile kernel, 2 = tensor-core-fed kernel with the
 // Hadamard transform inside the MMA
@@ -371,6 +375,7 @@ extern "C" int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void*
                                const float* amax_use, unsigned* amax_cur, int sr, const unsigned* rng, unsigned salt,
                                void* stream) {
   if (!x || !codes || !scales || !amax_use || !rng) return NVFP4_ERR_NULL;
+  if (sr < 0 || sr > 2) return NVFP4_ERR_ENUM;
   if (M < 0 || C < 0 || (M % kTileTok) || (C & 127) || ldx < C) return NVFP4_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (ldx & 7) || (reinterpret_cast<uintptr_t>(codes) & 15u) ||
       (reinterpret_cast<uintptr_t>(scales) & 7u))
@@ -391,6 +396,7 @@ extern "C" int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void*
   const long long ntiles = (long long)(M / kTileTok) * (C / kTileCol);
   int grid = 2 * sms;
   if (ntiles < grid) grid = (int)ntiles;
+  if (sr == 2) return launch_tile<NVFP4_EMIT_SR_HW, false, true>(map, p, grid, st);
   return sr ? launch_tile<NVFP4_EMIT_SR, false, true>(map, p, grid, st)
             : launch_tile<NVFP4_EMIT_NEAREST, false, true>(map, p, grid, st);
 }
@@ -405,6 +411,10 @@ extern "C" int nvfp4_quant_tile_status(int* out, int reset) {
   int tc = 0;
   const int rc = nvfp4_quant_tc_status(&tc, reset);
   if (rc != NVFP4_OK) return rc;
+  int ring = 0;
+  const int rc2 = nvfp4_emit_rows_ring_status(&ring, reset);
+  if (rc2 != NVFP4_OK) return rc2;
+  if (*out == 0 && ring) *out = 32 + ring;  // TMA-fed row emitter: 33 producer, 34 consumer
   if (*out == 0 && tc) *out = 16 + tc;    // tensor-core-fed kernel: 17 / 19 its loading and MMA-issuing warp (waiting for a tile / a free stage), 18 a consumer
   return NVFP4_OK;
 }

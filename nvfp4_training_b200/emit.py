@@ -39,27 +39,30 @@ class ColQ:
 def col_emit(x, q: ColQ, amax_use, amax_cur, rng, sr=False, salt=0):
     """RHT16 along the tokens + quantization of x^T with the delayed scale `amax_use`; records the
     RHT-domain amax of x into `amax_cur` (float bits, atomicMax: zero it first) (llm-1b/emit.py:82-85).
-    `rng`: CUDA int32 words, rng[0] = SR seed, rng[1] = Hadamard sign bits."""
+    `rng`: CUDA int32 words, rng[0] = SR seed, rng[1] = Hadamard sign bits.  `sr`: False / True (the reference's
+    dither and sequence) / "hw" (hardware stochastic convert, this library's counter-based words)."""
     L.require_cuda(x, q.d, q.s, amax_use, amax_cur, rng)
     M, C = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and M % 256 == 0 and C % 64 == 0
     assert C % 128 == 0, C          # swizzled scale tiles of 128 columns are written whole
     assert rng.element_size() == 4 and rng.numel() >= 2 and amax_cur.element_size() == 4
     L.check(L.load().nvfp4_emit_cols(L.ptr(x), x.stride(0), M, C, L.ptr(q.d), L.ptr(q.s), L.ptr(amax_use), L.ptr(amax_cur),
-                                     int(bool(sr)), L.ptr(rng), salt & 0xFFFFFFFF, L.stream()), "emit_cols")
+                                     2 if sr == "hw" else int(bool(sr)), L.ptr(rng), salt & 0xFFFFFFFF, L.stream()), "emit_cols")
     return q
 
 
 def row_emit(x, q: RowQ, rng, sr=False, salt=0):
     """Quantize the rows of x [T, C] into q (llm-1b/emit.py:72-79).  `rng`: CUDA int32/uint32 words,
-    rng[0] = stochastic-rounding seed (read on the device, so a captured graph sees fresh seeds)."""
+    rng[0] = stochastic-rounding seed (read on the device, so a captured graph sees fresh seeds).
+    `sr`: False = round to nearest, True = the reference's mantissa dither and random sequence, "hw" = the hardware
+    stochastic convert with this library's counter-based words (an addition; rows of at most 11776 columns)."""
     L.require_cuda(x, q.d, q.s, q.rs)
     T, C = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and C % 256 == 0
     assert T % 128 == 0, T
     if sr:
         assert rng is not None and rng.is_cuda and rng.element_size() == 4
-    L.check(L.load().nvfp4_emit_rows(L.ptr(x), x.stride(0), T, C, L.ptr(q.d), L.ptr(q.s), L.ptr(q.rs), int(bool(sr)),
+    L.check(L.load().nvfp4_emit_rows(L.ptr(x), x.stride(0), T, C, L.ptr(q.d), L.ptr(q.s), L.ptr(q.rs), 2 if sr == "hw" else int(bool(sr)),
                                      L.ptr(rng) if rng is not None else None, salt & 0xFFFFFFFF, L.stream()), "emit_rows")
     return q
 

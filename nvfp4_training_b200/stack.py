@@ -99,6 +99,8 @@ class LinearStack:
         GEMM epilogue."""
         assert mode in ("tensor", "emit")
         self.mode = mode
+        # emitter mode rounds gradients with the hardware convert ("hw"); True selects the reference's dither sequences
+        self.emit_sr = "hw" if sr_mode == _lib.ROUND_SR_HW else True
         self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
         self.ar_blocks = max(1, ar_blocks)   # transformer blocks per gradient all-reduce
         self.cfg, self.T, self.device, self.group = cfg, microbatch, torch.device(device), group
@@ -217,8 +219,8 @@ class LinearStack:
         for p in reversed(projs):
             gy = self.gy_pool[p.name]
             use_x, use_g = self.amax_use[p.lid, 0:1], self.amax_use[p.lid, 1:2]
-            rq = emit.row_emit(gy, emit.RowQ(T, p.N, self.device), self.rng, sr=True, salt=p.lid * 8 + 1)
-            cg = emit.col_emit(gy, emit.ColQ(T, p.N, self.device), use_g, self.amax_cur[p.lid, 1:2], self.rng, sr=True,
+            rq = emit.row_emit(gy, emit.RowQ(T, p.N, self.device), self.rng, sr=self.emit_sr, salt=p.lid * 8 + 1)
+            cg = emit.col_emit(gy, emit.ColQ(T, p.N, self.device), use_g, self.amax_cur[p.lid, 1:2], self.rng, sr=self.emit_sr,
                                salt=p.lid * 8 + 2)
             gx = emit.mm_row_wt(rq, p.wq, scale=True)
             emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)

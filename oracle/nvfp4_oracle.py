@@ -485,6 +485,12 @@ def emit_rows(x, seed=0, sr=False, salt=0):
     rows = np.arange(T, dtype=np.uint32)[:, None]
     lanes = np.arange(32, dtype=np.uint32)[None, :]
     key = np.uint32((seed if sr else 0) & 0xFFFFFFFF) ^ np.uint32(salt & 0xFFFFFFFF)
+    if sr == 2 or sr == "hw":
+        # this library's hardware-convert mode: key from seed ^ salt and the block index r*(C/16) + block
+        y = (xb * k[..., None]).astype(np.float32)
+        blk = np.arange(T * (C // 16), dtype=np.uint64).reshape(T, C // 16).astype(np.uint32)
+        c16 = sr_hw_code(y, sr_bits_hw(int(key), blk))
+        return pack_codes(c16.reshape(T, C)), sbyte, rs
     subs = 4 if (C == 11264 and sr) else 1
     if subs == 1:
         states = [hash32(key ^ hash32(rows * np.uint32(32) + lanes))]
@@ -520,6 +526,13 @@ def emit_cols(x, signs, amax_use, seed=0, sr=False, salt=0):
     sd = e4m3_decode(sbyte).astype(np.float32)
     with np.errstate(divide="ignore", invalid="ignore"):
         k = np.where(sd > 0, inv / np.where(sd > 0, sd, np.float32(1)), np.float32(0)).astype(np.float32)
+    if sr == 2 or sr == "hw":
+        # this library's hardware-convert mode: key from seed ^ salt and the block index c*(M/16) + block
+        y = (t * k[..., None]).astype(np.float32)
+        blk = np.arange(C * (M // 16), dtype=np.uint64).reshape(C, M // 16).astype(np.uint32)
+        key = (seed & 0xFFFFFFFF) ^ (salt & 0xFFFFFFFF)
+        c16 = sr_hw_code(y, sr_bits_hw(key, blk))
+        return pack_codes(c16.reshape(C, M)), sbyte, amax_cur
     codes = np.empty((C, M // 16, 16), dtype=np.uint8)
     cols = np.arange(C, dtype=np.uint32)[:, None]
     grps = np.arange(M // 64, dtype=np.uint32)[None, :]

@@ -65,6 +65,8 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_emit_rows(p, 384, 128, 384, p, p, p, 0, None, 0, None) == -2          # C % 256
     assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, p, 1, None, 0, None) == -1          # SR needs the device seed
     assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, None, 0, None, 0, None) == -1
+    assert lib.nvfp4_emit_rows(p, 256, 128, 256, p, p, p, 3, p, 0, None) == -4            # rounding mode 0, 1 or 2
+    assert lib.nvfp4_emit_rows_set_path(2) == -4 and lib.nvfp4_emit_rows_set_path(1) == 0 and lib.nvfp4_emit_rows_set_path(0) == 0
     assert lib.nvfp4_emit_cols(p, 128, 128, 128, p, p, p, p, 0, None, 0, None) == -1       # rng carries the sign bits
     assert lib.nvfp4_emit_cols(p, 192, 128, 192, p, p, p, p, 0, p, 0, None) == -2          # C % 128
     assert lib.nvfp4_emit_cols(p, 128, 64, 128, p, p, p, p, 0, p, 0, None) == -2           # M % 128

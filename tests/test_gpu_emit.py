@@ -10,11 +10,15 @@ from tests.gpu_util import make_dy, make_w, make_x, rel_fro, to_dev, u8
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def emit():
+@pytest.fixture(scope="module", params=[0, 1], ids=["ring", "warp_per_row"])
+def emit(request):
+    """Both kernels behind nvfp4_emit_rows: 0 = rows through the TMA-fed shared-memory ring, 1 = warp per row."""
     from nvfp4_training_b200 import _lib, emit
-    _lib.load()
-    return emit
+    lib = _lib.load()
+    assert lib.nvfp4_emit_rows_set_path(request.param) == 0
+    yield emit
+    lib.nvfp4_emit_rows_set_path(0)
+    _lib.check_status()
 
 
 def _check(q, ref, T, C):
@@ -114,6 +118,18 @@ def test_col_emit_sr_bit_exact_with_the_reference_stream(emit, seed, salt):
     cur = torch.zeros(1, dtype=torch.int32, device="cuda")
     q = emit.col_emit(to_dev(g), emit.ColQ(M, C), use, cur, _rng(seed, signs), sr=True, salt=salt)
     _check_cols(q, O.emit_cols(g, signs, au, seed=seed, sr=True, salt=salt), cur, M, C)
+
+
+def test_col_emit_hardware_sr_bit_exact(emit):
+    """The hardware stochastic-convert mode of the column emitter against the oracle's model of the convert with this
+    library's counter-based words (key from rng[0] ^ salt and the block index)."""
+    M, C, signs = 2048, 384, 0xA6B1
+    g = make_dy(78, M, C)
+    au = np.float32(np.abs(O.rht16_cols(g, signs)).max() * np.float32(1.5))
+    use = torch.tensor([float(au)], dtype=torch.float32, device="cuda")
+    cur = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = emit.col_emit(to_dev(g), emit.ColQ(M, C), use, cur, _rng(77, signs), sr="hw", salt=5)
+    _check_cols(q, O.emit_cols(g, signs, au, seed=77, sr="hw", salt=5), cur, M, C)
 
 
 def test_wgrad_from_two_column_operands(emit):
@@ -251,3 +267,36 @@ def test_gemm_row_scale_epilogue(emit, tile):
     finally:
         L.load().nvfp4_gemm_force_tile_n(0)
     L.check_status()
+
+
+def test_row_emit_ring_many_rows_per_cta_and_hardware_sr():
+    """The ring kernel with many rows per CTA (every slot of the ring is reused several times, every consumer warp
+    takes several rows): [4096, 2048] round to nearest (whole tensor) and [2048, 11264] with the reference's
+    four-sequence dither stream; and the hardware stochastic-rounding mode against the oracle's model of the convert
+    with this library's counter-based words."""
+    from nvfp4_training_b200 import _lib, emit
+    lib = _lib.load()
+    assert lib.nvfp4_emit_rows_set_path(0) == 0
+    x = make_x(3, 4096, 2048)
+    q = emit.row_emit(to_dev(x), emit.RowQ(4096, 2048), None)
+    _check(q, O.emit_rows(x), 4096, 2048)
+    g = make_dy(4, 2048, 11264)
+    rng = torch.tensor([99, 0], dtype=torch.int32, device="cuda")
+    q = emit.row_emit(to_dev(g), emit.RowQ(2048, 11264), rng, sr=True, salt=7)
+    _check(q, O.emit_rows(g, seed=99, sr=True, salt=7), 2048, 11264)
+    g = make_dy(5, 1024, 5632)
+    q = emit.row_emit(to_dev(g), emit.RowQ(1024, 5632), rng, sr="hw", salt=11)
+    _check(q, O.emit_rows(g, seed=99, sr="hw", salt=11), 1024, 5632)
+    # unbiasedness of the hardware mode at tensor level: mean of 64 draws beats round-to-nearest by 4x
+    gd = to_dev(g)
+    acc = torch.zeros(1024, 5632, device="cuda")
+    for s_ in range(64):
+        rng[0] = s_ + 1
+        qq = emit.row_emit(gd, emit.RowQ(1024, 5632), rng, sr="hw")
+        acc += emit.dequant(qq.d, qq.s, qq.rs)
+    qq = emit.row_emit(gd, emit.RowQ(1024, 5632), None)
+    gf = gd.float()
+    e_rn = ((emit.dequant(qq.d, qq.s, qq.rs) - gf).norm() / gf.norm()).item()
+    e_sr = ((acc / 64 - gf).norm() / gf.norm()).item()
+    assert e_sr <= 0.25 * e_rn, (e_sr, e_rn)
+    _lib.check_status()

@@ -128,7 +128,7 @@ def test_stack_emitter_mode_graphs_equal_eager_and_oracle():
     b._bwd_block(b.blocks[0], keep=True, first=True)
     torch.cuda.synchronize()
     cx, sx, _ = O.emit_cols(x, _RHT_SIGNS, use[p.lid, 0])
-    cg, sg, _ = O.emit_cols(gy, _RHT_SIGNS, use[p.lid, 1], seed=seed, sr=True, salt=p.lid * 8 + 2)
+    cg, sg, _ = O.emit_cols(gy, _RHT_SIGNS, use[p.lid, 1], seed=seed, sr="hw", salt=p.lid * 8 + 2)
     want = O.gemm_unit(cg, sg, cx, sx) * (float(use[p.lid, 1]) / 2688.0) * (float(use[p.lid, 0]) / 2688.0)
     assert rel_fro(f32(p.gw), want) <= 1e-4
     # forward y and dgrad of the same projection: per-row scales in the epilogue
@@ -137,7 +137,7 @@ def test_stack_emitter_mode_graphs_equal_eager_and_oracle():
     wc, ws, wct, wst, wgs = O.quant_w2d(w)
     y = O.gemm_unit(rc, rsb, wc, ws) * rs.astype(np.float64)[:, None] * float(wgs)
     assert rel_fro(f32(p.y), y) <= 4e-3
-    gc, gsb, grs = O.emit_rows(gy, seed=seed, sr=True, salt=p.lid * 8 + 1)
+    gc, gsb, grs = O.emit_rows(gy, seed=seed, sr="hw", salt=p.lid * 8 + 1)
     gx = O.gemm_unit(gc, gsb, wct, wst) * grs.astype(np.float64)[:, None] * float(wgs)
     assert rel_fro(f32(p.gx), gx) <= 4e-3
     _lib.check_status()
