@@ -184,6 +184,33 @@ def time_events(fn, iters, warm=3):
     return a.elapsed_time(b) / iters * 1e-3
 
 
+def time_graph(fn, iters, warm=2):
+    """Like time_events, with the `iters` calls captured once into a CUDA graph and replayed: the timing then holds no
+    host launch overhead (a Python call into the library costs 10-20 us, more than a small kernel runs)."""
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(warm):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(iters):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    t = a.elapsed_time(b) / iters * 1e-3
+    del g
+    return t
+
+
 def _lib_consts():
     from nvfp4_training_b200 import _lib
     return _lib
@@ -439,8 +466,8 @@ def comm_breakdown(stack, n_micro, steps):
 
 # ------------------------------------------------------------------------------------------ configuration sweeps
 def config_sweeps(cfg, peaks):
-    """The other benchmark configurations, each timed with CUDA events on one GPU (rotating operand sets larger than
-    L2 where one set would fit):
+    """The other benchmark configurations, each timed with CUDA events on one GPU around a CUDA-graph replay of the
+    launches (no host launch overhead in the figures; rotating operand sets larger than L2 where one set would fit):
       config2   every projection of one block at T = 4096: the whole layer (quantizers + 3 GEMMs, weights cached) and
                 its three GEMMs alone
       config3   wgrad stress: dY [16384, 5632] stochastic + X [16384, 2048] nearest, RHT16 on both, FP32 dW
@@ -478,12 +505,12 @@ def config_sweeps(cfg, peaks):
             a, b, _ = ops[it[0] % nset]
             it[0] += 1
             torch._scaled_mm(a.d, b.d.t(), a.s.view(-1), b.s.view(-1), out_dtype=torch.bfloat16)
-        t = time_events(run, iters=max(8, 2 * nset))
+        t = time_graph(run, iters=max(8, 2 * nset))
         out = {"M": M, "N": N, "K": K, "us": t * 1e6, "tflops": 2.0 * M * N * K / t / 1e12,
                "frac_of_4x_bf16": 2.0 * M * N * K / t / 1e12 / fp4_peak}
         if lib and not fp32:
             try:
-                tl = time_events(run_lib, iters=max(8, 2 * nset))
+                tl = time_graph(run_lib, iters=max(8, 2 * nset))
                 out["scaled_mm_tflops"] = 2.0 * M * N * K / tl / 1e12
             except Exception as e:
                 out["scaled_mm_error"] = repr(e)[:100]
@@ -505,7 +532,7 @@ def config_sweeps(cfg, peaks):
             def run():
                 it[0] += 1
                 fn(xs[it[0] % nset])
-            t = time_events(run, iters=max(6, 2 * nset))
+            t = time_graph(run, iters=max(6, 2 * nset))
             return {"us": t * 1e6, "gbs": n * bpe / t / 1e9, "frac_hbm": n * bpe / t / 1e9 / hbm}
         res["config5_quant"][label] = {
             "elements": n,
@@ -537,7 +564,7 @@ def config_sweeps(cfg, peaks):
             it[0] += 1
             _, am, qxt = linear_fwd(xs[i], q, keep_xt=True)
             linear_bwd(None, am, gys[i], qt, 1, 2, gw_out=gw, sr_mode=HW, overwrite=True, qxt=qxt)
-        t = time_events(layer, iters=12)
+        t = time_graph(layer, iters=12)
         fl = 6.0 * T * N * K
         res["config2"][name] = {"T": T, "N": N, "K": K, "layer_us": t * 1e6, "layer_tflops": fl / t / 1e12,
                                 "layer_frac_of_4x_bf16": fl / t / 1e12 / fp4_peak,
@@ -554,7 +581,7 @@ def config_sweeps(cfg, peaks):
         qgt = nvq.quant_cols_rht(gy, _RHT_SIGNS, sr=True, seed=3, am=am_g, sr_mode=HW)
         qxt = nvq.quant_cols_rht(x, _RHT_SIGNS, am=am_x)
         nvq.mm(qgt, qxt, out_dtype=torch.float32, out=dw)
-    t = time_events(wgrad, iters=12)
+    t = time_graph(wgrad, iters=12)
     res["config3"] = {"T": T, "N": N, "K": K, "quant_plus_gemm_us": t * 1e6, "tflops": 2.0 * T * N * K / t / 1e12,
                       "gemm_alone": gemm_time(N, K, T, fp32=True)}
     exact = gy.double().t() @ x.double()
@@ -596,7 +623,8 @@ def run_ours(args):
     plan = shard_plan(world, rank, GLOBAL_TOKENS, args.microbatch)
     mb, n_micro = plan["microbatch"], plan["n_micro"]
     stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=0, input_seed=1000 + rank, use_graphs=not args.no_graphs,
-                        comm_sms=args.comm_sms if world > 1 else 0, ar_blocks=args.ar_blocks)
+                        comm_sms=args.comm_sms if world > 1 else 0, ar_blocks=args.ar_blocks,
+                        wgrad_side_stream=not args.no_wgrad_stream)
     if not args.no_graphs:
         stack.capture()
     do_ar = world > 1
@@ -860,6 +888,8 @@ def main():
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs left free for NCCL during backward when N > 1 (default: 32 at N >= 8, else 16)")
+    ap.add_argument("--no-wgrad-stream", action="store_true",
+                    help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--skip-isolated", action="store_true",
                     help="skip the isolated-kernel legs, the configuration sweeps and the communication breakdown (for profiler runs)")

@@ -152,8 +152,8 @@ int nvfp4_quant_tile_status(int* out, int reset);
  * hash32(r*32+l)) over its 8-column chunks in column order, one step per pair of values; for C == 11264 the
  * sequence of `row_emit_11264`: four per lane, sequence s from hash32(rng[0] ^ salt ^ hash32(r*128+s*32+l)) over
  * the chunks 4 j + s.  sr == 2: hardware stochastic convert (cvt.rs.satfinite.e2m1x4.f32) with this library's
- * counter-based words, key from rng[0] ^ salt and the block index r*(C/16) + block (no reference counterpart; rows
- * of at most 11776 columns).  rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0,
+ * counter-based words, key from rng[0] ^ salt and the block index r*(C/16) + block (no reference
+ * counterpart).  rng: device words (rng[0] = seed), required when sr != 0.  Requires C % 256 == 0,
  * T % 128 == 0, ldx % 8 == 0, x 16-byte aligned.  Two kernels stand behind it: rows of at most 11776 columns travel
  * as whole rows through a shared-memory ring fed by bulk copies (cp.async.bulk) and are quantized from there;
  * longer rows take a warp-per-row kernel that re-reads them through L2.  Same bytes from both.
@@ -220,7 +220,11 @@ int nvfp4_swizzle_scales(const void* s_linear, long long lds, int R, int C16, vo
  *   pa, pb    device FP32 scalars used by alpha_mode (may be null for NVFP4_ALPHA_ONE); NVFP4_ALPHA_ROW: pa = FP32 [M]
  *   accumulate  0: C = result; 1: C += result (fp32 only, atomic adds)
  *   splitk    >= 1: the K range is cut into that many slices of whole 256-element tiles, each
- *             added atomically into C; needs accumulate = 1 or C zeroed by the caller when > 1
+ *             added atomically into C; needs accumulate = 1 or C zeroed by the caller when > 1.
+ *             0 (fp32 C only; bf16 C runs unsliced): the library picks the slice count from its tile cost model --
+ *             weight-gradient shapes with few output tiles and a long K fill the SMs better in slices -- and, when it
+ *             slices a call with accumulate = 0, zero-fills C itself first.  Slices add in no fixed order, so the
+ *             last bits of C may differ from run to run, as in the reference's split-K (llm-1b/fp4k.cu:272-278)
  *   status    optional device int; a CTA whose bounded pipeline wait expires writes a non-zero
  *             code there and leaves the kernel without completing its tiles (never expected)
  * Requires M % 128 == 0, N % 128 == 0, K % 64 == 0.

@@ -24,7 +24,9 @@ __device__ __forceinline__ u32 absmax_packed(u32 m, const uint4& q) {
 }
 
 // Quantize one 8-column chunk (half a block; lane ^ 1 holds the other half) of row r.
-template <bool SR>
+// SR: 0 round to nearest, 1 the reference's dither and per-lane sequence, 2 hardware stochastic convert with the
+// library's counter-based words (the words of the TMA-fed kernel: keyed by the block, half h = lane & 1 of it).
+template <int SR>
 __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg, long long r, int col, int C,
                                            u32* __restrict__ codes, unsigned char* __restrict__ scales, int lane) {
   float v[8];
@@ -42,7 +44,7 @@ __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg
   float y[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) y[i] = __fmul_rn(v[i], k);
-  if (SR) {
+  if (SR == 1) {
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
       const u32 rnd = lcg_step(lcg);
@@ -50,7 +52,13 @@ __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg
       y[i + 1] = sr_dither11(y[i + 1], (rnd >> 5) & 0x3FF800u);
     }
   }
-  codes[(r * C + col) >> 3] = e2m1x8_rn(y);
+  if (SR == 2) {
+    // `lcg` carries seed ^ salt here
+    u32 key = sr_hw_block_key(lcg, (u32)(r * (C >> 4) + (col >> 4)));
+    codes[(r * C + col) >> 3] = round8<NVFP4_ROUND_SR_HW>(y, key, lcg, 0u, lane & 1);
+  } else {
+    codes[(r * C + col) >> 3] = e2m1x8_rn(y);
+  }
   if (!(lane & 1)) scales[sw_off(r, col >> 4, C >> 6)] = (unsigned char)sb;
 }
 
@@ -59,7 +67,7 @@ __device__ __forceinline__ void emit_chunk(const uint4& raw, float inv, u32& lcg
 // picks for 11264-column rows (`row_emit_11264` = row_reg<4, 11>, llm-1b/emit.cu:228-260, llm-1b/emit.py:64-67): four
 // sequences per lane, sequence s seeded with hash32(seed ^ salt ^ hash32(r*128 + s*32 + lane)) and walking the
 // chunks 4 j + s in order; SUBS = 1 is the generic `row_emit` sequence (one per lane, seeded with r*32 + lane).
-template <int KEEP, bool SR, int SUBS = 1>
+template <int KEEP, int SR, int SUBS = 1>
 __global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int C,
                                                         u32* __restrict__ codes, unsigned char* __restrict__ scales,
                                                         float* __restrict__ rs_out, int T, const u32* __restrict__ rng,
@@ -96,7 +104,7 @@ __global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __r
         emit_chunk<SR>(ld_chunk(row + c + sidx * 256), inv, lcg4[sidx], r, c + sidx * 256 + lane * 8, C, codes, scales, lane);
     return;
   }
-  u32 lcg = hash32(seed ^ hash32((u32)(r * 32 + lane)));
+  u32 lcg = SR == 2 ? seed : hash32(seed ^ hash32((u32)(r * 32 + lane)));
   if (KEEP > 0) {
 #pragma unroll
     for (int j = 0; j < NK; j++) emit_chunk<SR>(kept[j], inv, lcg, r, j * 256 + lane * 8, C, codes, scales, lane);
@@ -106,10 +114,11 @@ __global__ void __launch_bounds__(256) emit_rows_kernel(const __nv_bfloat16* __r
 }
 
 template <int KEEP>
-static void launch_rows(bool sr, unsigned blocks, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int C, u32* codes,
+static void launch_rows(int sr, unsigned blocks, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int C, u32* codes,
                         unsigned char* scales, float* rs, int T, const u32* rng, u32 salt) {
-  if (sr) emit_rows_kernel<KEEP, true><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
-  else emit_rows_kernel<KEEP, false><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
+  if (sr == 2) emit_rows_kernel<KEEP, 2><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
+  else if (sr) emit_rows_kernel<KEEP, 1><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
+  else emit_rows_kernel<KEEP, 0><<<blocks, 256, 0, st>>>(x, ldx, C, codes, scales, rs, T, rng, salt);
 }
 
 }  // namespace nvfp4
@@ -138,21 +147,20 @@ extern "C" int nvfp4_emit_rows(const void* x, long long ldx, int T, int C, void*
   if (T == 0 || C == 0) return NVFP4_OK;
   if (g_emit_rows_path == 0 && nvfp4_emit_rows_ring_accepts(x, ldx, T, C, codes))
     return nvfp4_emit_rows_ring_launch(x, ldx, T, C, codes, scales, rs_out, sr, rng, salt, stream);
-  if (sr == 2) return NVFP4_ERR_ENUM;      // the hardware-convert mode exists in the TMA-fed kernel only
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned blocks = (unsigned)((T + 7) / 8);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   u32* cp = static_cast<u32*>(codes);
   unsigned char* sp = static_cast<unsigned char*>(scales);
   switch (C / 256) {
-    case 8: launch_rows<8>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
-    case 12: launch_rows<12>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
-    case 22: launch_rows<22>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 8: launch_rows<8>(sr, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 12: launch_rows<12>(sr, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    case 22: launch_rows<22>(sr, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
     case 44:   // 11264 columns: the reference's launcher switches to its four-sequence kernel here
-      if (sr) emit_rows_kernel<0, true, 4><<<blocks, 256, 0, st>>>(xp, ldx, C, cp, sp, rs_out, T, rng, salt);
-      else emit_rows_kernel<0, false, 1><<<blocks, 256, 0, st>>>(xp, ldx, C, cp, sp, rs_out, T, rng, salt);
+      if (sr == 1) emit_rows_kernel<0, 1, 4><<<blocks, 256, 0, st>>>(xp, ldx, C, cp, sp, rs_out, T, rng, salt);
+      else launch_rows<0>(sr, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt);
       break;
-    default: launch_rows<0>(sr != 0, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
+    default: launch_rows<0>(sr, blocks, st, xp, ldx, C, cp, sp, rs_out, T, rng, salt); break;
   }
   NVFP4_LAUNCH_CHECK();
   return NVFP4_OK;

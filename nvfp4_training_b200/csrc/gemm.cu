@@ -891,9 +891,11 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   if (alpha_mode < NVFP4_ALPHA_ONE || alpha_mode > NVFP4_ALPHA_ROW) return NVFP4_ERR_ENUM;
   if (alpha_mode != NVFP4_ALPHA_ONE && (!pa || !pb)) return NVFP4_ERR_NULL;
   if (c_dtype != NVFP4_DTYPE_BF16 && c_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
-  if (M < 0 || N < 0 || K < 0 || (M % 128) || (N % 128) || (K % 64) || splitk < 1) return NVFP4_ERR_SHAPE;
+  if (M < 0 || N < 0 || K < 0 || (M % 128) || (N % 128) || (K % 64) || splitk < 0) return NVFP4_ERR_SHAPE;
   if (lda < K / 2 || ldb < K / 2 || ldc < N) return NVFP4_ERR_SHAPE;
   if ((accumulate || splitk > 1) && c_dtype != NVFP4_DTYPE_FP32) return NVFP4_ERR_ENUM;
+  const bool auto_split = splitk == 0;      // the library picks the number of K slices (FP32 output only)
+  if (auto_split) splitk = 1;
   if (!al16(a) || !al16(b) || !al16(sa) || !al16(sb) || !al16(c) || (lda & 15) || (ldb & 15) || (ldc & 7))
     return NVFP4_ERR_ALIGN;
   if (M == 0 || N == 0) return NVFP4_OK;
@@ -912,6 +914,31 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   if (g_sm_budget > 0 && g_sm_budget < sms) sms = g_sm_budget >= 2 ? (g_sm_budget & ~1) : 2;
 
   const int ktiles = (K + kBK - 1) / kBK;
+  if (auto_split && c_dtype == NVFP4_DTYPE_FP32 && (M % 256 == 0) && g_force_bn == 0 && ktiles >= 16) {
+    // Weight-gradient shapes have few output tiles and a long contraction: 96 or 176 tiles over 74 SM pairs leave
+    // a third of the machine idle in the last round.  Slicing K evens that out; the price is the per-tile fixed
+    // cost once more per slice, FP32 atomic adds instead of stores, and a zero fill when the call overwrites C.
+    // Same cost model as the tile-width choice below (units of about half a microsecond).
+    const long long ncl = sms / 2;
+    double best = 0;
+    for (int s = 1; s <= 8 && s <= ktiles; s++) {
+      const int per_s = (ktiles + s - 1) / s;
+      if ((ktiles + per_s - 1) / per_s != s) continue;
+      const long long t256 = (N % 256 == 0) ? (long long)(M / 256) * (N / 256) * s : 0;
+      const long long t192 = (long long)(M / 256) * ((N + 191) / 192) * s;
+      double cost = (double)((t192 + ncl - 1) / ncl) * (1.88 + 0.3255 * per_s);
+      if (t256) cost = fmin(cost, (double)((t256 + ncl - 1) / ncl) * (2.98 + 0.346 * per_s));
+      if (s > 1) {
+        cost *= 1.03;                                                           // atomics in the epilogue
+        if (!accumulate) cost += (double)M * (double)N * 4.0 / 1.4e6;           // zero fill first
+      }
+      if (s == 1 || cost < best * 0.97) { best = cost; splitk = s; }
+    }
+    if (splitk > 1 && !accumulate) {
+      if (cudaMemset2DAsync(c, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, st) != cudaSuccess) return NVFP4_ERR_CUDA;
+      accumulate = 1;
+    }
+  }
   if (splitk > ktiles) splitk = ktiles;
   int per = (ktiles + splitk - 1) / splitk;
   splitk = (ktiles + per - 1) / per;

@@ -55,7 +55,7 @@ def row_emit(x, q: RowQ, rng, sr=False, salt=0):
     """Quantize the rows of x [T, C] into q (llm-1b/emit.py:72-79).  `rng`: CUDA int32/uint32 words,
     rng[0] = stochastic-rounding seed (read on the device, so a captured graph sees fresh seeds).
     `sr`: False = round to nearest, True = the reference's mantissa dither and random sequence, "hw" = the hardware
-    stochastic convert with this library's counter-based words (an addition; rows of at most 11776 columns)."""
+    stochastic convert with this library's counter-based words (an addition)."""
     L.require_cuda(x, q.d, q.s, q.rs)
     T, C = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and C % 256 == 0
@@ -114,13 +114,13 @@ def mm(ad, as_, bd, bs, out_dtype=torch.bfloat16):
     return nvq.mm(a, b, out_dtype=out_dtype, scale=False)[0]
 
 
-def _gemm(ad, as_, bd, bs, out, alpha_mode, pa, pb, accumulate=False):
+def _gemm(ad, as_, bd, bs, out, alpha_mode, pa, pb, accumulate=False, splitk=1):
     M, N, K = ad.shape[0], bd.shape[0], ad.shape[1] * 2
     assert bd.shape[1] * 2 == K and out.shape == (M, N) and out.stride(1) == 1
     L.require_cuda(ad, bd, out)
     L.check(L.load().nvfp4_gemm(L.ptr(ad), L.ptr(as_), ad.stride(0), L.ptr(bd), L.ptr(bs), bd.stride(0), L.ptr(out),
                                 L.DTYPE_FP32 if out.dtype == torch.float32 else L.DTYPE_BF16, out.stride(0), M, N, K,
-                                alpha_mode, L.ptr(pa), L.ptr(pb), 1.0, 1.0, int(accumulate), 1,
+                                alpha_mode, L.ptr(pa), L.ptr(pb), 1.0, 1.0, int(accumulate), splitk,
                                 L.ptr(L.status_word(ad.device)), L.stream()), "gemm")
     return out
 
@@ -144,7 +144,8 @@ def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32, scale=False, amax_a=None, 
         return mm(a.d, a.s, b.d, b.s, out_dtype=out_dtype)
     if out is None:
         out = torch.empty(a.d.shape[0], b.d.shape[0], dtype=out_dtype, device=a.d.device)
-    return _gemm(a.d, a.s, b.d, b.s, out, L.ALPHA_AMAX, amax_a, amax_b, accumulate)
+    return _gemm(a.d, a.s, b.d, b.s, out, L.ALPHA_AMAX, amax_a, amax_b, accumulate,
+                 splitk=0 if out.dtype == torch.float32 else 1)
 
 
 def mm_row_w(q: RowQ, w: WQ, scale=False):

@@ -2,9 +2,12 @@
 quantizers with row-major `[R, C/16]` scales, FP32 weights, and `gemm` with bf16 output or FP32
 split-K accumulation, on the sm_100a C-ABI library.
 
-The tensor-core path consumes swizzled scales, so `gemm` first rewrites both operands' scales into
-a scratch buffer it allocates with torch (the C entry point takes it as `workspace`).
+The tensor-core path consumes swizzled scales, so `gemm` first rewrites the operands' scales into
+a scratch buffer it allocates with torch (the C entry point takes it as `workspace`).  An operand whose
+swizzled scales are already known (`Q.sw`, kept by `fp4torch.FP4Weight` for the weights) skips that step.
 """
+import weakref
+
 import torch
 
 from . import _lib as L
@@ -16,10 +19,44 @@ SR_MODE = L.ROUND_SR_DITHER_K
 class Q:
     """Packed NVFP4 tensor: data [R, C/2] uint8, scales [R, C/16] uint8, amax (device scalar),
     k (extra scale) (llm-1b/fp4ops.py:18-23)."""
-    __slots__ = ("d", "s", "amax", "k")
+    __slots__ = ("d", "s", "amax", "k", "sw")
 
-    def __init__(self, d, s, amax, k=1.0):
+    def __init__(self, d, s, amax, k=1.0, sw=None):
         self.d, self.s, self.amax, self.k = d, s, amax, k
+        self.sw = sw        # optional: the same scales in the 128x4-tile swizzled layout (an addition of this library)
+
+
+def swizzle_scales(s, out=None):
+    """Row-major scales [R, C/16] (row stride honoured) -> the swizzled layout the tensor core reads, flat uint8."""
+    R, C16 = s.shape
+    assert R % 128 == 0 and C16 % 4 == 0, (R, C16)
+    if out is None:
+        out = torch.empty(R * C16, dtype=torch.uint8, device=s.device)
+    L.check(L.load().nvfp4_swizzle_scales(L.ptr(s), s.stride(0), R, C16, L.ptr(out), L.stream()), "swizzle_scales")
+    return out
+
+
+# Swizzled scale copies of long-lived operands (weights), found by the address of their row-major scales: the
+# torch custom ops of fp4torch receive plain tensors, not Q objects.  An entry is valid while the tensor it was
+# made from is alive (its memory cannot have been reused) and is rewritten by whoever rewrites that tensor.
+_SW_CACHE = {}
+
+
+def remember_swizzled(s, sw):
+    _SW_CACHE[s.data_ptr()] = (weakref.ref(s), sw)
+    if len(_SW_CACHE) > 4096:
+        for k in [k for k, (r, _) in _SW_CACHE.items() if r() is None]:
+            del _SW_CACHE[k]
+
+
+def swizzled_of(s):
+    e = _SW_CACHE.get(s.data_ptr())
+    if e is None:
+        return None
+    t = e[0]()
+    if t is None or t.data_ptr() != s.data_ptr() or t.shape != s.shape or t.stride() != s.stride():
+        return None
+    return e[1]
 
 
 def amax_of(x):
@@ -97,6 +134,9 @@ def quant_w2d(w, out=None):
     qw.amax.copy_(amax_of(w))
     L.check(L.load().nvfp4_quant_w2d(L.ptr(w.contiguous()), L.DTYPE_FP32, N, K, L.ptr(qw.d), L.ptr(qw.s), L.ptr(qwt.d),
                                      L.ptr(qwt.s), L.SCALES_LINEAR, L.ptr(qw.amax), None, L.stream()), "quant_w2d")
+    for q in (qw, qwt):
+        if q.sw is not None:        # a rewritten pair keeps its swizzled scale copies in step
+            swizzle_scales(q.s, out=q.sw)
     return qw, qwt
 
 
@@ -115,11 +155,23 @@ def gemm(a: Q, b: Q, out=None, splitk=1):
         assert out.dtype == torch.float32 and out.stride(1) == 1
         acc, cdt = 1, L.DTYPE_FP32
     lib = L.load()
-    ws = torch.empty(lib.nvfp4_gemm_linear_workspace_bytes(M, N, K), dtype=torch.uint8, device=a.d.device)
-    L.check(lib.nvfp4_gemm_linear(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), a.s.stride(0), L.ptr(b.d), L.ptr(b.s),
-                                  b.d.stride(0), b.s.stride(0), L.ptr(out), cdt, out.stride(0), M, N, K, L.ALPHA_AMAX,
-                                  L.ptr(a.amax), L.ptr(b.amax), float(a.k), float(b.k), acc, splitk, L.ptr(ws),
-                                  ws.numel(), L.ptr(L.status_word(a.d.device)), L.stream()), "gemm")
+    sw_a = a.sw if a.sw is not None else swizzled_of(a.s)
+    sw_b = b.sw if b.sw is not None else swizzled_of(b.s)
+    if sw_a is None and sw_b is None:
+        ws = torch.empty(lib.nvfp4_gemm_linear_workspace_bytes(M, N, K), dtype=torch.uint8, device=a.d.device)
+        L.check(lib.nvfp4_gemm_linear(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), a.s.stride(0), L.ptr(b.d), L.ptr(b.s),
+                                      b.d.stride(0), b.s.stride(0), L.ptr(out), cdt, out.stride(0), M, N, K, L.ALPHA_AMAX,
+                                      L.ptr(a.amax), L.ptr(b.amax), float(a.k), float(b.k), acc, splitk, L.ptr(ws),
+                                      ws.numel(), L.ptr(L.status_word(a.d.device)), L.stream()), "gemm")
+        return out
+    # at least one operand brings its swizzled scales: swizzle the other and call the swizzled-scale GEMM
+    if sw_a is None:
+        sw_a = swizzle_scales(a.s)
+    if sw_b is None:
+        sw_b = swizzle_scales(b.s)
+    L.check(lib.nvfp4_gemm(L.ptr(a.d), L.ptr(sw_a), a.d.stride(0), L.ptr(b.d), L.ptr(sw_b), b.d.stride(0), L.ptr(out), cdt,
+                           out.stride(0), M, N, K, L.ALPHA_AMAX, L.ptr(a.amax), L.ptr(b.amax), float(a.k), float(b.k), acc,
+                           splitk, L.ptr(L.status_word(a.d.device)), L.stream()), "gemm")
     return out
 
 

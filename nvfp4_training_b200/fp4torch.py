@@ -92,4 +92,11 @@ class FP4Weight:
         self._q = F.quant_w2d(self.w.data, out=self._q)      # in place after the first call
         qw, qwt = self._q
         self.wd, self.ws, self.wtd, self.wts, self.amax = qw.d, qw.s, qwt.d, qwt.s, qw.amax
+        # the tensor core reads swizzled scales: keep those of the weight (they change only here), so that each
+        # GEMM swizzles just its activation operand
+        N, K = self.w.shape
+        if qw.sw is None and N % 128 == 0 and K % 128 == 0:     # later refreshes rewrite them inside quant_w2d
+            qw.sw, qwt.sw = F.swizzle_scales(qw.s), F.swizzle_scales(qwt.s)
+            F.remember_swizzled(qw.s, qw.sw)
+            F.remember_swizzled(qwt.s, qwt.sw)
         return self

@@ -64,14 +64,18 @@ def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS):
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None, overwrite=False, qxt=None, am_gy=None):
+               sr_mode=None, overwrite=False, qxt=None, am_gy=None, wgrad_stream=None, keep_alive=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
     returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
     rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding.
     `qxt`: the transposed operand of x from `linear_fwd(..., keep_xt=True)`; x may then be None.
-    `am_gy`: amax(gy) if the caller already has it."""
+    `am_gy`: amax(gy) if the caller already has it.
+    `wgrad_stream`: the weight-gradient GEMM is off the backward's critical chain (nothing downstream reads dW before
+    the optimizer), so it may run on this side stream beside the dgrad GEMM and whatever follows it: its CTAs fill
+    the SMs the other kernels' last waves leave idle.  The caller joins the stream before it reads `gw_out` and
+    passes a list as `keep_alive`, which receives the operands the side stream still reads (drop them after the join)."""
     gy = gy.contiguous()
     ag = am_gy if am_gy is not None else nvq.amax(gy)
     if _tileable(gy):
@@ -80,13 +84,23 @@ def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch
     else:
         qg = nvq.quant_rows(gy, sr=True, seed=seed, am=ag, sr_mode=sr_mode)
         qgt = nvq.quant_cols_rht(gy, signs, sr=True, seed=seed_cols, am=ag, sr_mode=sr_mode)
+    side = wgrad_stream if (gw_out is not None and wgrad_stream is not None) else None
+    if side is not None:
+        # the side stream starts from the quantized operands, not from the dgrad GEMM enqueued next
+        if qxt is None:
+            qxt = nvq.quant_cols_rht(x, signs, am=am_x)
+        side.wait_stream(torch.cuda.current_stream())
     # dgrad: gx = gy @ w     (quantized along N; W^T uses the same 2D-block values)
     gx = nvq.mm(qg, qwt)
     # wgrad: gw = gy^T @ x   (both quantized along tokens, after a 16-pt RHT)
     if qxt is None:
         qxt = nvq.quant_cols_rht(x, signs, am=am_x)
-    if gw_out is not None:
-        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite)
+    if side is not None:
+        with torch.cuda.stream(side):
+            gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0)
+        keep_alive.append((qgt, qxt))
+    elif gw_out is not None:
+        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0)
     else:
         gw = nvq.mm(qgt, qxt, out_dtype=wgrad_dtype)
     return gx, gw

@@ -162,9 +162,10 @@ def quant_w2d(w, am=None, want=(True, True), out=None):
     return (Q(q, s, g) if want[0] else None, Q(qt, st, g) if want[1] else None)
 
 
-def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False):
+def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False, splitk=1):
     """a [M,K], b [N,K] (both K-major) -> a @ b^T [M, N].  If scale=False returns (raw, alpha)
-    (llm-1b/nvq.py:90-96).  `out` / `accumulate` (fp32 only) are additions for in-place wgrad."""
+    (llm-1b/nvq.py:90-96).  `out` / `accumulate` (fp32 only) are additions for in-place wgrad; `splitk=0` (fp32 only)
+    lets the library slice a long contraction over the SMs (sums then land in no fixed order)."""
     M, N, K = a.d.shape[0], b.d.shape[0], a.d.shape[1] * 2
     assert b.d.shape[1] * 2 == K, (a.d.shape, b.d.shape)
     assert out_dtype in (torch.bfloat16, torch.float32)
@@ -178,7 +179,8 @@ def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=Fa
                                 L.ptr(out), L.DTYPE_FP32 if out_dtype == torch.float32 else L.DTYPE_BF16,
                                 out.stride(0), M, N, K, L.ALPHA_GS if scale else L.ALPHA_ONE,
                                 L.ptr(a.gs) if scale else None, L.ptr(b.gs) if scale else None, 1.0, 1.0,
-                                int(accumulate), 1, L.ptr(L.status_word(a.d.device)), L.stream()), "mm")
+                                int(accumulate), splitk if out_dtype == torch.float32 else 1,
+                                L.ptr(L.status_word(a.d.device)), L.stream()), "mm")
     if not scale:
         return out, a.gs * b.gs
     return out

@@ -89,7 +89,7 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor"):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor", wgrad_side_stream=True):
         """`seed` initialises the weights (the same on every rank of a data-parallel job: replicated
         weights), `input_seed` the synthetic activation / gradient pools (different per rank: each rank
         holds its own rows of the batch; default seed + 1000).
@@ -99,6 +99,9 @@ class LinearStack:
         GEMM epilogue."""
         assert mode in ("tensor", "emit")
         self.mode = mode
+        # weight-gradient GEMMs run on a side stream, joined at the end of each block's backward: they are off the
+        # critical chain amax -> quantize -> dgrad, and fill the SMs that chain's kernels leave idle in their last waves
+        self.wgrad_stream = torch.cuda.Stream(device=device) if wgrad_side_stream else None
         # emitter mode rounds gradients with the hardware convert ("hw"); True selects the reference's dither sequences
         self.emit_sr = "hw" if sr_mode == _lib.ROUND_SR_HW else True
         self.comm_sms = comm_sms     # SMs left to NCCL while backward GEMMs and the all-reduce overlap
@@ -216,15 +219,25 @@ class LinearStack:
 
     def _bwd_block_emit(self, projs, keep=False, first=False):
         T = self.T
+        alive = []          # operands the side stream still reads
         for p in reversed(projs):
             gy = self.gy_pool[p.name]
             use_x, use_g = self.amax_use[p.lid, 0:1], self.amax_use[p.lid, 1:2]
             rq = emit.row_emit(gy, emit.RowQ(T, p.N, self.device), self.rng, sr=self.emit_sr, salt=p.lid * 8 + 1)
             cg = emit.col_emit(gy, emit.ColQ(T, p.N, self.device), use_g, self.amax_cur[p.lid, 1:2], self.rng, sr=self.emit_sr,
                                salt=p.lid * 8 + 2)
+            if self.wgrad_stream is not None:
+                self.wgrad_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.wgrad_stream):
+                    emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
+                alive.append(cg)
             gx = emit.mm_row_wt(rq, p.wq, scale=True)
-            emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
+            if self.wgrad_stream is None:
+                emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
             p.gx = gx if keep else None
+        if self.wgrad_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.wgrad_stream)
+        del alive
 
     def _fwd_block(self, projs, keep=False):
         if self.mode == "emit":
@@ -238,11 +251,16 @@ class LinearStack:
         gradients need no clearing pass."""
         if self.mode == "emit":
             return self._bwd_block_emit(projs, keep, first)
+        alive = []
         for p in reversed(projs):
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(None, p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
-                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt)
+                               gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt,
+                               wgrad_stream=self.wgrad_stream, keep_alive=alive)
             p.gx = gx if keep else None
+        if self.wgrad_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.wgrad_stream)
+        del alive
 
     def calibrate(self):
         """Emitter mode: two passes over all projections so that the delayed column scales come from observed

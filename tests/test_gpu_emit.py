@@ -300,3 +300,25 @@ def test_row_emit_ring_many_rows_per_cta_and_hardware_sr():
     e_sr = ((acc / 64 - gf).norm() / gf.norm()).item()
     assert e_sr <= 0.25 * e_rn, (e_sr, e_rn)
     _lib.check_status()
+
+
+def test_row_emit_hardware_sr_warp_per_row_and_long_rows():
+    """The hardware stochastic-rounding mode through the warp-per-row kernel: forced on a shape the ring kernel also
+    takes (same bytes from both), and on rows longer than the ring holds (the LM head's output gradient has 49152
+    columns)."""
+    from nvfp4_training_b200 import _lib, emit
+    lib = _lib.load()
+    rng = torch.tensor([41, 0], dtype=torch.int32, device="cuda")
+    g = make_dy(6, 256, 5632)
+    want = O.emit_rows(g, seed=41, sr="hw", salt=3)
+    try:
+        for path in (1, 0):
+            assert lib.nvfp4_emit_rows_set_path(path) == 0
+            q = emit.row_emit(to_dev(g), emit.RowQ(256, 5632), rng, sr="hw", salt=3)
+            _check(q, want, 256, 5632)
+    finally:
+        lib.nvfp4_emit_rows_set_path(0)
+    g = make_dy(7, 128, 49152)
+    q = emit.row_emit(to_dev(g), emit.RowQ(128, 49152), rng, sr="hw", salt=9)
+    _check(q, O.emit_rows(g, seed=41, sr="hw", salt=9), 128, 49152)
+    _lib.check_status()

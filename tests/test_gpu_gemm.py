@@ -132,6 +132,25 @@ def test_pair_kernel_splitk(mods, splitk):
     L.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 8192), (768, 512, 4096), (512, 384, 16384)])
+def test_mm_library_chosen_splitk(mods, M, N, K):
+    """splitk = 0: few output tiles and a long contraction, so the library slices K; overwrite (it zero-fills the
+    output itself, here pre-filled with garbage) and accumulate (adds to what is there)."""
+    nvq, _, L = mods
+    qa = nvq.quant_rows(to_dev(make_x(M + K, M, K)))
+    qb = nvq.quant_rows(to_dev(make_w(N, N, K)))
+    y = ref_product(qa, qb, nvq)
+    out = torch.full((M, N), 7.0, device="cuda")
+    nvq.mm(qa, qb, out_dtype=torch.float32, out=out, splitk=0)
+    check_close(out, y, bf16=False)
+    out.fill_(1.0)
+    nvq.mm(qa, qb, out_dtype=torch.float32, out=out, accumulate=True, splitk=0)
+    nvq.mm(qa, qb, out_dtype=torch.float32, out=out, accumulate=True, splitk=0)
+    check_close(out, 2 * y + 1, bf16=False)
+    check_close(nvq.mm(qa, qb, splitk=0), y, bf16=True)       # bf16 output: never sliced
+    L.check_status()
+
+
 @pytest.mark.parametrize("splitk", [1, 3, 16])
 def test_fp4ops_gemm_splitk_and_strides(mods, splitk):
     """small-model/test_fp4ops.py:23-37 and bench_wgrad.py: linear scales, strided d/s views,

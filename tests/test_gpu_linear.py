@@ -74,3 +74,30 @@ def test_fp4torch_custom_op_linear():
     assert ((w.grad - ex_dw).norm() / ex_dw.norm()).item() < 0.25
     fw.refresh()
     _lib.check_status()
+
+
+def test_fp4weight_keeps_swizzled_scales():
+    """FP4Weight holds the swizzled form of its scales and `fp4ops.gemm` finds it by the address of the row-major
+    scales the custom ops pass: same bytes out as the path that swizzles both operands per call, also after a
+    refresh with new weight values (the copies are rewritten with the weight)."""
+    from nvfp4_training_b200 import _lib, fp4ops, fp4torch
+    torch.manual_seed(3)
+    T, K, N = 256, 256, 384
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda") / K ** 0.5
+    fw = fp4torch.FP4Weight(w)
+    for rnd in range(2):
+        assert fp4ops.swizzled_of(fw.ws) is not None and fp4ops.swizzled_of(fw.wts) is not None
+        assert torch.equal(fp4ops.swizzled_of(fw.ws), fp4ops.swizzle_scales(fw.ws))
+        assert torch.equal(fp4ops.swizzled_of(fw.wts), fp4ops.swizzle_scales(fw.wts))
+        y = torch.ops.nvfp4.fwd(x, fw.wd, fw.ws, fw.amax)
+        # the same operands through copies nobody has registered: both scales swizzled inside the call
+        y_plain = fp4ops.gemm(fp4ops.quant_rows(x), fp4ops.Q(fw.wd.clone(), fw.ws.clone(), fw.amax))
+        assert torch.equal(y, y_plain)
+        g = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+        qg = fp4ops.quant_rows(g)
+        dx = fp4ops.gemm(qg, fp4ops.Q(fw.wtd, fw.wts, fw.amax))
+        assert torch.equal(dx, fp4ops.gemm(qg, fp4ops.Q(fw.wtd.clone(), fw.wts.clone(), fw.amax)))
+        w.mul_(1.7).add_(torch.randn_like(w) * 0.01)
+        fw.refresh()
+    _lib.check_status()
