@@ -608,7 +608,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}: launch with torch.distributed.run"
     torch.cuda.set_device(local)
-    _lib.load()
+    _lib.load().nvfp4_set_pdl(1 if args.pdl else 0)
     if args.comm_sms is None:
         # measured on 8 B200s: 34.4 ms per step with 16 SMs left to NCCL, 32.0 with 32, 31.7 with 48, 46.8 with 8;
         # with fewer ranks the collective is smaller next to the compute and the GEMMs keep more SMs
@@ -890,6 +890,7 @@ def main():
                     help="SMs left free for NCCL during backward when N > 1 (default: 32 at N >= 8, else 16)")
     ap.add_argument("--no-wgrad-stream", action="store_true",
                     help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")
+    ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch of the library's kernels (off by default)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--skip-isolated", action="store_true",
                     help="skip the isolated-kernel legs, the configuration sweeps and the communication breakdown (for profiler runs)")

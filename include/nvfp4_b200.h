@@ -74,6 +74,22 @@ const char* nvfp4_error_string(int status);
 int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream);
 
 /*
+ * out[0] = max(out[0], max|x|): nvfp4_amax_bf16 without the clearing of out[0], for callers that clear a batch of
+ * amax words with one fill (out[0] must hold a non-negative finite value or +0).  No reference counterpart.  Without
+ * the fill the amax kernel follows the previous kernel of the stream directly (one graph node less per call).
+ */
+int nvfp4_amax_bf16_update(const void* x, long long n, float* out, void* stream);
+
+/*
+ * Programmatic dependent launch of this library's amax, one-read quantizer and GEMM kernels: when on, such a kernel
+ * may become resident and run its set-up (barriers, tensor-memory allocation, constant tables) while the previous
+ * kernel of the stream drains; it waits for that kernel's completion before it touches global memory, and reads
+ * global memory past L1 only.  Off by default (measured gain on the 81-linear step: 0.2-0.6 %); the environment
+ * variable NVFP4_PDL=1 or this call switch it on.  Process-wide; no reference counterpart.
+ */
+int nvfp4_set_pdl(int on);
+
+/*
  * 1x16 block quantization of x [R, C] bf16 (row stride ldx elements) along C.
  * Replaces kernel `quant_rows` (llm-1b/nvq.cu:93-116, llm-1b/fp4k.cu:66-87) and launchers
  * `nvq.quant_rows` (llm-1b/nvq.py:47-57), `fp4ops.quant_rows` (llm-1b/fp4ops.py:30-38).

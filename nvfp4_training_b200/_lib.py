@@ -25,6 +25,8 @@ SIGNATURES = {
     "nvfp4_version": (_i, []),
     "nvfp4_error_string": (_c.c_char_p, [_i]),
     "nvfp4_amax_bf16": (_i, [_vp, _ll, _vp, _vp]),
+    "nvfp4_amax_bf16_update": (_i, [_vp, _ll, _vp, _vp]),
+    "nvfp4_set_pdl": (_i, [_i]),
     "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp, _vp]),
     "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp, _vp]),
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),

@@ -17,7 +17,45 @@ typedef uint64_t u64;
     }                                                          \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through launch_kernel() may become resident while the kernel
+// before it in the stream still runs: its prologue (barrier set-up, tensor-memory allocation, constant tables) then
+// overlaps the predecessor's last wave, and the launch latency disappears.  The contract every kernel launched this
+// way keeps: pdl_trigger() first thing (its own successor may be staged), and pdl_wait() executed by every thread
+// before the first access to global memory -- it returns once all earlier kernels of the stream have completed and
+// their writes are visible.  Both are no-ops in a kernel launched the ordinary way.  Such a kernel also reads global
+// memory only past the L1 cache (ld.global.cg, TMA, atomics): it is launched, and its SM's L1 invalidated, while
+// older kernels still run, so a line one of them reads afterwards (say a scale word at an address the allocator
+// hands out again) would otherwise still sit in L1, stale, when the staged kernel gets to read the new value.
+bool nvfp4_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t nvfp4_launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = nvfp4_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 namespace nvfp4 {
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// loads served by L2 (see above)
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ u32 ld_cg_u32(const u32* p) {
+  u32 v;
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
 
 constexpr float kFp4E4m3 = 2688.0f;   // 6 * 448
 constexpr float kTiny = 1e-30f;

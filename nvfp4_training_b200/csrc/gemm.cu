@@ -148,6 +148,7 @@ template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   using C = Cfg<BN>;
+  pdl_trigger();
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -181,6 +182,7 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const u32 tmem_base = *tmem_slot;
+  pdl_wait();         // operands, scales and alpha words are earlier kernels' results; C may still be read by them
 
   // The two issuing warps run their loops with all 32 lanes converged, so that loop state,
   // addresses and descriptors stay warp-uniform (the asynchronous-copy and tensor-core instructions
@@ -319,9 +321,9 @@ gemm_nvf4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
       const long long row = (long long)mt * kBM + quad * 32 + lane;
       float alpha = 1.f;
-      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
-      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
-      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = __ldg(p.pa + row) * __ldg(p.pb);   // this lane's row
+      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = ld_cg_f32(p.pa) * ld_cg_f32(p.pb);
+      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = ld_cg_f32(p.pa) * ld_cg_f32(p.pb) * p.kscale;
+      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = ld_cg_f32(p.pa + row) * ld_cg_f32(p.pb);   // this lane's row
       const long long col = (long long)nt * BN + half * kEpiCols;
       if (p.c_fp32) {
         float* dst = static_cast<float*>(p.c) + row * p.ldc + col;
@@ -581,6 +583,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                       const PairParams p) {
   using C = PairCfg<BN>;
   constexpr int kStages = C::kStages;
+  pdl_trigger();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* staging = smem + kStages * C::kStageBytes;
@@ -617,6 +620,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   cluster_sync_all();                                 // barriers of both CTAs exist before anyone signals them
   tc_fence_after();
   const u32 tmem_base = *tmem_slot;
+  pdl_wait();         // operands, scales and alpha words are earlier kernels' results; C may still be read by them
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -789,9 +793,9 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
       const long long row0 = (long long)mt * 256 + rank * 128 + quad * 32;      // first row of this warp
       float alpha = 1.f;
-      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = __ldg(p.pa) * __ldg(p.pb);
-      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = __ldg(p.pa) * __ldg(p.pb) * p.kscale;
-      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = __ldg(p.pa + row0 + lane) * __ldg(p.pb);   // each lane stages its own row
+      if (p.alpha_mode == NVFP4_ALPHA_GS) alpha = ld_cg_f32(p.pa) * ld_cg_f32(p.pb);
+      else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = ld_cg_f32(p.pa) * ld_cg_f32(p.pb) * p.kscale;
+      else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = ld_cg_f32(p.pa + row0 + lane) * ld_cg_f32(p.pb);   // each lane stages its own row
       const long long col0 = (long long)nt * BN + half * NC;
       void* cbase = p.c_fp32 ? static_cast<void*>(static_cast<float*>(p.c) + row0 * p.ldc + col0)
                              : static_cast<void*>(static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0);
@@ -873,8 +877,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   }
   const long long work = (long long)(p.M / kBM) * (p.N / BN) * p.splitk;
   const unsigned grid = (unsigned)(work < sms ? work : sms);
-  gemm_nvf4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(ma, mb, p);
-  NVFP4_LAUNCH_CHECK();
+  if (nvfp4_launch_kernel(gemm_nvf4_kernel<BN>, dim3(grid), dim3(kThreads), C::kSmemBytes, st, ma, mb, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NVFP4_ERR_CUDA;
+  }
   return NVFP4_OK;
 }
 
@@ -991,7 +997,11 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
           return NVFP4_ERR_CUDA;                                                                                           \
         di->FLAG = true;                                                                                                   \
       }                                                                                                                    \
-      gemm_nvf4_pair_kernel<BN_><<<grid, kThreads, PairCfg<BN_>::kSmemBytes, st>>>(ma, mb, msa, msb, pp);                  \
+      if (nvfp4_launch_kernel(gemm_nvf4_pair_kernel<BN_>, dim3(grid), dim3(kThreads), PairCfg<BN_>::kSmemBytes, st, ma, mb,    \
+                              msa, msb, pp) != cudaSuccess) {                                                               \
+        (void)cudaGetLastError();                                                                                          \
+        return NVFP4_ERR_CUDA;                                                                                             \
+      }                                                                                                                    \
     }
     if (pbn == 256) NVFP4_LAUNCH_PAIR(256, attr_pair)
     else if (pbn == 192) NVFP4_LAUNCH_PAIR(192, attr_pair192)

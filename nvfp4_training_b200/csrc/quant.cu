@@ -1,6 +1,8 @@
 // NVFP4 quantizer kernels for sm_100a: per-tensor amax, 1x16 row quantizer, transposed
 // RHT16 quantizer, 16x16 weight quantizer (W and W^T), scale re-swizzle.  All HBM-bound:
 // 128-bit coalesced loads, register-resident blocks, warp shuffles for exchanges/reductions.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace nvfp4 {
@@ -23,14 +25,22 @@ __device__ __forceinline__ uint4 ldg128(const void* p) {
 
 // ------------------------------------------------------------------------------------------ amax
 // max|x| via atomicMax on the float bit pattern (non-negative floats order like unsigned ints).
+__device__ __forceinline__ uint4 ld_cg_128(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, long long n8, float* out) {
+  pdl_trigger();
+  pdl_wait();
   u32 m = 0u;  // running max of |x| as bf16 bit patterns in both halves of a word
   const long long stride = (long long)gridDim.x * blockDim.x;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < n8; i += 4 * stride) {
     uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) v[j] = ldg128(x + i + j * stride);
+    for (int j = 0; j < 4; j++) v[j] = ld_cg_128(x + i + j * stride);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       m = __vmaxu2(m, v[j].x & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].y & 0x7FFF7FFFu);
@@ -38,7 +48,7 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
     }
   }
   for (; i < n8; i += stride) {
-    uint4 v = ldg128(x + i);
+    uint4 v = ld_cg_128(x + i);
     m = __vmaxu2(m, v.x & 0x7FFF7FFFu); m = __vmaxu2(m, v.y & 0x7FFF7FFFu);
     m = __vmaxu2(m, v.z & 0x7FFF7FFFu); m = __vmaxu2(m, v.w & 0x7FFF7FFFu);
   }
@@ -326,22 +336,45 @@ static int sm_count() {
 
 using namespace nvfp4;
 
+static int g_pdl = -1;      // -1: not decided yet (environment NVFP4_PDL=1 switches it on), else 0 / 1
+bool nvfp4_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("NVFP4_PDL");
+    g_pdl = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pdl != 0;
+}
+extern "C" int nvfp4_set_pdl(int on) {
+  g_pdl = on ? 1 : 0;
+  return NVFP4_OK;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-extern "C" int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream) {
+static int amax_launch(const void* x, long long n, float* out, bool clear, void* stream) {
   if (!out || (!x && n > 0)) return NVFP4_ERR_NULL;
   if (n < 0 || (n & 7)) return NVFP4_ERR_SHAPE;
   if (!aligned16(x)) return NVFP4_ERR_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(out, 0, sizeof(float), st) != cudaSuccess) return NVFP4_ERR_CUDA;
+  if (clear && cudaMemsetAsync(out, 0, sizeof(float), st) != cudaSuccess) return NVFP4_ERR_CUDA;
   if (n == 0) return NVFP4_OK;
   const long long n8 = n >> 3;
   long long blocks = (n8 + 256 * 4 - 1) / (256 * 4);
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  amax_bf16_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const uint4*>(x), n8, out);
-  NVFP4_LAUNCH_CHECK();
+  if (nvfp4_launch_kernel(amax_bf16_kernel, dim3((unsigned)blocks), dim3(256), 0, st, static_cast<const uint4*>(x), n8, out) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NVFP4_ERR_CUDA;
+  }
   return NVFP4_OK;
+}
+
+extern "C" int nvfp4_amax_bf16(const void* x, long long n, float* out, void* stream) {
+  return amax_launch(x, n, out, true, stream);
+}
+
+extern "C" int nvfp4_amax_bf16_update(const void* x, long long n, float* out, void* stream) {
+  return amax_launch(x, n, out, false, stream);
 }
 
 extern "C" int nvfp4_quant_rows(const void* x, long long ldx, int R, int C, void* codes, void* scales,

@@ -166,6 +166,7 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const u32 tiles0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const u32 i16_s = tiles0 + kQStages * kQTileBytes;            // 16 rows x 128 B, then padding to 1024
@@ -214,7 +215,9 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     q_tmem_alloc(smem_u32(&tmem_slot), kQTmemCols);
     q_tmem_relinquish();
   }
-  const float amax = __ldg(p.amax);
+  // everything above touches shared and tensor memory only; the tensor's amax is the previous kernel's result
+  pdl_wait();
+  const float amax = ld_cg_f32(p.amax);
   const bool first = blockIdx.x == 0 && threadIdx.x == 0;
   TensorScale ts_r, ts_c;
   if (ROWS) ts_r = make_tensor_scale<ROUNDING>(amax, 1.f, lut_r, first ? p.gs_r_out : nullptr);
@@ -314,8 +317,8 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
     const int half = (warp - 1) >> 2;               // columns 64 * half .. + 63 of a buffer
     u32 seed_r = p.seed_r, seed_c = p.seed_c;
     if (ROUNDING != NVFP4_ROUND_NEAREST) {
-      if (p.seed_r_dev) seed_r = __ldg(p.seed_r_dev);
-      if (p.seed_c_dev) seed_c = __ldg(p.seed_c_dev);
+      if (p.seed_r_dev) seed_r = ld_cg_u32(p.seed_r_dev);
+      if (p.seed_c_dev) seed_c = ld_cg_u32(p.seed_c_dev);
     }
     const int nblk = p.C >> 4;                      // 16-column blocks per row
     const int nmb = p.M >> 4;                       // 16-token blocks per column
@@ -480,8 +483,10 @@ static int launch_tc(const CUtensorMap& map, const TcParams& p, int grid, cudaSt
       return NVFP4_ERR_CUDA;
     configured[dev] = true;
   }
-  quant_tc_kernel<ROUNDING, ROWS, COLS, TCRHT><<<grid, kQThreads, kQSmem, st>>>(map, p);
-  NVFP4_LAUNCH_CHECK();
+  if (nvfp4_launch_kernel(quant_tc_kernel<ROUNDING, ROWS, COLS, TCRHT>, dim3((unsigned)grid), dim3(kQThreads), kQSmem, st, map, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NVFP4_ERR_CUDA;
+  }
   return NVFP4_OK;
 }
 

@@ -49,13 +49,14 @@ def _tileable(t):
     return t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0
 
 
-def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS):
+def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS, am_out=None):
     """fprop of llm-1b/model.py:46-53 with W already quantized: returns (y bf16 [T, N], amax(x)).
     amax(x) is handed back so the backward pass does not recompute it (same value).  With
     `keep_xt` the transposed RHT operand of x that wgrad needs (llm-1b/model.py:66) is produced in
     the same pass over x and returned as a third value, so the backward pass neither re-reads nor
-    has to keep x."""
-    am = nvq.amax(x.contiguous())
+    has to keep x.  `am_out`: a zeroed device word that receives amax(x) (callers that clear many such words with
+    one fill save a fill per call)."""
+    am = nvq.amax(x.contiguous()) if am_out is None else nvq.amax(x.contiguous(), out=am_out, clear=False)
     if keep_xt and _tileable(x):
         qx, qxt = nvq.quant_rows_cols_rht(x, signs, am=am)
         return nvq.mm(qx, qw), am, qxt
@@ -64,20 +65,20 @@ def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS):
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None, overwrite=False, qxt=None, am_gy=None, wgrad_stream=None, keep_alive=None):
+               sr_mode=None, overwrite=False, qxt=None, am_gy=None, wgrad_stream=None, keep_alive=None, am_out=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
     returned; otherwise a new tensor of `wgrad_dtype` is returned.  `sr_mode` picks the stochastic
     rounding (default: the module default of `nvq`); `overwrite` stores into `gw_out` instead of adding.
     `qxt`: the transposed operand of x from `linear_fwd(..., keep_xt=True)`; x may then be None.
-    `am_gy`: amax(gy) if the caller already has it.
+    `am_gy`: amax(gy) if the caller already has it; `am_out`: else a zeroed device word to compute it into.
     `wgrad_stream`: the weight-gradient GEMM is off the backward's critical chain (nothing downstream reads dW before
     the optimizer), so it may run on this side stream beside the dgrad GEMM and whatever follows it: its CTAs fill
     the SMs the other kernels' last waves leave idle.  The caller joins the stream before it reads `gw_out` and
     passes a list as `keep_alive`, which receives the operands the side stream still reads (drop them after the join)."""
     gy = gy.contiguous()
-    ag = am_gy if am_gy is not None else nvq.amax(gy)
+    ag = am_gy if am_gy is not None else (nvq.amax(gy) if am_out is None else nvq.amax(gy, out=am_out, clear=False))
     if _tileable(gy):
         # both operands of gy from one pass over it
         qg, qgt = nvq.quant_rows_cols_rht(gy, signs, sr=True, seed=seed, seed_cols=seed_cols, am=ag, sr_mode=sr_mode)

@@ -28,14 +28,17 @@ class Q:
         self.d, self.s, self.gs = d, s, gs
 
 
-def amax(x, out=None):
-    """max|x| of a contiguous bf16 tensor as a device fp32 [1] (llm-1b/nvq.py:32-40)."""
+def amax(x, out=None, clear=True):
+    """max|x| of a contiguous bf16 tensor as a device fp32 [1] (llm-1b/nvq.py:32-40).  `clear=False` (an addition):
+    `out` is a word the caller has zeroed, e.g. one of a batch cleared with a single fill, and is only raised."""
     L.require_cuda(x, out)
     if out is None:
+        assert clear
         out = torch.empty(1, dtype=torch.float32, device=x.device)
     n = x.numel()
     assert n % 8 == 0 and x.is_contiguous() and x.dtype == torch.bfloat16
-    L.check(L.load().nvfp4_amax_bf16(L.ptr(x), n, L.ptr(out), L.stream()), "amax")
+    fn = L.load().nvfp4_amax_bf16 if clear else L.load().nvfp4_amax_bf16_update
+    L.check(fn(L.ptr(x), n, L.ptr(out), L.stream()), "amax")
     return out
 
 

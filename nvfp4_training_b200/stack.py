@@ -123,6 +123,8 @@ class LinearStack:
             self.blocks.append([self._make_proj("head", cfg.vocab, cfg.d, 0.02, lid, gen)])
             lid += 1
         self.n_proj = lid
+        self.w_am = torch.zeros(lid, dtype=torch.float32, device=self.device)           # amax of each weight
+        self.am_words = torch.zeros(2, lid, dtype=torch.float32, device=self.device)   # amax of x / of dy per projection
         # the weight gradients of `ar_blocks` consecutive blocks live in one flat FP32 buffer, so that
         # their all-reduce is one collective (the LM head keeps a buffer of its own: it is first in
         # the backward order and its collective should start at once)
@@ -193,12 +195,14 @@ class LinearStack:
         if self.graph_refresh is not None:
             self.graph_refresh.replay()
             return
+        self.w_am.zero_()                   # one fill for all weights' amax words: the rest is a chain of kernels
         for projs in self.blocks:
             for p in projs:
+                am = nvq.amax(p.w, out=self.w_am[p.lid:p.lid + 1], clear=False)
                 if p.q is None:
-                    p.q, p.qt = nvq.quant_w2d(p.w)
+                    p.q, p.qt = nvq.quant_w2d(p.w, am=am)
                 else:
-                    nvq.quant_w2d(p.w, out=(p.q, p.qt))      # in place: captured graphs keep these buffers
+                    nvq.quant_w2d(p.w, am=am, out=(p.q, p.qt))      # in place: captured graphs keep these buffers
 
     def zero_grads(self):
         for projs in self.blocks:
@@ -242,8 +246,13 @@ class LinearStack:
     def _fwd_block(self, projs, keep=False):
         if self.mode == "emit":
             return self._fwd_block_emit(projs, keep)
+        # the block's amax words are cleared by one fill, so each projection is a kernel-to-kernel chain
+        # amax -> quantizer -> GEMM with no fill node in between
+        lo, hi = projs[0].lid, projs[-1].lid + 1
+        self.am_words[0, lo:hi].zero_()
         for p in projs:
-            y, p.am_x, p.qxt = linear_fwd(self.x_pool[p.name], p.q, keep_xt=True, signs=_RHT_SIGNS)
+            y, p.am_x, p.qxt = linear_fwd(self.x_pool[p.name], p.q, keep_xt=True, signs=_RHT_SIGNS,
+                                          am_out=self.am_words[0, p.lid:p.lid + 1])
             p.y = y if keep else None
 
     def _bwd_block(self, projs, keep=False, first=False):
@@ -252,11 +261,13 @@ class LinearStack:
         if self.mode == "emit":
             return self._bwd_block_emit(projs, keep, first)
         alive = []
+        lo, hi = projs[0].lid, projs[-1].lid + 1
+        self.am_words[1, lo:hi].zero_()
         for p in reversed(projs):
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(None, p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
                                gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt,
-                               wgrad_stream=self.wgrad_stream, keep_alive=alive)
+                               wgrad_stream=self.wgrad_stream, keep_alive=alive, am_out=self.am_words[1, p.lid:p.lid + 1])
             p.gx = gx if keep else None
         if self.wgrad_stream is not None:
             torch.cuda.current_stream().wait_stream(self.wgrad_stream)

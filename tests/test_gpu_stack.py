@@ -141,3 +141,45 @@ def test_stack_emitter_mode_graphs_equal_eager_and_oracle():
     gx = O.gemm_unit(gc, gsb, wct, wst) * grs.astype(np.float64)[:, None] * float(wgs)
     assert rel_fro(f32(p.gx), gx) <= 4e-3
     _lib.check_status()
+
+
+def test_stack_programmatic_launch_on_equals_off():
+    """The kernels of a projection follow each other by programmatic dependent launch (each may start its set-up while
+    its predecessor drains and waits for it before touching global memory).  Same seeds, the switch on and off, with
+    graphs and without, weight gradients on a side stream or not: bit-equal FP32 weight gradients after two steps."""
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.stack import LinearStack, StackConfig
+    lib = _lib.load()
+    cfg = StackConfig(vocab=512, d=256, layers=2, heads=2, kv_heads=1, ff=384, lm_head=True)
+    grads = []
+    try:
+        for pdl, graphs, side in ((1, True, True), (0, True, True), (1, False, True), (1, True, False), (0, False, False)):
+            assert lib.nvfp4_set_pdl(pdl) == 0
+            st = LinearStack(cfg, 256, torch.device("cuda"), seed=5, use_graphs=graphs, wgrad_side_stream=side)
+            if graphs:
+                st.capture()
+            for _ in range(2):
+                st.step(2, do_allreduce=False)
+            torch.cuda.synchronize()
+            grads.append([p.gw.clone() for blk in st.blocks for p in blk])
+    finally:
+        lib.nvfp4_set_pdl(1)
+    _lib.check_status()
+    for other in grads[1:]:
+        for g0, g1 in zip(grads[0], other):
+            assert torch.equal(g0, g1)
+    assert grads[0][0].abs().max().item() > 0
+
+
+def test_amax_update_keeps_the_larger_value():
+    from nvfp4_training_b200 import nvq
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    words = torch.zeros(3, device="cuda")
+    nvq.amax(x, out=words[0:1], clear=False)
+    nvq.amax(x * 4, out=words[1:2], clear=False)
+    nvq.amax(x, out=words[1:2], clear=False)           # smaller: leaves the word
+    assert words[0].item() == x.abs().max().item()
+    assert words[1].item() == (x * 4).abs().max().item()
+    assert words[2].item() == 0.0
+    assert nvq.amax(x).item() == words[0].item()
