@@ -285,6 +285,26 @@ def isolated_kernels(cfg, T, peaks):
     detail["emit_cols_sr"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
     t = q(lambda t, a: emit.col_emit(t, cq, use, cur, rng, sr="hw"))
     detail["emit_cols_sr_hw"] = {"elts": n, "us": t * 1e6, "gbs": n * 2.5625 / t / 1e9}
+    # producer-fused emitters of the reference's trainer.  swiglu_emit: [T, 2 x 5632] raw gate | up output (the
+    # four [T, 5632] tensors above taken in pairs) -> row operand of silu(g) * u: 4 B in + 0.5625 B out per value
+    gu = [torch.cat([x[0], x[1]], dim=1), torch.cat([x[2], x[3]], dim=1)]
+    rs_in = torch.full((T,), 0.5, dtype=torch.float32, device=dev)
+    one = torch.ones(1, dtype=torch.float32, device=dev)
+    t = time_events(lambda: (it.__setitem__(0, it[0] + 1), emit.swiglu_emit(gu[it[0] % 2], rs_in, one, rq)), iters=20)
+    detail["swiglu_emit"] = {"elts": n, "us": t * 1e6, "gbs": n * 4.5625 / t / 1e9}
+    del gu
+    # rms_emit: residual add + RMSNorm + row operand on [T, 2048]: x, y in, x_new out (2 B each), 0.5625 B of operand
+    xs = [t_[:, :2048].contiguous() for t_ in x] + [t_[:, 2048:4096].contiguous() for t_ in x]
+    xo = torch.empty(T, 2048, dtype=torch.bfloat16, device=dev)
+    wn = torch.ones(2048, dtype=torch.bfloat16, device=dev)
+    rq2 = emit.RowQ(T, 2048)
+    n2 = T * 2048
+    t = time_events(lambda: (it.__setitem__(0, it[0] + 1),
+                             emit.rms_emit(xs[it[0] % 8], wn, rq2, y=xs[(it[0] + 3) % 8], ys=rs_in, ygw=one, xout=xo)), iters=24)
+    detail["rms_emit_residual"] = {"elts": n2, "us": t * 1e6, "gbs": n2 * 6.5625 / t / 1e9}
+    t = time_events(lambda: (it.__setitem__(0, it[0] + 1), emit.rms_emit(xs[it[0] % 8], wn, rq2)), iters=24)
+    detail["rms_emit"] = {"elts": n2, "us": t * 1e6, "gbs": n2 * 2.5625 / t / 1e9}
+    del xs, xo
     w = [torch.randn(11264, 2048, generator=g, device=dev).bfloat16() for _ in range(4)]
     it = [0]
 

@@ -200,6 +200,36 @@ int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void* codes, voi
                     void* stream);
 
 /*
+ * Producer-fused emitters of the reference's trainer: the row operand (codes, swizzled scales, per-row FP32 scale
+ * rs_out, as nvfp4_emit_rows writes them) straight from the FP32 values a normalisation / activation computes.
+ *
+ * nvfp4_rms_emit replaces `rms_emit` (llm-1b/emit.cu:97-147, launcher llm-1b/emit.py:40-47): per row t of x [T, D]
+ * bf16, x_new = x + y * (ys[t] * ygw[0]) when y is given (stored to xout as bf16 and continued from the stored
+ * value), rstd = rsqrt(mean(x_new^2) + eps), h = (x_new * rstd) * w.  Optional outputs: h (bf16 [T, D]), rstd_out
+ * (FP32 [T]), and the row operand of the FP32 h when codes is non-null (then T % 128 == 0).  D in {1024, 2048, 4096}
+ * (the reference: 2048).  y non-null requires ys, ygw and xout.
+ *
+ * nvfp4_swiglu_emit replaces `swiglu_emit` / `swiglu_emit_5632` (llm-1b/emit.cu:149-222, launcher
+ * llm-1b/emit.py:50-58): gu [T, 2F] bf16 = raw gate | up GEMM output, true value = raw * (rs_in[t] * gw[0]);
+ * a = silu(g) * u.  Optional outputs: a_out (bf16 [T, F]), a_f32 (FP32 [T, F], for tests: the value that is
+ * quantized), the row operand of a when codes is non-null (then T % 128 == 0).  F % 256 == 0.
+ *
+ * Arithmetic: FP32; fused multiply-adds for x + y*s, the sum of squares (per lane in column order, then a butterfly
+ * over the 32 lanes) and mean + eps; round-to-nearest multiplications elsewhere; rsqrtf, __expf and the division of
+ * the sigmoid are the hardware approximations, everything after them is exact IEEE arithmetic on their results.
+ *
+ * nvfp4_mom_acc replaces `mom_acc` (llm-1b/emit.cu:343-363): m (bf16, n values, n % 8 == 0) <- m + (alpha[0] * scale)
+ * * g, rounded stochastically to bf16 (16 random bits added below the bf16 mantissa, then truncation); thread
+ * i = element / 8 runs s <- s*1664525 + 1013904223 from hash32(rng[0] ^ salt ^ hash32(i)), one step per pair of values.
+ */
+int nvfp4_rms_emit(const void* x, const void* y, const float* ys, const float* ygw, void* xout, const void* w, void* h,
+                   void* codes, void* scales, float* rs_out, float* rstd_out, int T, int D, float eps, void* stream);
+int nvfp4_swiglu_emit(const void* gu, const float* rs_in, const float* gw, int F, void* a_out, float* a_f32, void* codes,
+                      void* scales, float* rs_out, int T, void* stream);
+int nvfp4_mom_acc(void* m, const void* g, const float* alpha, float scale, long long n, const unsigned* rng,
+                  unsigned salt, void* stream);
+
+/*
  * 16x16-block quantization of a weight w [N, K] (bf16 or fp32, contiguous): one scale per block,
  * emitting W (q [N, K/2], s for [N, K/16]) and W^T (qt [K, N/2], st for [K, N/16]) with identical
  * code values.  Either output pair may be null to skip it.

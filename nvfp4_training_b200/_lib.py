@@ -32,6 +32,9 @@ SIGNATURES = {
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),
     "nvfp4_quant_tile_status": (_i, [_vp, _i]),
     "nvfp4_quant_tile_set_path": (_i, [_i]),
+    "nvfp4_rms_emit": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "nvfp4_swiglu_emit": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "nvfp4_mom_acc": (_i, [_vp, _vp, _vp, _f, _ll, _vp, _u, _vp]),
     "nvfp4_emit_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _i, _vp, _u, _vp]),
     "nvfp4_emit_rows_set_path": (_i, [_i]),
     "nvfp4_emit_cols": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _u, _vp]),

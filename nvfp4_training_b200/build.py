@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnvfp4_b200.so")
-SOURCES = ["quant.cu", "quant_tile.cu", "quant_mma.cu", "emit_ops.cu", "emit_rows_ring.cu", "gemm.cu", "noalloc.cu", "selftest.cu"]
+SOURCES = ["quant.cu", "quant_tile.cu", "quant_mma.cu", "emit_ops.cu", "emit_rows_ring.cu", "emit_fused.cu", "gemm.cu", "noalloc.cu", "selftest.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -2,10 +2,10 @@
 row operand with an exact per-row FP32 scale, so no tensor-wide amax pass precedes it, and the raw
 block-scaled GEMM whose result the consumer multiplies by `rs[t] * gs`.
 
-Built: `RowQ`, `ColQ`, `row_emit`, `col_emit`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`, `mm_col`, `scale_rows`, `dequant`.
+Built: `RowQ`, `ColQ`, `row_emit`, `col_emit`, `rms_emit`, `swiglu_emit`, `mom_acc`, `WQ`, `mm`, `mm_row_w`, `mm_row_wt`,
+`mm_col`, `scale_rows`, `dequant`.
 `mm_row_w` / `mm_row_wt` / `mm_col` take `scale=True` to apply `rs[row] * gs` (resp. the two delayed tensor scales) in
 the GEMM epilogue, which the reference does in a separate elementwise pass (`scale_rows`, llm-1b/model2.py:152-154).
-The fused producers (`rms_emit`, `swiglu_emit`) and `mom_acc` are not built.
 """
 import torch
 
@@ -65,6 +65,56 @@ def row_emit(x, q: RowQ, rng, sr=False, salt=0):
     L.check(L.load().nvfp4_emit_rows(L.ptr(x), x.stride(0), T, C, L.ptr(q.d), L.ptr(q.s), L.ptr(q.rs), 2 if sr == "hw" else int(bool(sr)),
                                      L.ptr(rng) if rng is not None else None, salt & 0xFFFFFFFF, L.stream()), "emit_rows")
     return q
+
+
+def rms_emit(x, w, q: RowQ = None, h=None, rstd=None, y=None, ys=None, ygw=None, xout=None, eps=1e-5):
+    """Residual add + RMSNorm + row quantization in one pass (llm-1b/emit.py:40-47, llm-1b/emit.cu:97-147):
+    x_new = x + y * ys[t] * ygw (written to `xout`), hn = x_new * rstd * w -> row operand `q`; optional `h` (bf16 hn)
+    and `rstd` (fp32 [T]) outputs.  x [T, D] contiguous bf16 with D in {1024, 2048, 4096} (the reference: 2048)."""
+    T, D = x.shape
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and w.dtype == torch.bfloat16 and w.numel() == D
+    L.require_cuda(x, w)
+    if y is not None:
+        assert y.shape == x.shape and y.is_contiguous() and ys is not None and ygw is not None and xout is not None
+        assert xout.shape == x.shape and xout.is_contiguous() and ys.dtype == torch.float32 and ygw.dtype == torch.float32
+    if q is not None:
+        assert T % 128 == 0 and q.d.shape == (T, D // 2)
+    if h is not None:
+        assert h.shape == x.shape and h.is_contiguous() and h.dtype == torch.bfloat16
+    o = lambda t: L.ptr(t) if t is not None else None
+    L.check(L.load().nvfp4_rms_emit(L.ptr(x), o(y), o(ys), o(ygw), o(xout), L.ptr(w), o(h), o(q.d if q else None),
+                                    o(q.s if q else None), o(q.rs if q else None), o(rstd), T, D, float(eps), L.stream()),
+            "rms_emit")
+    return q
+
+
+def swiglu_emit(gu, rs_in, gw, q: RowQ = None, a=None, a_f32=None):
+    """SwiGLU on the raw gate | up GEMM output [T, 2F] + row quantization of a = silu(g) * u, true g, u = raw *
+    rs_in[t] * gw (llm-1b/emit.py:50-58, llm-1b/emit.cu:149-222).  Optional `a` (bf16 [T, F]); `a_f32` (fp32 [T, F],
+    an addition for tests: the values that are quantized)."""
+    T, F2 = gu.shape
+    F = F2 // 2
+    assert gu.dtype == torch.bfloat16 and gu.is_contiguous() and F2 % 512 == 0
+    assert rs_in.dtype == torch.float32 and rs_in.numel() == T and gw.dtype == torch.float32
+    L.require_cuda(gu, rs_in, gw)
+    if q is not None:
+        assert T % 128 == 0 and q.d.shape == (T, F // 2)
+    o = lambda t: L.ptr(t) if t is not None else None
+    L.check(L.load().nvfp4_swiglu_emit(L.ptr(gu), L.ptr(rs_in), L.ptr(gw), F, o(a), o(a_f32), o(q.d if q else None),
+                                       o(q.s if q else None), o(q.rs if q else None), T, L.stream()), "swiglu_emit")
+    return q
+
+
+def mom_acc(m, g, alpha, scale, rng, salt=0):
+    """m (bf16) += alpha * scale * g (bf16), stochastically rounded (llm-1b/emit.py:77-80, llm-1b/emit.cu:343-363).
+    alpha: device fp32 [1]; rng: device int32 words, rng[0] = seed."""
+    n = m.numel()
+    assert n % 8 == 0 and g.numel() == n and m.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
+    assert m.is_contiguous() and g.is_contiguous() and alpha.dtype == torch.float32
+    L.require_cuda(m, g, alpha, rng)
+    L.check(L.load().nvfp4_mom_acc(L.ptr(m), L.ptr(g), L.ptr(alpha), float(scale), n, L.ptr(rng), salt & 0xFFFFFFFF, L.stream()),
+            "mom_acc")
+    return m
 
 
 class WQ:

@@ -608,3 +608,114 @@ def qref_rows(x):
     zero = np.broadcast_to((sbyte == 0)[..., None], codes.shape)
     codes = np.where(zero, np.signbit(xb).astype(np.uint8) << 3, codes).astype(np.uint8)
     return codes.reshape(T, C), sbyte, gs
+
+
+# ----------------------------------------------------------------------------- producer-fused emitters
+# Restatement of `rms_emit`, `swiglu_emit` and `mom_acc` of the reference's 1B trainer (llm-1b/emit.cu:97-222,
+# 343-363).  PARITY UNPINNED, like the emitters above: the reference holds no CPU implementation or fixture of these
+# kernels and builds them with --use_fast_math, so the order of operations below is the explicit FP32 form the
+# sm_100a kernels use (fused multiply-adds where the reference's expressions contract, IEEE multiplications and
+# divisions elsewhere).  The three hardware approximations (rsqrtf, __expf, approximate division) have no CPU
+# model: `rstd` / the FP32 activation are taken from the GPU when given (checked against FP64 within a tolerance by
+# the caller) and computed in FP64 otherwise.
+def fma_f32(a, b, c):
+    """Correctly rounded float32 a*b + c.  The product of two float32 is exact in float64; the sum is formed with its
+    exact rounding error (TwoSum), and where the float64 sum sits exactly half-way between two float32 values the
+    error term decides the direction."""
+    a, b, c = np.broadcast_arrays(np.asarray(a, dtype=np.float32), np.asarray(b, dtype=np.float32), np.asarray(c, dtype=np.float32))
+    p = a.astype(np.float64) * b.astype(np.float64)
+    c64 = c.astype(np.float64)
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)                      # exact: p + c == s + err
+    with np.errstate(over="ignore"):
+        r = s.astype(np.float32)
+    fin = np.isfinite(r) & (err != 0)
+    if fin.any():
+        r64 = r.astype(np.float64)
+        with np.errstate(over="ignore"):
+            lo = np.nextafter(r, np.float32(-np.inf)).astype(np.float64)
+            hi = np.nextafter(r, np.float32(np.inf)).astype(np.float64)
+        d = s - r64
+        tie_lo = fin & (d < 0) & (s - lo == r64 - s)       # s is the midpoint of [lo, r]
+        tie_hi = fin & (d > 0) & (hi - s == s - r64)
+        # float32(s) resolved the tie to even; the true value s + err lies strictly on err's side of it
+        r = np.where(tie_lo, np.where(err < 0, lo, r64), np.where(tie_hi, np.where(err > 0, hi, r64), r64)).astype(np.float32)
+        on_r = fin & (d == 0)                               # s representable: err cannot move the rounding
+        r = np.where(on_r, s, r).astype(np.float32)
+    return r
+
+
+def bf16_round(x):
+    """float32 -> nearest bf16 value (ties to even), as float32."""
+    return bf16_bits_to_f32(f32_to_bf16_bits(np.asarray(x, dtype=np.float32)))
+
+
+def rms_emit(x, w, y=None, ys=None, ygw=None, eps=1e-5, rstd=None):
+    """`rms_emit` (llm-1b/emit.cu:97-147): x_new = x + y*(ys[t]*ygw) (rounded to bf16 and continued from the rounded
+    value), rstd = rsqrt(mean(x_new^2) + eps), h = (x_new*rstd)*w, row operand of the FP32 h.  x, y: [T, D] float32
+    holding bf16 values, w [D], ys [T], ygw scalar.  The sum of squares follows the kernel: lane l = (column/8) % 32
+    accumulates its chunks 256 j + 8 l in column order with fused multiply-adds, then a butterfly over the lanes
+    (strides 16, 8, 4, 2, 1).  Returns a dict: xout (None without y), rstd, rstd_ref (FP64-derived), h (FP32), h_bf16,
+    codes, scales (row-major bytes), rs."""
+    x = np.asarray(x, dtype=np.float32)
+    T, D = x.shape
+    assert D % 256 == 0
+    v, xout = x, None
+    if y is not None:
+        ysc = (np.asarray(ys, dtype=np.float32) * np.float32(ygw)).astype(np.float32)
+        v = fma_f32(np.asarray(y, dtype=np.float32), ysc[:, None], x)
+        xout = bf16_round(v)
+        v = xout
+    lanes = v.reshape(T, D // 256, 32, 8)
+    ss = np.zeros((T, 32), dtype=np.float32)
+    for j in range(D // 256):
+        for i in range(8):
+            ss = fma_f32(lanes[:, j, :, i], lanes[:, j, :, i], ss)
+    idx = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        ss = (ss + ss[:, idx ^ o]).astype(np.float32)
+    ms = fma_f32(ss[:, 0], np.float32(1.0 / D), np.float32(eps))
+    rstd_ref = (1.0 / np.sqrt(ms.astype(np.float64))).astype(np.float32)
+    rstd = rstd_ref if rstd is None else np.asarray(rstd, dtype=np.float32)
+    h = ((v * rstd[:, None]).astype(np.float32) * np.asarray(w, dtype=np.float32)[None, :]).astype(np.float32)
+    codes, scales, rs = emit_rows(h)
+    return {"xout": xout, "rstd": rstd, "rstd_ref": rstd_ref, "h": h, "h_bf16": bf16_round(h), "codes": codes,
+            "scales": scales, "rs": rs}
+
+
+def swiglu_emit(gu, rs_in, gw, a_f32=None):
+    """`swiglu_emit` (llm-1b/emit.cu:149-222): gu [T, 2F] = raw gate | up GEMM output (float32 holding bf16), true
+    value = raw * (rs_in[t] * gw); a = silu(g) * u; row operand of the FP32 a.  `a_f32`: the activation as the GPU
+    computed it (its exponential and division are hardware approximations); without it a is formed in FP64.
+    Returns a dict: a (FP32), a_ref (FP64-derived), a_bf16, codes, scales, rs."""
+    gu = np.asarray(gu, dtype=np.float32)
+    T, F2 = gu.shape
+    F = F2 // 2
+    sc = (np.asarray(rs_in, dtype=np.float32) * np.float32(gw)).astype(np.float32)
+    xg = (gu[:, :F] * sc[:, None]).astype(np.float32)
+    xu = (gu[:, F:] * sc[:, None]).astype(np.float32)
+    with np.errstate(over="ignore"):
+        a_ref = (xg.astype(np.float64) / (1.0 + np.exp(-xg.astype(np.float64))) * xu.astype(np.float64)).astype(np.float32)
+    a = a_ref if a_f32 is None else np.asarray(a_f32, dtype=np.float32)
+    codes, scales, rs = emit_rows(a)
+    return {"a": a, "a_ref": a_ref, "a_bf16": bf16_round(a), "codes": codes, "scales": scales, "rs": rs}
+
+
+def mom_acc(m, g, alpha, scale, seed, salt=0):
+    """`mom_acc` (llm-1b/emit.cu:343-363): m (bf16) <- m + (alpha*scale)*g rounded stochastically to bf16 by adding 16
+    random bits below the bf16 mantissa and truncating.  m, g: flat float32 arrays holding bf16 values, length % 8
+    == 0.  Thread i = element/8 runs s <- s*1664525 + 1013904223 from hash32(seed ^ salt ^ hash32(i)), one step per
+    pair of values: low half-word for the even value, high half-word for the odd one.  Returns float32 holding bf16."""
+    m = np.asarray(m, dtype=np.float32).reshape(-1, 8)
+    g = np.asarray(g, dtype=np.float32).reshape(-1, 8)
+    a = np.float32(np.float32(alpha) * np.float32(scale))
+    x = fma_f32(a, g, m)
+    n8 = m.shape[0]
+    h = hash32(np.uint32((seed ^ salt) & 0xFFFFFFFF) ^ hash32(np.arange(n8, dtype=np.uint64).astype(np.uint32)))
+    out = np.empty((n8, 8), dtype=np.uint32)
+    for j in range(0, 8, 2):
+        h = (h * np.uint32(1664525) + np.uint32(1013904223)).astype(np.uint32)
+        out[:, j] = ((f2u(x[:, j]).astype(np.uint64) + (h & np.uint32(0xFFFF)).astype(np.uint64)) & 0xFFFFFFFF) >> 16
+        out[:, j + 1] = ((f2u(x[:, j + 1]).astype(np.uint64) + (h >> np.uint32(16)).astype(np.uint64)) & 0xFFFFFFFF) >> 16
+    return bf16_bits_to_f32(out.astype(np.uint16)).reshape(-1)

@@ -103,3 +103,51 @@ def test_emit_rows_11264_columns_uses_the_four_sequence_stream():
                 k = np.float32(inv / sd) if sd > 0 else np.float32(0)
                 c8, st = O._emit_pack8(x[r, col:col + 8][None, :], np.array([k], dtype=np.float32), True, st)
                 assert np.array_equal(np.asarray(c8).reshape(-1), got[col:col + 8]), (sub, lane, j)
+
+
+def test_fma_f32_is_correctly_rounded():
+    """The oracle's fused multiply-add against exact rational arithmetic, including products that sit exactly half-way
+    between two float32 values with an addend far below the last bit (where a float64 sum would round the wrong way)."""
+    from fractions import Fraction
+    rng = np.random.default_rng(0)
+    n = 1500
+    a = rng.standard_normal(n).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    c = (rng.standard_normal(n) * 10.0 ** rng.integers(-12, 3, n)).astype(np.float32)
+    a[:200] = np.float32(1 + 2.0 ** -12)
+    b[:200] = np.float32(1 + 2.0 ** -12)          # product 1 + 2^-11 + 2^-24: a midpoint of the float32 grid
+    c[:100] = np.float32(2.0 ** -60)
+    c[100:200] = np.float32(-2.0 ** -60)
+    r = O.fma_f32(a, b, c)
+    for i in range(n):
+        v = Fraction(float(a[i])) * Fraction(float(b[i])) + Fraction(float(c[i]))
+        f = np.float32(float(v))
+        cands = [np.nextafter(f, np.float32(-np.inf)), f, np.nextafter(f, np.float32(np.inf))]
+        best = min(cands, key=lambda t: (abs(Fraction(float(t)) - v), int(np.float32(t).view(np.uint32)) & 1))
+        assert np.float32(best).view(np.uint32) == r[i].view(np.uint32), i
+    assert r[0] > r[150]
+
+
+def test_fused_producers_self_consistency():
+    """rms_emit / swiglu_emit of the oracle: the operand dequantizes back to the FP32 values it was made from within
+    one code step of each block, rstd matches the plain formula, the residual is bf16; mom_acc is unbiased."""
+    rng = np.random.default_rng(1)
+    bf = lambda v: O.bf16_round(np.asarray(v, dtype=np.float32))
+    T, D = 16, 2048
+    x, y = bf(rng.standard_normal((T, D))), bf(rng.standard_normal((T, D)) * 40)
+    ys, ygw, w = (0.01 + 0.02 * rng.random(T)).astype(np.float32), np.float32(0.7), bf(1 + 0.1 * rng.standard_normal(D))
+    o = O.rms_emit(x, w, y, ys, ygw)
+    xn = x.astype(np.float64) + y.astype(np.float64) * (ys * ygw).astype(np.float64)[:, None]
+    assert np.array_equal(o["xout"], bf(o["xout"])) and np.abs(o["xout"] - xn).max() <= np.abs(xn).max() * 2.0 ** -8
+    want = 1 / np.sqrt((o["xout"].astype(np.float64) ** 2).mean(axis=1) + 1e-5)
+    assert np.abs(o["rstd"] / want - 1).max() < 1e-6
+    step = np.repeat(O.e4m3_decode(o["scales"]) * o["rs"][:, None], 16, axis=1)
+    assert (np.abs(O.emit_rows_dequant(o["codes"], o["scales"], o["rs"]) - o["h"]) <= step + 1e-12).all()
+    gu = bf(rng.standard_normal((T, 1024)) * 3)
+    s = O.swiglu_emit(gu, np.full(T, 0.5, np.float32), 1.5)
+    step = np.repeat(O.e4m3_decode(s["scales"]) * s["rs"][:, None], 16, axis=1)
+    assert (np.abs(O.emit_rows_dequant(s["codes"], s["scales"], s["rs"]) - s["a"]) <= step + 1e-12).all()
+    m, g = bf(rng.standard_normal(4096) * 0.1), bf(rng.standard_normal(4096) * 1e-3)
+    acc = sum(O.mom_acc(m, g, 0.5, 0.5, seed, 3).astype(np.float64) for seed in range(1, 65)) / 64
+    exact = m.astype(np.float64) + 0.25 * g.astype(np.float64)
+    assert np.mean(np.abs(acc - exact) / (np.abs(exact) * 2.0 ** -8)) < 0.15
