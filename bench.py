@@ -863,7 +863,18 @@ def run_case(args):
             rq = emit.RowQ(a.M, a.N)
             rng = torch.tensor([1, 0], dtype=torch.int32, device="cuda")
             cases = cases + (("emit_rows_rn", lambda x: emit.row_emit(x, rq, None), 2.5625),
-                             ("emit_rows_sr", lambda x: emit.row_emit(x, rq, rng, sr=True), 2.5625))
+                             ("emit_rows_sr", lambda x: emit.row_emit(x, rq, rng, sr=True), 2.5625),
+                             ("emit_rows_hw", lambda x: emit.row_emit(x, rq, rng, sr="hw"), 2.5625))
+            one = torch.ones(1, dtype=torch.float32, device="cuda")
+            rs_in = torch.full((a.M,), 0.5, dtype=torch.float32, device="cuda")
+            if a.N in (1024, 2048, 4096):
+                wn = torch.ones(a.N, dtype=torch.bfloat16, device="cuda")
+                xo = torch.empty(a.M, a.N, dtype=torch.bfloat16, device="cuda")
+                cases = cases + (("rms_emit_operand", lambda x: emit.rms_emit(x, wn, rq), 2.5625),
+                                 ("rms_emit_residual", lambda x: emit.rms_emit(x, wn, rq, y=xs[0], ys=rs_in, ygw=one, xout=xo), 6.5625))
+            if a.only and "swiglu" in a.only:
+                gus = [torch.cat([x_, x_], dim=1) for x_ in xs]          # raw gate | up output [M, 2N]
+                cases = cases + (("swiglu_emit", lambda x: emit.swiglu_emit(gus[turn[0] % a.sets], rs_in, one, rq), 4.5625),)
             if a.M % 256 == 0:
                 cq = emit.ColQ(a.M, a.N)
                 use = torch.full((1,), 16.0, dtype=torch.float32, device="cuda")

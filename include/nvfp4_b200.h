@@ -214,8 +214,9 @@ int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void* codes, voi
  * a = silu(g) * u.  Optional outputs: a_out (bf16 [T, F]), a_f32 (FP32 [T, F], for tests: the value that is
  * quantized), the row operand of a when codes is non-null (then T % 128 == 0).  F % 256 == 0.
  *
- * Arithmetic: FP32; fused multiply-adds for x + y*s, the sum of squares (per lane in column order, then a butterfly
- * over the 32 lanes) and mean + eps; round-to-nearest multiplications elsewhere; rsqrtf, __expf and the division of
+ * Arithmetic: FP32; fused multiply-adds for x + y*s, the sum of squares (lane l = (column/16) % 32 sums the even and
+ * the odd elements of its 16-value blocks separately in column order, adds the two, then a butterfly over the 32
+ * lanes) and mean + eps; round-to-nearest multiplications elsewhere; rsqrtf, __expf and the division of
  * the sigmoid are the hardware approximations, everything after them is exact IEEE arithmetic on their results.
  *
  * nvfp4_mom_acc replaces `mom_acc` (llm-1b/emit.cu:343-363): m (bf16, n values, n % 8 == 0) <- m + (alpha[0] * scale)

@@ -654,24 +654,26 @@ def bf16_round(x):
 def rms_emit(x, w, y=None, ys=None, ygw=None, eps=1e-5, rstd=None):
     """`rms_emit` (llm-1b/emit.cu:97-147): x_new = x + y*(ys[t]*ygw) (rounded to bf16 and continued from the rounded
     value), rstd = rsqrt(mean(x_new^2) + eps), h = (x_new*rstd)*w, row operand of the FP32 h.  x, y: [T, D] float32
-    holding bf16 values, w [D], ys [T], ygw scalar.  The sum of squares follows the kernel: lane l = (column/8) % 32
-    accumulates its chunks 256 j + 8 l in column order with fused multiply-adds, then a butterfly over the lanes
-    (strides 16, 8, 4, 2, 1).  Returns a dict: xout (None without y), rstd, rstd_ref (FP64-derived), h (FP32), h_bf16,
+    holding bf16 values, w [D], ys [T], ygw scalar.  The sum of squares follows the kernel: lane l = (column/16) % 32
+    owns the 16-value blocks 32 j + l and accumulates their even and their odd elements separately with fused
+    multiply-adds (blocks, then pairs, in column order), adds the two sums, then a butterfly over the lanes (strides
+    16, 8, 4, 2, 1).  Returns a dict: xout (None without y), rstd, rstd_ref (FP64-derived), h (FP32), h_bf16,
     codes, scales (row-major bytes), rs."""
     x = np.asarray(x, dtype=np.float32)
     T, D = x.shape
-    assert D % 256 == 0
+    assert D % 512 == 0
     v, xout = x, None
     if y is not None:
         ysc = (np.asarray(ys, dtype=np.float32) * np.float32(ygw)).astype(np.float32)
         v = fma_f32(np.asarray(y, dtype=np.float32), ysc[:, None], x)
         xout = bf16_round(v)
         v = xout
-    lanes = v.reshape(T, D // 256, 32, 8)
-    ss = np.zeros((T, 32), dtype=np.float32)
-    for j in range(D // 256):
-        for i in range(8):
-            ss = fma_f32(lanes[:, j, :, i], lanes[:, j, :, i], ss)
+    lanes = v.reshape(T, D // 512, 32, 8, 2)            # [row, group of 512 columns, lane, pair, element of the pair]
+    acc = np.zeros((T, 32, 2), dtype=np.float32)
+    for j in range(D // 512):
+        for t in range(8):
+            acc = fma_f32(lanes[:, j, :, t, :], lanes[:, j, :, t, :], acc)
+    ss = (acc[..., 0] + acc[..., 1]).astype(np.float32)
     idx = np.arange(32)
     for o in (16, 8, 4, 2, 1):
         ss = (ss + ss[:, idx ^ o]).astype(np.float32)

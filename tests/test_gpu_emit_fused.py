@@ -4,8 +4,8 @@ restatement of llm-1b/emit.cu:97-222, 343-363.
 Each producer has one step the CPU cannot model bit for bit, a hardware approximation: rsqrtf in `rms_emit`, __expf and
 the approximate division of the sigmoid in `swiglu_emit`.  The kernels hand that intermediate out (rstd per row; the
 FP32 activation), so the tests split in two:
-  * the approximate step against FP64 within a stated tolerance: rstd within 2 units in the last place (the documented
-    bound of rsqrtf), the activation within 2e-5 relative + 1e-9 absolute;
+  * the approximate step against FP64 within a stated tolerance: rstd within 2^-22 relative (the hardware reciprocal
+    square root is specified to about 2^-22.9), the activation within 2e-5 relative + 1e-9 absolute;
   * everything else bit for bit given that intermediate: the residual stream written back, the bf16 outputs, the row
     maxima / per-row scales, scale bytes and codes.
 `mom_acc` is integer and IEEE arithmetic only: bit-exact, plus an unbiasedness bound.
@@ -49,8 +49,9 @@ def check_rowq(q, ref, T, C):
 
 def rms_inputs(seed, T, D):
     rng = np.random.default_rng(seed)
-    x = bf16_round(rng.standard_normal((T, D)).astype(np.float32) * (1 + 4 * rng.random((T, 1)).astype(np.float32)))
+    x = rng.standard_normal((T, D)).astype(np.float32) * (1 + 4 * rng.random((T, 1)).astype(np.float32))
     x[:, rng.permutation(D)[:4]] *= 20                         # massive-activation columns
+    x = bf16_round(x)
     y = bf16_round(rng.standard_normal((T, D)).astype(np.float32) * 50)       # raw GEMM output, scaled by ys * ygw
     ys = (0.01 + 0.02 * rng.random(T)).astype(np.float32)
     ygw = np.float32(0.731)
@@ -72,8 +73,8 @@ def test_rms_emit(emit, T, D, with_y):
     emit.rms_emit(to_dev(x), to_dev(w), q, h=h, rstd=rstd, eps=1e-5, **kw)
     g_rstd = rstd.cpu().numpy()
     ref = O.rms_emit(x, w, y if with_y else None, ys, ygw, eps=1e-5, rstd=g_rstd)
-    # the approximate step: rsqrtf within 2 ulp of the correctly rounded value
-    assert ulps(g_rstd, ref["rstd_ref"]).max() <= 2
+    # the approximate step: the reciprocal square root against the correctly rounded value
+    assert np.abs(g_rstd.astype(np.float64) / ref["rstd_ref"].astype(np.float64) - 1).max() <= 2.0 ** -22
     # everything else bit for bit
     if with_y:
         assert np.array_equal(bits(xout), O.f32_to_bf16_bits(ref["xout"]))
@@ -98,7 +99,7 @@ def test_rms_emit_without_operand_any_row_count(emit):
     ref = O.rms_emit(x, w, y, ys, ygw, rstd=rstd.cpu().numpy())
     assert np.array_equal(bits(xout), O.f32_to_bf16_bits(ref["xout"]))
     assert np.array_equal(bits(h), O.f32_to_bf16_bits(ref["h"]))
-    assert ulps(rstd.cpu().numpy(), ref["rstd_ref"]).max() <= 2
+    assert np.abs(rstd.cpu().numpy().astype(np.float64) / ref["rstd_ref"].astype(np.float64) - 1).max() <= 2.0 ** -22
 
 
 def swiglu_inputs(seed, T, F):
