@@ -36,6 +36,9 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
   pdl_wait();
   u32 m = 0u;  // running max of |x| as bf16 bit patterns in both halves of a word
   const long long stride = (long long)gridDim.x * blockDim.x;
+  // batches of four loads in flight per thread.  The last, partial batch clamps the indices past the end to the last
+  // element (a maximum does not mind reading it again) rather than walking one load at a time: on a 33 MB tensor a
+  // thread has seven loads, and three of them in sequence cost more than the first four together.
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < n8; i += 4 * stride) {
     uint4 v[4];
@@ -47,10 +50,16 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
       m = __vmaxu2(m, v[j].z & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].w & 0x7FFF7FFFu);
     }
   }
-  for (; i < n8; i += stride) {
-    uint4 v = ld_cg_128(x + i);
-    m = __vmaxu2(m, v.x & 0x7FFF7FFFu); m = __vmaxu2(m, v.y & 0x7FFF7FFFu);
-    m = __vmaxu2(m, v.z & 0x7FFF7FFFu); m = __vmaxu2(m, v.w & 0x7FFF7FFFu);
+  if (i < n8) {
+    const long long last = n8 - 1;
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = ld_cg_128(x + min(i + j * stride, last));
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      m = __vmaxu2(m, v[j].x & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].y & 0x7FFF7FFFu);
+      m = __vmaxu2(m, v[j].z & 0x7FFF7FFFu); m = __vmaxu2(m, v[j].w & 0x7FFF7FFFu);
+    }
   }
   u32 mm = max(m & 0xFFFFu, m >> 16);
   // NaN patterns (> 0x7F80) count as +inf
