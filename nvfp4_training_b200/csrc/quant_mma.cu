@@ -174,6 +174,30 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   const u32 full0 = smem_u32(bars), empty0 = full0 + 8 * kQStages;
   const u32 tfull = empty0 + 8 * kQStages, tempty = tfull + 16;     // two tensor-memory buffers: [2] each
 
+  // ---- barriers first, and the loads of the first tiles at once: their latency (1-2 us) runs under the set-up below
+  // (tables, tensor-memory allocation), which matters for tensors of a few tens of MB where a launch lasts 20-40 us
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < kQStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(tfull + 8 * b, 1); mbar_init(tempty + 8 * b, kQConsumerWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  auto load_tile = [&](const TcWalk& tw, u32 stage) {
+    if (elect_one()) {
+      const u32 bar = full0 + 8 * stage, dst = tiles0 + stage * kQTileBytes;
+      mbar_arrive_expect_tx(bar, kQTileBytes);
+      tma_load_2d(dst, &map, tw.ct * kQCol, tw.mt * kQTok, bar);
+      tma_load_2d(dst + kQBoxBytes, &map, tw.ct * kQCol + 64, tw.mt * kQTok, bar);
+    }
+    __syncwarp();
+  };
+  TcWalk ahead(p.M, p.C);            // the producer's position: kQStages tiles ahead of the MMAs
+  if (warp == 0) {
+    __syncwarp();
+    pdl_wait();                      // x may be the previous kernel's output
+    for (u32 s = 0; s < (u32)kQStages && ahead.valid(); s++, ahead.next()) load_tile(ahead, s);
+  }
+
   // ---- constants of the MMAs: identity and the two sign/interleave matrices, in the K-major 128-byte-swizzle
   // layout (row n at n * 128 bytes, its 16-byte chunk j at position j ^ (n & 7)); only K columns 0..15 are read
   for (u32 i = threadIdx.x; i < (2048u + 2u * kQPermBytes) / 4u; i += kQThreads)
@@ -203,12 +227,6 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
       }
     }
   }
-  if (threadIdx.x == 0) {
-    abort_word = 0;
-    for (int s = 0; s < kQStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(tfull + 8 * b, 1); mbar_init(tempty + 8 * b, kQConsumerWarps); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
   // the tensor core reads shared memory through the asynchronous proxy
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 0) {
@@ -235,19 +253,10 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
   constexpr bool BOTH = ROWS && COLS;
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer and MMA issuer (one warp)
-    // Loads run kQStages tiles ahead: the load of tile n + kQStages is issued once the MMAs of tile n have
-    // released their stage.
+    // Loads run kQStages tiles ahead (the first ones were issued at the top of the kernel): the load of tile
+    // n + kQStages is issued once the MMAs of tile n have released their stage.
     constexpr u32 idesc_row = q_idesc(16, false), idesc_col = q_idesc(32, true);
     const u64 b_i16 = q_desc_k(i16_s), b_p1 = q_desc_k(p1_s), b_p2 = q_desc_k(p2_s);
-    auto load_tile = [&](const TcWalk& tw, u32 stage) {
-      if (elect_one()) {
-        const u32 bar = full0 + 8 * stage, dst = tiles0 + stage * kQTileBytes;
-        mbar_arrive_expect_tx(bar, kQTileBytes);
-        tma_load_2d(dst, &map, tw.ct * kQCol, tw.mt * kQTok, bar);
-        tma_load_2d(dst + kQBoxBytes, &map, tw.ct * kQCol + 64, tw.mt * kQTok, bar);
-      }
-      __syncwarp();
-    };
     // D[token, 64 b + 16 kk + n] = sum_k X[token, 64 b + 16 kk + k] * I[n, k]
     auto row_mmas = [&](u32 tile, u32 d) {
 #pragma unroll
@@ -264,8 +273,6 @@ __global__ void __launch_bounds__(kQThreads, 2) quant_tc_kernel(const __grid_con
         q_mma_bf16(d + (u32)(32 * pr), q_desc_mn(tile + (32 * pr + 16) * 128), b_p2, idesc_col, 1u);
       }
     };
-    TcWalk ahead(p.M, p.C);
-    for (u32 s = 0; s < (u32)kQStages && ahead.valid(); s++, ahead.next()) load_tile(ahead, s);
     u32 stage = 0, phase = 0, n = 0;
     for (TcWalk tw(p.M, p.C); tw.valid(); tw.next(), n++) {
       // buffers and their parities: with both outputs each buffer is used once per tile, else once per two tiles
