@@ -630,12 +630,18 @@ def run_ours(args):
     torch.cuda.set_device(local)
     _lib.load().nvfp4_set_pdl(1 if args.pdl else 0)
     if args.comm_sms is None:
-        # measured on 8 B200s: 34.4 ms per step with 16 SMs left to NCCL, 32.0 with 32, 31.7 with 48, 46.8 with 8;
-        # with fewer ranks the collective is smaller next to the compute and the GEMMs keep more SMs
-        args.comm_sms = 32 if world >= 8 else 16
+        # SMs kept out of the backward GEMM grids for NCCL.  The GEMM draws its tiles at run time, so a grid that finds
+        # SMs taken by the collective needs no budget: the clusters that run share the work and the late ones find
+        # none (a few microseconds of tail per launch).  With 2 ranks the collective is in flight for about a third of
+        # the backward pass and no budget wins (75.2-77.1 ms per step against 77.2-79.7 with 16 SMs set aside, same
+        # boxes); with 8 ranks it is in flight almost all the time, the tail would be paid on nearly every launch, and
+        # the budget measured best earlier (32 SMs) is kept.
+        args.comm_sms = 32 if world >= 8 else 0
+    if not args.nccl_ctas:
+        args.nccl_ctas = 32
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_MAX_CTAS", str(max(4, args.comm_sms)))     # NCCL stays inside the SMs left free for it
+        os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks, peak_src = load_peaks()
 
@@ -710,7 +716,7 @@ def run_ours(args):
     comm = None
     if world > 1 and ms_ar > 0:
         comm = {"step_without_allreduce_ms": ms_noar, "comm_exposed_ms": ms - ms_noar, "allreduce_alone_ms": ms_ar,
-                "allreduce_bytes": ar_bytes,
+                "allreduce_bytes": ar_bytes, "gemm_sm_budget": args.comm_sms, "nccl_max_ctas": args.nccl_ctas,
                 "allreduce_alone_busbw_gbs": 2.0 * (world - 1) / world * ar_bytes / (ms_ar * 1e-3) / 1e9,
                 "how": "same step with the collective switched off; the block-by-block all-reduces of all gradient "
                        "buffers alone; CUDA events, max over ranks"}
@@ -918,7 +924,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
-                    help="SMs left free for NCCL during backward when N > 1 (default: 32 at N >= 8, else 16)")
+                    help="SMs kept out of the backward GEMM grids for NCCL when N > 1 (default: 32 at N >= 8, else 0)")
+    ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default 32)")
     ap.add_argument("--no-wgrad-stream", action="store_true",
                     help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch of the library's kernels (off by default)")

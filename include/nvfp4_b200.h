@@ -298,6 +298,14 @@ int nvfp4_gemm_force_tile_n(int bn);
 int nvfp4_gemm_set_sm_budget(int sms);
 
 /*
+ * The CTA-pair GEMM hands out its work items at run time from a per-launch counter in device memory (a grid that finds
+ * SMs occupied by another kernel shares the items among the CTAs that do run); the counter returns to zero when a
+ * launch completes.  After a launch that was abandoned (status word set by an expired wait) call this once to clear
+ * the counters of the current device.  Synchronises the device.  No reference counterpart.
+ */
+int nvfp4_gemm_reset_scheduler(void);
+
+/*
  * Same product for operands whose scales are in the LINEAR layout (row strides ldsa / ldsb bytes):
  * the scales are first rewritten into the swizzled layout inside `workspace`, then nvfp4_gemm runs.
  * This is the `fp4ops.gemm` contract (llm-1b/fp4ops.py:64-80: strided d and s views allowed).

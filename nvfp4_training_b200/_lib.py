@@ -27,6 +27,7 @@ SIGNATURES = {
     "nvfp4_amax_bf16": (_i, [_vp, _ll, _vp, _vp]),
     "nvfp4_amax_bf16_update": (_i, [_vp, _ll, _vp, _vp]),
     "nvfp4_set_pdl": (_i, [_i]),
+    "nvfp4_gemm_reset_scheduler": (_i, []),
     "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp, _vp]),
     "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp, _vp]),
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),
@@ -125,6 +126,8 @@ def check_status(device=None):
     code = int(status_word(dev).item())
     if code:
         status_word(dev).zero_()
+        with torch.cuda.device(dev):
+            load().nvfp4_gemm_reset_scheduler()      # an abandoned launch may have left its work counter half-way
         raise Nvfp4Error(f"GEMM pipeline wait expired (role code {code})")
     qcode = ctypes.c_int(0)
     with torch.cuda.device(dev):

@@ -402,7 +402,7 @@ struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBBytes + kSFABytes + kSFBBytes;   // multiple of 1024
   static constexpr int kStageRowBytes = BN == 256 ? 128 : 64;                     // staging row of one lane
   static constexpr int kStagingBytes = kEpiWarps * 32 * kStageRowBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 512;   // + alignment + barriers and tile queue
   static constexpr u32 kTxBytes = 2u * kStageBytes;        // both CTAs' loads of one stage
   // Tensor-memory columns.  BN = 256: accumulators at columns 0 and 208 overlap in columns 208..255,
   // which the epilogue drains first and hands back at once; scales behind them at 464 (A: 16 columns,
@@ -483,7 +483,45 @@ struct PairParams {
   int atomic;
   int splitk;
   int ktiles_per_split;
+  unsigned* counter;      // this launch's work counter (zero before the launch, zero again after it)
 };
+
+// ---- dynamic tile scheduler of the pair kernel
+// Work items are not dealt out in advance: a cluster takes the next item from a global counter whenever it is ready
+// for one.  A grid that finds some SMs occupied (a collective running beside the GEMM) then needs no tuning: the
+// clusters that do run share all the items, the ones that start late find none.  The leader CTA's producer warp draws
+// the numbers and publishes them to every role of both CTAs through a small queue in shared memory: entry k lives in
+// slot k % kSchedSlots as one 64-bit word {item, k + 1}, written with a single store (to the peer through
+// shared::cluster) and polled by its readers.  A slot is reused kSchedSlots entries later; no reader lags that far:
+// the producer runs at most kStages K tiles (at most kStages items) ahead of the MMA warp, the MMA warp at most two
+// items (accumulators) ahead of the epilogue, and the draw for the next entry happens one entry early: 7 + 2 + 1 < 16.
+// The counter resets itself: each cluster draws until it gets a number >= num_work, so exactly num_work + clusters
+// numbers are drawn per launch and whoever draws the last one stores zero.
+constexpr int kSchedSlots = 16;
+__device__ unsigned g_tile_counters[4096];
+
+__device__ __forceinline__ void sched_publish(u32 slot_local, u32 slot_peer, u32 k, u32 item) {
+  const u64 v = ((u64)(k + 1u) << 32) | (u64)item;
+  asm volatile("st.volatile.shared::cta.u64 [%0], %1;" ::"r"(slot_local), "l"(v) : "memory");
+  asm volatile("st.volatile.shared::cluster.u64 [%0], %1;" ::"r"(slot_peer), "l"(v) : "memory");
+}
+// Entry k of this CTA's queue; -1 when the CTA is aborting or the bounded wait expired.
+__device__ __forceinline__ int sched_wait(u32 sched0, u32 k, volatile int* abort_flag) {
+  const u32 addr = sched0 + 8u * (k & (u32)(kSchedSlots - 1));
+  u64 t0 = 0;
+  for (u32 it = 1;; ++it) {
+    u64 v;
+    asm volatile("ld.volatile.shared::cta.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    if ((u32)(v >> 32) == k + 1u) return (int)(u32)v;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return -1;
+      const u64 now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return -1; }
+      __nanosleep(100);
+    }
+  }
+}
 
 // Convert, scale and store the NCOLS accumulator values each lane holds for its row (32 rows per warp,
 // starting at `cbase`), through this warp's staging area so that global stores are coalesced: a round
@@ -594,13 +632,18 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   u64* acc_empty = acc_full + 2;                      // [2]
   u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  u64* sched = acc_empty + 4;                         // kSchedSlots 64-bit words behind the two 32-bit words above
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const u32 rank = cluster_ctarank();                 // 0 = leader (issues the MMAs), 1 = peer
   const int tiles_m = p.M / 256, tiles_n = (p.N + BN - 1) / BN;
   const int ktiles = (p.K + kBK - 1) / kBK;
   const int num_work = tiles_m * tiles_n * p.splitk;
-  const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+  const int ncl = gridDim.x >> 1;
+  const u32 sched0 = smem_u32(sched);
+  // the leader's first draw: its latency runs under the set-up below
+  unsigned first_item = 0u;
+  if (rank == 0 && threadIdx.x == 0) first_item = atomicAdd(p.counter, 1u);
   const u32 smem_base = smem_u32(smem);
   const u32 full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
   const u32 accf0 = smem_u32(acc_full), acce0 = smem_u32(acc_empty);
@@ -609,6 +652,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int s = 0; s < kStages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int a = 0; a < 2; a++) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 2 * kEpiWarps); }
     *abort_flag = 0;
+    for (int i = 0; i < kSchedSlots; i++) sched[i] = 0ull;      // tag 0 matches no entry
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -631,10 +675,31 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
     }
     const u32 leader_full0 = map_to_cta(full0, 0);    // the leader's `full` barriers in cluster address space
+    const u32 sched_peer0 = map_to_cta(sched0, 1);
+    const u32 last_draw = (u32)num_work + (u32)ncl - 1u;         // the draw that finds the counter complete
     int stage = 0; u32 phase = 0;
     u32 st_addr = smem_base;
     bool ok = true;
-    for (int w = cid; w < num_work && ok; w += ncl) {
+    u32 next_item = __shfl_sync(0xffffffffu, first_item, 0);     // leader: drawn by lane 0 in the prologue
+    for (u32 k = 0; ok; k++) {
+      int w;
+      if (rank == 0) {
+        // publish entry k to both CTAs, then draw entry k + 1 (needed only after this item's loads are issued)
+        w = (int)next_item;
+        if (lane == 0) {
+          const u32 slot = 8u * (k & (u32)(kSchedSlots - 1));
+          sched_publish(sched0 + slot, sched_peer0 + slot, k, next_item);
+          if (next_item == last_draw) atomicExch(p.counter, 0u);     // every draw of this launch has happened
+        }
+        if (w >= num_work) break;
+        unsigned drawn = 0u;
+        if (lane == 0) drawn = atomicAdd(p.counter, 1u);
+        next_item = __shfl_sync(0xffffffffu, drawn, 0);
+      } else {
+        w = sched_wait(sched0, k, abort_flag);
+        if (w < 0) { ok = false; break; }
+        if (w >= num_work) break;
+      }
       int mt, nt, z;
       decode_tile(w, tiles_m, tiles_n, mt, nt, z);
       const int kt0 = z * p.ktiles_per_split;
@@ -667,7 +732,10 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       u32 a_lo = a_lo0;
       u32 tile = 0;                                   // tiles done by this cluster
       bool ok = true;
-      for (int w = cid; w < num_work && ok; w += ncl, tile++) {
+      for (; ok; tile++) {
+        const int w = sched_wait(sched0, tile, abort_flag);
+        if (w < 0) { ok = false; break; }
+        if (w >= num_work) break;
         int mt, nt, z;
         decode_tile(w, tiles_m, tiles_n, mt, nt, z);
         const int kt0 = z * p.ktiles_per_split;
@@ -742,7 +810,10 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const u32 acce_leader0 = map_to_cta(acce0, 0);
     u32 tile = 0;
     bool ok = true;
-    for (int w = cid; w < num_work && ok; w += ncl, tile++) {
+    for (; ok; tile++) {
+      const int w = sched_wait(sched0, tile, abort_flag);
+      if (w < 0) { ok = false; break; }
+      if (w >= num_work) break;
       int mt, nt, zz;
       decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
       const u32 acc = tile & 1u;
@@ -851,7 +922,7 @@ static bool make_sf_map(CUtensorMap* map, const void* base, long long rows, long
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-struct DevInfo { int sms; bool attr128, attr256, attr_pair, attr_pair128, attr_pair192; };
+struct DevInfo { int sms; bool attr128, attr256, attr_pair, attr_pair128, attr_pair192; unsigned* counters; };
 static DevInfo* dev_info() {
   static DevInfo info[64];
   static bool init[64] = {false};
@@ -861,6 +932,9 @@ static DevInfo* dev_info() {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return nullptr;
     info[dev].sms = n; info[dev].attr128 = info[dev].attr256 = info[dev].attr_pair = info[dev].attr_pair128 = info[dev].attr_pair192 = false;
+    void* ctr = nullptr;
+    if (cudaGetSymbolAddress(&ctr, g_tile_counters) != cudaSuccess) return nullptr;
+    info[dev].counters = static_cast<unsigned*>(ctr);
     init[dev] = true;
   }
   return &info[dev];
@@ -986,6 +1060,10 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.atomic = (accumulate || splitk > 1) ? 1 : 0;
     pp.splitk = splitk;
     pp.ktiles_per_split = per;
+    // a counter of its own for every launch in flight: consecutive launches take consecutive slots, a slot comes
+    // round again 4096 launches later
+    static unsigned launch_seq = 0;
+    pp.counter = di->counters + (launch_seq++ & 4095u);
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
     const long long clusters = work < sms / 2 ? work : sms / 2;
     const unsigned grid = (unsigned)(2 * clusters);
@@ -1050,6 +1128,15 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
   if (rc != NVFP4_OK) return rc;
   return nvfp4_gemm(a, wsa, lda, b, wsb, ldb, c, c_dtype, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, accumulate, splitk,
                     status, stream);
+}
+
+// Clears the work counters of the pair kernel's scheduler on the current device: needed only after a launch was
+// abandoned (a bounded wait expired and the status word was set), which can leave a counter half-way.
+extern "C" int nvfp4_gemm_reset_scheduler(void) {
+  DevInfo* di = dev_info();
+  if (!di) return NVFP4_ERR_CUDA;
+  if (cudaMemset(di->counters, 0, sizeof(unsigned) * 4096) != cudaSuccess) return NVFP4_ERR_CUDA;
+  return NVFP4_OK;
 }
 
 extern "C" int nvfp4_gemm_set_sm_budget(int sms) {
