@@ -304,6 +304,8 @@ int nvfp4_gemm_set_sm_budget(int sms);
  * the counters of the current device.  Synchronises the device.  No reference counterpart.
  */
 int nvfp4_gemm_reset_scheduler(void);
+/* 1 (default): work items drawn at run time as described above; 0: dealt out in advance, cluster c takes items c, c + clusters, ...  Process-wide. */
+int nvfp4_gemm_set_scheduler(int dynamic);
 
 /*
  * Same product for operands whose scales are in the LINEAR layout (row strides ldsa / ldsb bytes):

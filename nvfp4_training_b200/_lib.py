@@ -28,6 +28,7 @@ SIGNATURES = {
     "nvfp4_amax_bf16_update": (_i, [_vp, _ll, _vp, _vp]),
     "nvfp4_set_pdl": (_i, [_i]),
     "nvfp4_gemm_reset_scheduler": (_i, []),
+    "nvfp4_gemm_set_scheduler": (_i, [_i]),
     "nvfp4_quant_rows": (_i, [_vp, _ll, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _u, _vp, _vp]),
     "nvfp4_quant_cols_rht": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _u, _i, _u, _vp, _vp]),
     "nvfp4_quant_tile": (_i, [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _u, _i, _u, _u, _vp, _vp, _vp]),

@@ -37,6 +37,7 @@ constexpr int kBKBytes = 128;       // bytes of K per stage row = 256 FP4 values
 constexpr int kBK = 256;            // FP4 values of K per stage
 constexpr int kEpiWarps = 8;         // two warps per 32-lane quadrant of tensor memory
 constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kPairThreads = kThreads + 32;   // CTA-pair kernel: one more warp, which draws the work items
 
 template <int BN>
 struct Cfg {
@@ -484,40 +485,55 @@ struct PairParams {
   int splitk;
   int ktiles_per_split;
   unsigned* counter;      // this launch's work counter (zero before the launch, zero again after it)
+  int dynamic;            // 1: items after a cluster's first are drawn from the counter; 0: dealt out in advance (item = cluster + k * clusters)
 };
 
 // ---- dynamic tile scheduler of the pair kernel
 // Work items are not dealt out in advance: a cluster takes the next item from a global counter whenever it is ready
 // for one.  A grid that finds some SMs occupied (a collective running beside the GEMM) then needs no tuning: the
-// clusters that do run share all the items, the ones that start late find none.  The leader CTA's producer warp draws
-// the numbers and publishes them to every role of both CTAs through a small queue in shared memory: entry k lives in
-// slot k % kSchedSlots as one 64-bit word {item, k + 1}, written with a single store (to the peer through
-// shared::cluster) and polled by its readers.  A slot is reused kSchedSlots entries later; no reader lags that far:
-// the producer runs at most kStages K tiles (at most kStages items) ahead of the MMA warp, the MMA warp at most two
-// items (accumulators) ahead of the epilogue, and the draw for the next entry happens one entry early: 7 + 2 + 1 < 16.
-// The counter resets itself: each cluster draws until it gets a number >= num_work, so exactly num_work + clusters
-// numbers are drawn per launch and whoever draws the last one stores zero.
+// clusters that do run share the items, the ones that start late do their first item and find no more.  A warp of
+// its own in the leader CTA draws the numbers, decodes them and publishes the tile coordinates to every role of both
+// CTAs through a small queue in shared memory: entry k lives in slot k % kSchedSlots as one 64-bit word (coordinates
+// and a tag derived from k), written with a single store (to the peer through shared::cluster) and polled by its
+// readers.  The drawing warp stays at most kSchedAhead entries ahead of the MMA warp (which posts the entry it is
+// working on), the epilogue is at most two entries (accumulators) behind the MMA warp, the producers are ahead of it:
+// nobody reads a slot that is being reused.  Why a warp of its own: a draw is a global atomic with a result, and under
+// the operand traffic of the GEMM its round trip is long; issued by the producer warp it cost 3-8 % on K = 2048
+// shapes (the same queue fed without atomics cost nothing).
+// A cluster's first item is its own index, later ones are clusters + draw.  The counter resets itself: each cluster
+// draws until its item would be >= num_work, so exactly num_work numbers are drawn per launch (num_work - clusters
+// items and one miss per cluster) and whoever draws the last one stores zero.
+constexpr int kSchedAhead = 4;
 constexpr int kSchedSlots = 16;
 __device__ unsigned g_tile_counters[4096];
 
-__device__ __forceinline__ void sched_publish(u32 slot_local, u32 slot_peer, u32 k, u32 item) {
-  const u64 v = ((u64)(k + 1u) << 32) | (u64)item;
+// Queue entry: tag (k + 1, 16 bits) | K slice (8 bits) | column tile (20 bits) | row tile (20 bits).  The leader's
+// producer decodes the item number once, off everybody's critical path; row tile 0xFFFFF says "no more items".
+constexpr u32 kSchedEnd = 0xFFFFFu;
+__device__ __forceinline__ u64 sched_pack(u32 k, u32 mt, u32 nt, u32 z) {
+  return ((u64)((k + 1u) & 0xFFFFu) << 48) | ((u64)z << 40) | ((u64)nt << 20) | (u64)mt;
+}
+__device__ __forceinline__ void sched_publish(u32 slot_local, u32 slot_peer, u64 v) {
   asm volatile("st.volatile.shared::cta.u64 [%0], %1;" ::"r"(slot_local), "l"(v) : "memory");
   asm volatile("st.volatile.shared::cluster.u64 [%0], %1;" ::"r"(slot_peer), "l"(v) : "memory");
 }
-// Entry k of this CTA's queue; -1 when the CTA is aborting or the bounded wait expired.
-__device__ __forceinline__ int sched_wait(u32 sched0, u32 k, volatile int* abort_flag) {
+// Entry k of this CTA's queue into (mt, nt, z); false when the CTA is aborting or the bounded wait expired.
+__device__ __forceinline__ bool sched_wait(u32 sched0, u32 k, volatile int* abort_flag, int& mt, int& nt, int& z) {
   const u32 addr = sched0 + 8u * (k & (u32)(kSchedSlots - 1));
+  const u32 tag = (k + 1u) & 0xFFFFu;
   u64 t0 = 0;
   for (u32 it = 1;; ++it) {
     u64 v;
     asm volatile("ld.volatile.shared::cta.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
-    if ((u32)(v >> 32) == k + 1u) return (int)(u32)v;
+    if ((u32)(v >> 48) == tag) {
+      mt = (int)((u32)v & 0xFFFFFu); nt = (int)((u32)(v >> 20) & 0xFFFFFu); z = (int)((u32)(v >> 40) & 0xFFu);
+      return true;
+    }
     if ((it & 63u) == 0u) {
-      if (*abort_flag) return -1;
+      if (*abort_flag) return false;
       const u64 now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return -1; }
+      else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
       __nanosleep(100);
     }
   }
@@ -615,7 +631,7 @@ __device__ __forceinline__ void decode_tile(int w, int tiles_m, int tiles_n, int
 }
 
 template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                       const PairParams p) {
@@ -633,17 +649,15 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   u32* tmem_slot = reinterpret_cast<u32*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   u64* sched = acc_empty + 4;                         // kSchedSlots 64-bit words behind the two 32-bit words above
+  volatile u32* mma_at = reinterpret_cast<volatile u32*>(sched + kSchedSlots);   // entry the leader's MMA warp works on
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const u32 rank = cluster_ctarank();                 // 0 = leader (issues the MMAs), 1 = peer
   const int tiles_m = p.M / 256, tiles_n = (p.N + BN - 1) / BN;
   const int ktiles = (p.K + kBK - 1) / kBK;
   const int num_work = tiles_m * tiles_n * p.splitk;
-  const int ncl = gridDim.x >> 1;
+  const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
   const u32 sched0 = smem_u32(sched);
-  // the leader's first draw: its latency runs under the set-up below
-  unsigned first_item = 0u;
-  if (rank == 0 && threadIdx.x == 0) first_item = atomicAdd(p.counter, 1u);
   const u32 smem_base = smem_u32(smem);
   const u32 full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
   const u32 accf0 = smem_u32(acc_full), acce0 = smem_u32(acc_empty);
@@ -653,6 +667,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int a = 0; a < 2; a++) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 2 * kEpiWarps); }
     *abort_flag = 0;
     for (int i = 0; i < kSchedSlots; i++) sched[i] = 0ull;      // tag 0 matches no entry
+    *mma_at = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -675,33 +690,19 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
     }
     const u32 leader_full0 = map_to_cta(full0, 0);    // the leader's `full` barriers in cluster address space
-    const u32 sched_peer0 = map_to_cta(sched0, 1);
-    const u32 last_draw = (u32)num_work + (u32)ncl - 1u;         // the draw that finds the counter complete
     int stage = 0; u32 phase = 0;
     u32 st_addr = smem_base;
     bool ok = true;
-    u32 next_item = __shfl_sync(0xffffffffu, first_item, 0);     // leader: drawn by lane 0 in the prologue
     for (u32 k = 0; ok; k++) {
-      int w;
-      if (rank == 0) {
-        // publish entry k to both CTAs, then draw entry k + 1 (needed only after this item's loads are issued)
-        w = (int)next_item;
-        if (lane == 0) {
-          const u32 slot = 8u * (k & (u32)(kSchedSlots - 1));
-          sched_publish(sched0 + slot, sched_peer0 + slot, k, next_item);
-          if (next_item == last_draw) atomicExch(p.counter, 0u);     // every draw of this launch has happened
-        }
-        if (w >= num_work) break;
-        unsigned drawn = 0u;
-        if (lane == 0) drawn = atomicAdd(p.counter, 1u);
-        next_item = __shfl_sync(0xffffffffu, drawn, 0);
-      } else {
-        w = sched_wait(sched0, k, abort_flag);
-        if (w < 0) { ok = false; break; }
-        if (w >= num_work) break;
-      }
       int mt, nt, z;
-      decode_tile(w, tiles_m, tiles_n, mt, nt, z);
+      if (k == 0 || !p.dynamic) {
+        const int w = cid + (int)k * ncl;
+        if (w >= num_work) break;
+        decode_tile(w, tiles_m, tiles_n, mt, nt, z);
+      } else {
+        if (!sched_wait(sched0, k, abort_flag, mt, nt, z)) { ok = false; break; }
+        if (mt == (int)kSchedEnd) break;
+      }
       const int kt0 = z * p.ktiles_per_split;
       const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
       const int ya = mt * 256 + (int)rank * 128, yb = nt * BN + (int)rank * (BN / 2);
@@ -733,11 +734,16 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       u32 tile = 0;                                   // tiles done by this cluster
       bool ok = true;
       for (; ok; tile++) {
-        const int w = sched_wait(sched0, tile, abort_flag);
-        if (w < 0) { ok = false; break; }
-        if (w >= num_work) break;
         int mt, nt, z;
-        decode_tile(w, tiles_m, tiles_n, mt, nt, z);
+        if (tile == 0 || !p.dynamic) {
+          const int w = cid + (int)tile * ncl;
+          if (w >= num_work) break;
+          decode_tile(w, tiles_m, tiles_n, mt, nt, z);
+        } else {
+          if (!sched_wait(sched0, tile, abort_flag, mt, nt, z)) { ok = false; break; }
+          if (mt == (int)kSchedEnd) break;
+        }
+        if (lane == 0) *mma_at = tile;                // the drawing warp may go kSchedAhead entries beyond this one
         const int kt0 = z * p.ktiles_per_split;
         const int kt1 = min(ktiles, kt0 + p.ktiles_per_split);
         const u32 acc = tile & 1u;
@@ -801,6 +807,36 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
       if (!ok && lane == 0 && p.status) atomicExch(p.status, 12);
     }
+  } else if (warp == 2 + kEpiWarps) {
+    // ------------------------------------------------------------------ work-item draws (leader CTA only, one lane)
+    if (p.dynamic && rank == 0 && lane == 0) {
+      const u32 sched_peer0 = map_to_cta(sched0, 1);
+      const u32 last_draw = (u32)num_work - 1u;       // the draw that finds the counter complete
+      bool fail = false;
+      for (u32 k = 1;; k++) {
+        // flow control against the MMA warp's position, bounded like every wait
+        u64 t0 = 0;
+        for (u32 it = 1; k > *mma_at + (u32)kSchedAhead; ++it) {
+          __nanosleep(200);
+          if ((it & 15u) == 0u) {
+            if (*abort_flag) { fail = true; break; }
+            const u64 now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; fail = true; break; }
+          }
+        }
+        if (fail) break;
+        const u32 drawn = atomicAdd(p.counter, 1u);
+        if (drawn == last_draw) atomicExch(p.counter, 0u);      // every draw of this launch has happened
+        const int w = ncl + (int)drawn;
+        int mt = (int)kSchedEnd, nt = 0, z = 0;
+        if (w < num_work) decode_tile(w, tiles_m, tiles_n, mt, nt, z);
+        const u32 slot = 8u * (k & (u32)(kSchedSlots - 1));
+        sched_publish(sched0 + slot, sched_peer0 + slot, sched_pack(k, (u32)mt, (u32)nt, (u32)z));
+        if (w >= num_work) break;
+      }
+      if (fail && p.status) atomicExch(p.status, 14);
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     constexpr int NC = C::kEpiCols;
@@ -811,11 +847,15 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     u32 tile = 0;
     bool ok = true;
     for (; ok; tile++) {
-      const int w = sched_wait(sched0, tile, abort_flag);
-      if (w < 0) { ok = false; break; }
-      if (w >= num_work) break;
       int mt, nt, zz;
-      decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
+      if (tile == 0 || !p.dynamic) {
+        const int w = cid + (int)tile * ncl;
+        if (w >= num_work) break;
+        decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
+      } else {
+        if (!sched_wait(sched0, tile, abort_flag, mt, nt, zz)) { ok = false; break; }
+        if (mt == (int)kSchedEnd) break;
+      }
       const u32 acc = tile & 1u;
       {
         const u32 bar = BN == 256 ? accf0 : accf0 + 8 * acc;
@@ -904,6 +944,7 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static int g_dynamic_sched = 1;   // pair kernel: 1 = work items drawn at run time, 0 = dealt out in advance
 static int g_sm_budget = 0;  // 0 = all SMs; otherwise the persistent GEMM grids use at most this many (even) SMs
 static int g_pair_bn = 0;    // 0 = heuristic, 128 / 192 / 256 = forced tile width of the CTA-pair kernel
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
@@ -1064,6 +1105,8 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     // round again 4096 launches later
     static unsigned launch_seq = 0;
     pp.counter = di->counters + (launch_seq++ & 4095u);
+    // (items shorter than four K tiles stay dealt out in advance: one draw takes about as long as such an item)
+    pp.dynamic = (g_dynamic_sched && per >= 4 && splitk <= 255 && (M / 256) < (int)kSchedEnd && (N + pbn - 1) / pbn <= (int)kSchedEnd) ? 1 : 0;
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
     const long long clusters = work < sms / 2 ? work : sms / 2;
     const unsigned grid = (unsigned)(2 * clusters);
@@ -1075,7 +1118,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
           return NVFP4_ERR_CUDA;                                                                                           \
         di->FLAG = true;                                                                                                   \
       }                                                                                                                    \
-      if (nvfp4_launch_kernel(gemm_nvf4_pair_kernel<BN_>, dim3(grid), dim3(kThreads), PairCfg<BN_>::kSmemBytes, st, ma, mb,    \
+      if (nvfp4_launch_kernel(gemm_nvf4_pair_kernel<BN_>, dim3(grid), dim3(kPairThreads), PairCfg<BN_>::kSmemBytes, st, ma, mb,\
                               msa, msb, pp) != cudaSuccess) {                                                               \
         (void)cudaGetLastError();                                                                                          \
         return NVFP4_ERR_CUDA;                                                                                             \
@@ -1128,6 +1171,11 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
   if (rc != NVFP4_OK) return rc;
   return nvfp4_gemm(a, wsa, lda, b, wsb, ldb, c, c_dtype, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, accumulate, splitk,
                     status, stream);
+}
+
+extern "C" int nvfp4_gemm_set_scheduler(int dynamic) {
+  g_dynamic_sched = dynamic ? 1 : 0;
+  return NVFP4_OK;
 }
 
 // Clears the work counters of the pair kernel's scheduler on the current device: needed only after a launch was

@@ -207,3 +207,34 @@ def test_cols_rht_fallback_kernel_large(mods):
     assert np.array_equal(u8(q.d), codes)
     assert np.array_equal(O.unswizzle_scales(u8(q.s), C, M // 16), scales)
     assert q.gs.item() == float(gs)
+
+
+def test_gemm_items_dealt_in_advance_equal_drawn_at_run_time():
+    """The CTA-pair kernel with its work items drawn at run time (default) and dealt out in advance: same bytes out
+    (every item is computed once, by whichever cluster takes it), under an SM budget that makes every cluster walk
+    many items, for bf16, FP32 and accumulating outputs."""
+    from nvfp4_training_b200 import _lib as L, nvq
+    lib = L.load()
+    M, N, K = 1024, 2816, 2304
+    qa = nvq.quant_rows(to_dev(make_x(1, M, K)))
+    qb = nvq.quant_rows(to_dev(make_w(2, N, K)))
+    outs = {}
+    try:
+        for mode in (1, 0):
+            assert lib.nvfp4_gemm_set_scheduler(mode) == 0
+            for budget in (0, 4):
+                lib.nvfp4_gemm_set_sm_budget(budget)
+                y16 = nvq.mm(qa, qb)
+                y32 = nvq.mm(qa, qb, out_dtype=torch.float32)
+                acc = torch.ones(M, N, device="cuda")
+                nvq.mm(qa, qb, out_dtype=torch.float32, out=acc, accumulate=True)
+                outs[(mode, budget)] = (y16, y32, acc)
+    finally:
+        lib.nvfp4_gemm_set_scheduler(1)
+        lib.nvfp4_gemm_set_sm_budget(0)
+    L.check_status()
+    ref = outs[(0, 0)]
+    for key, got in outs.items():
+        for a, b in zip(ref, got):
+            assert torch.equal(a, b), key
+    assert ref[1].abs().max().item() > 0
