@@ -304,7 +304,9 @@ int nvfp4_gemm_set_sm_budget(int sms);
  * the counters of the current device.  Synchronises the device.  No reference counterpart.
  */
 int nvfp4_gemm_reset_scheduler(void);
-/* 1 (default): work items drawn at run time as described above; 0: dealt out in advance, cluster c takes items c, c + clusters, ...  Process-wide. */
+/* 1 (default): a cluster's first item is its own index, later ones are drawn at run time; 2: the first one is drawn
+ * too (half a microsecond more per launch; for GEMMs that run beside another kernel: a cluster that starts late then
+ * leaves no item waiting for it); 0: dealt out in advance, cluster c takes items c, c + clusters, ...  Process-wide. */
 int nvfp4_gemm_set_scheduler(int dynamic);
 
 /*

@@ -500,9 +500,11 @@ struct PairParams {
 // nobody reads a slot that is being reused.  Why a warp of its own: a draw is a global atomic with a result, and under
 // the operand traffic of the GEMM its round trip is long; issued by the producer warp it cost 3-8 % on K = 2048
 // shapes (the same queue fed without atomics cost nothing).
-// A cluster's first item is its own index, later ones are clusters + draw.  The counter resets itself: each cluster
-// draws until its item would be >= num_work, so exactly num_work numbers are drawn per launch (num_work - clusters
-// items and one miss per cluster) and whoever draws the last one stores zero.
+// Mode 1: a cluster's first item is its own index (no round trip to the counter before the first load), later ones
+// are clusters + draw; a cluster that starts late still has that first item to do.  Mode 2: the first item is drawn
+// as well (about half a microsecond more per launch), so a late cluster finds nothing left: the mode for GEMMs that
+// run beside a collective.  The counter resets itself: each cluster draws until it misses, so exactly num_work
+// (mode 2: num_work + clusters) numbers are drawn per launch and whoever draws the last one stores zero.
 constexpr int kSchedAhead = 4;
 constexpr int kSchedSlots = 16;
 __device__ unsigned g_tile_counters[4096];
@@ -695,7 +697,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     bool ok = true;
     for (u32 k = 0; ok; k++) {
       int mt, nt, z;
-      if (k == 0 || !p.dynamic) {
+      if ((k == 0 && p.dynamic != 2) || !p.dynamic) {
         const int w = cid + (int)k * ncl;
         if (w >= num_work) break;
         decode_tile(w, tiles_m, tiles_n, mt, nt, z);
@@ -735,7 +737,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       bool ok = true;
       for (; ok; tile++) {
         int mt, nt, z;
-        if (tile == 0 || !p.dynamic) {
+        if ((tile == 0 && p.dynamic != 2) || !p.dynamic) {
           const int w = cid + (int)tile * ncl;
           if (w >= num_work) break;
           decode_tile(w, tiles_m, tiles_n, mt, nt, z);
@@ -811,9 +813,12 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // ------------------------------------------------------------------ work-item draws (leader CTA only, one lane)
     if (p.dynamic && rank == 0 && lane == 0) {
       const u32 sched_peer0 = map_to_cta(sched0, 1);
-      const u32 last_draw = (u32)num_work - 1u;       // the draw that finds the counter complete
+      // first items dealt out (dynamic == 1): clusters + draw, num_work draws in all; first items drawn too
+      // (dynamic == 2): item = draw, num_work + clusters draws in all
+      const bool all = p.dynamic == 2;
+      const u32 last_draw = (u32)num_work - 1u + (all ? (u32)ncl : 0u);       // the draw that finds the counter complete
       bool fail = false;
-      for (u32 k = 1;; k++) {
+      for (u32 k = all ? 0u : 1u;; k++) {
         // flow control against the MMA warp's position, bounded like every wait
         u64 t0 = 0;
         for (u32 it = 1; k > *mma_at + (u32)kSchedAhead; ++it) {
@@ -828,7 +833,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (fail) break;
         const u32 drawn = atomicAdd(p.counter, 1u);
         if (drawn == last_draw) atomicExch(p.counter, 0u);      // every draw of this launch has happened
-        const int w = ncl + (int)drawn;
+        const int w = (all ? 0 : ncl) + (int)drawn;
         int mt = (int)kSchedEnd, nt = 0, z = 0;
         if (w < num_work) decode_tile(w, tiles_m, tiles_n, mt, nt, z);
         const u32 slot = 8u * (k & (u32)(kSchedSlots - 1));
@@ -848,7 +853,7 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     bool ok = true;
     for (; ok; tile++) {
       int mt, nt, zz;
-      if (tile == 0 || !p.dynamic) {
+      if ((tile == 0 && p.dynamic != 2) || !p.dynamic) {
         const int w = cid + (int)tile * ncl;
         if (w >= num_work) break;
         decode_tile(w, tiles_m, tiles_n, mt, nt, zz);
@@ -944,7 +949,7 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int g_dynamic_sched = 1;   // pair kernel: 1 = work items drawn at run time, 0 = dealt out in advance
+static int g_dynamic_sched = 1;   // pair kernel: 0 = work items dealt out in advance, 1 = drawn at run time after a cluster's first, 2 = all drawn
 static int g_sm_budget = 0;  // 0 = all SMs; otherwise the persistent GEMM grids use at most this many (even) SMs
 static int g_pair_bn = 0;    // 0 = heuristic, 128 / 192 / 256 = forced tile width of the CTA-pair kernel
 static int g_force_bn = 0;   // 0 = heuristic, 128 / 256 = forced one-CTA tile width, 512 = CTA-pair kernel (tuning and tests)
@@ -1106,7 +1111,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     static unsigned launch_seq = 0;
     pp.counter = di->counters + (launch_seq++ & 4095u);
     // (items shorter than four K tiles stay dealt out in advance: one draw takes about as long as such an item)
-    pp.dynamic = (g_dynamic_sched && per >= 4 && splitk <= 255 && (M / 256) < (int)kSchedEnd && (N + pbn - 1) / pbn <= (int)kSchedEnd) ? 1 : 0;
+    pp.dynamic = (g_dynamic_sched && per >= 4 && splitk <= 255 && (M / 256) < (int)kSchedEnd && (N + pbn - 1) / pbn <= (int)kSchedEnd) ? g_dynamic_sched : 0;
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
     const long long clusters = work < sms / 2 ? work : sms / 2;
     const unsigned grid = (unsigned)(2 * clusters);
@@ -1174,7 +1179,7 @@ extern "C" int nvfp4_gemm_linear(const void* a, const void* sa, long long lda, l
 }
 
 extern "C" int nvfp4_gemm_set_scheduler(int dynamic) {
-  g_dynamic_sched = dynamic ? 1 : 0;
+  g_dynamic_sched = dynamic < 0 ? 0 : dynamic > 2 ? 2 : dynamic;
   return NVFP4_OK;
 }
 

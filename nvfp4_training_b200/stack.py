@@ -308,11 +308,15 @@ class LinearStack:
             with torch.cuda.graph(g, pool=pool):
                 self._fwd_block(projs)
             self.graphs_fwd.append(g)
-        # backward graphs run beside the gradient all-reduce: keep `comm_sms` SMs out of the GEMM grids
+        # backward graphs run beside the gradient all-reduce: either keep `comm_sms` SMs out of the GEMM grids, or
+        # (no budget) let every cluster draw even its first work item at run time, so that clusters which find
+        # their SM taken by the collective and start late leave no item waiting for them
         lib = _lib.load()
         if self.comm_sms:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             lib.nvfp4_gemm_set_sm_budget(max(2, sms - self.comm_sms))
+        elif self.group is not None or (torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1):
+            lib.nvfp4_gemm_set_scheduler(2)
         try:
             for first, store in ((True, self.graphs_bwd_first), (False, self.graphs_bwd)):
                 for projs in reversed(self.blocks):
@@ -322,6 +326,7 @@ class LinearStack:
                     store.append(g)
         finally:
             lib.nvfp4_gemm_set_sm_budget(0)
+            lib.nvfp4_gemm_set_scheduler(1)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, pool=pool):
             self.refresh_weights()           # buffers exist already: the in-place form is captured

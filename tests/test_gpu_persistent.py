@@ -220,7 +220,7 @@ def test_gemm_items_dealt_in_advance_equal_drawn_at_run_time():
     qb = nvq.quant_rows(to_dev(make_w(2, N, K)))
     outs = {}
     try:
-        for mode in (1, 0):
+        for mode in (1, 2, 0):
             assert lib.nvfp4_gemm_set_scheduler(mode) == 0
             for budget in (0, 4):
                 lib.nvfp4_gemm_set_sm_budget(budget)
