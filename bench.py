@@ -630,13 +630,14 @@ def run_ours(args):
     torch.cuda.set_device(local)
     _lib.load().nvfp4_set_pdl(1 if args.pdl else 0)
     if args.comm_sms is None:
-        # SMs kept out of the backward GEMM grids for NCCL.  The GEMM draws its tiles at run time, so a grid that finds
-        # SMs taken by the collective needs no budget: the clusters that run share the work and the late ones find
-        # none (a few microseconds of tail per launch).  With 2 ranks the collective is in flight for about a third of
-        # the backward pass and no budget wins (75.2-77.1 ms per step against 77.2-79.7 with 16 SMs set aside, same
-        # boxes); with 8 ranks it is in flight almost all the time, the tail would be paid on nearly every launch, and
-        # the budget measured best earlier (32 SMs) is kept.
-        args.comm_sms = 32 if world >= 8 else 0
+        # SMs kept out of the persistent backward grids (GEMM, quantizer) for NCCL.  The GEMM draws its tiles at run
+        # time, so a grid that finds SMs taken by the collective needs no budget: the clusters that run share the work
+        # and the late ones find none.  With 2 ranks the collective is in flight for about a third of the backward pass
+        # and no budget wins (75.2-77.1 ms per step against 77.2-79.7 with 16 SMs set aside, same boxes); with 4 ranks
+        # it is in flight half the time and a budget wins again (42.4 ms with 24 SMs, 42.7 with 32, 44.1 without: the
+        # quantizer's CTAs own fixed shares of tiles and suffer from starting late); with 8 ranks it is in flight
+        # almost all the time and the budget measured best earlier (32 SMs) is kept.
+        args.comm_sms = 0 if world <= 2 else 24 if world < 8 else 32
     if not args.nccl_ctas:
         args.nccl_ctas = 32
     if world > 1:
@@ -924,7 +925,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
-                    help="SMs kept out of the backward GEMM grids for NCCL when N > 1 (default: 32 at N >= 8, else 0)")
+                    help="SMs kept out of the persistent backward grids for NCCL when N > 1 (default: 0 at N = 2, 24 at N = 4, 32 at N >= 8)")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default 32)")
     ap.add_argument("--no-wgrad-stream", action="store_true",
                     help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")

@@ -290,9 +290,10 @@ int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, cons
 int nvfp4_gemm_force_tile_n(int bn);
 
 /*
- * Cap the number of SMs the persistent GEMM grids occupy (0 = all).  Meant for data-parallel runs:
- * leaving a few SMs free lets the NCCL all-reduce kernels of the weight gradients run beside the
- * GEMMs instead of delaying their last CTAs.  Process-wide; takes effect for later calls (a captured
+ * Cap the number of SMs the persistent grids occupy (0 = all): the GEMM, and the one-read quantizer, the tile
+ * kernel and the ring emitter, whose CTAs each own a fixed share of the tiles or rows (a CTA that finds its SM taken
+ * and starts late would finish a whole share late).  Meant for data-parallel runs: leaving a few SMs free lets the
+ * NCCL all-reduce kernels of the weight gradients run beside them.  Process-wide; takes effect for later calls (a captured
  * CUDA graph keeps the grid it was captured with).  No reference counterpart (single GPU).
  */
 int nvfp4_gemm_set_sm_budget(int sms);

@@ -218,6 +218,8 @@ static int launch_ring(const RingParams& p, int grid, size_t smem, cudaStream_t 
 
 using namespace nvfp4;
 
+int nvfp4_sm_budget_value();   // gemm.cu: nvfp4_gemm_set_sm_budget
+
 // Whether the ring kernel takes this call (otherwise the warp-per-row kernel of emit_ops.cu runs).
 bool nvfp4_emit_rows_ring_accepts(const void* x, long long ldx, int T, int C, const void* codes) {
   if (T <= 0 || C <= 0 || (C & 255) || C > kRingMaxCols || ldx < C) return false;
@@ -243,6 +245,7 @@ int nvfp4_emit_rows_ring_launch(const void* x, long long ldx, int T, int C, void
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
   }
+  { const int b = nvfp4_sm_budget_value(); if (b > 0 && b < sms) sms = b; }   // SMs left to a collective running beside this kernel
   int grid = sms;
   if (T < grid * kRingWarps) grid = (T + kRingWarps - 1) / kRingWarps;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -1192,6 +1192,9 @@ extern "C" int nvfp4_gemm_reset_scheduler(void) {
   return NVFP4_OK;
 }
 
+// The budget as the persistent quantizer / emitter grids read it (0 = none).
+int nvfp4_sm_budget_value() { return g_sm_budget; }
+
 extern "C" int nvfp4_gemm_set_sm_budget(int sms) {
   if (sms < 0 || sms == 1) return NVFP4_ERR_SHAPE;   // the CTA-pair grids need at least one SM pair
   g_sm_budget = sms;

@@ -512,6 +512,8 @@ static int launch_tc_mode(const CUtensorMap& map, const TcParams& p, int grid, c
 
 using namespace nvfp4;
 
+int nvfp4_sm_budget_value();   // gemm.cu: nvfp4_gemm_set_sm_budget
+
 // Whether the tensor-core-fed kernel takes this call (shape and alignment); otherwise the scalar tile kernel runs.
 bool nvfp4_quant_tc_accepts(const void* x, long long ldx, int M, int C, const void* codes_r, const void* scales_r,
                             const void* codes_c, const void* scales_c) {
@@ -547,6 +549,7 @@ int nvfp4_quant_tc_launch(const void* x, long long ldx, int M, int C, void* code
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
   }
   const long long ntiles = (long long)(M / kQTok) * (C / kQCol);
+  { const int b = nvfp4_sm_budget_value(); if (b > 0 && b < sms) sms = b; }   // SMs left to a collective running beside this kernel
   int grid = 2 * sms;
   if (ntiles < grid) grid = (int)ntiles;
   switch (rounding) {

@@ -307,6 +307,8 @@ static int launch_tile_mode(const CUtensorMap& map, const TileParams& p, int gri
 
 using namespace nvfp4;
 
+int nvfp4_sm_budget_value();   // gemm.cu: nvfp4_gemm_set_sm_budget
+
 // the tensor-core-fed kernel (quant_mma.cu)
 bool nvfp4_quant_tc_accepts(const void* x, long long ldx, int M, int C, const void* codes_r, const void* scales_r,
                             const void* codes_c, const void* scales_c);
@@ -361,6 +363,7 @@ extern "C" int nvfp4_quant_tile(const void* x, long long ldx, int M, int C, void
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
   }
   const long long ntiles = (long long)(M / kTileTok) * (C / kTileCol);
+  { const int b = nvfp4_sm_budget_value(); if (b > 0 && b < sms) sms = b; }   // SMs left to a collective running beside this kernel
   int grid = 2 * sms;
   if (ntiles < grid) grid = (int)ntiles;
   switch (rounding) {
@@ -394,6 +397,7 @@ extern "C" int nvfp4_emit_cols(const void* x, long long ldx, int M, int C, void*
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
   }
   const long long ntiles = (long long)(M / kTileTok) * (C / kTileCol);
+  { const int b = nvfp4_sm_budget_value(); if (b > 0 && b < sms) sms = b; }   // SMs left to a collective running beside this kernel
   int grid = 2 * sms;
   if (ntiles < grid) grid = (int)ntiles;
   if (sr == 2) return launch_tile<NVFP4_EMIT_SR_HW, false, true>(map, p, grid, st);
