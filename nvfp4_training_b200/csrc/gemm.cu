@@ -19,6 +19,8 @@
 // advanced by adds, high words are constants): a single thread feeds the whole tensor core.
 // Every mbarrier wait is bounded: on expiry the CTA raises an abort flag, reports a code through
 // `status`, lets copies in flight land, frees its tensor memory and returns.
+#include <atomic>
+
 #include "tma.cuh"
 
 // Waits of warps that have nothing else to do (producer waiting for a free stage, epilogue waiting
@@ -1108,8 +1110,8 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.ktiles_per_split = per;
     // a counter of its own for every launch in flight: consecutive launches take consecutive slots, a slot comes
     // round again 4096 launches later
-    static unsigned launch_seq = 0;
-    pp.counter = di->counters + (launch_seq++ & 4095u);
+    static std::atomic<unsigned> launch_seq{0};
+    pp.counter = di->counters + (launch_seq.fetch_add(1u, std::memory_order_relaxed) & 4095u);
     // (items shorter than four K tiles stay dealt out in advance: one draw takes about as long as such an item)
     pp.dynamic = (g_dynamic_sched && per >= 4 && splitk <= 255 && (M / 256) < (int)kSchedEnd && (N + pbn - 1) / pbn <= (int)kSchedEnd) ? g_dynamic_sched : 0;
     const long long work = (long long)(M / 256) * ((N + pbn - 1) / pbn) * splitk;
