@@ -651,7 +651,7 @@ def run_ours(args):
     mb, n_micro = plan["microbatch"], plan["n_micro"]
     stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=0, input_seed=1000 + rank, use_graphs=not args.no_graphs,
                         comm_sms=args.comm_sms if world > 1 else 0, ar_blocks=args.ar_blocks,
-                        wgrad_side_stream=not args.no_wgrad_stream)
+                        wgrad_side_stream=not args.no_wgrad_stream, overlap_refresh=not args.no_overlap_refresh)
     if not args.no_graphs:
         stack.capture()
     do_ar = world > 1
@@ -685,12 +685,7 @@ def run_ours(args):
     launches_per_step = n_micro * stack.kernels_per_microbatch() + stack.n_proj * 2
 
     def e2e_step():
-        stack.refresh_weights()
-        for m in range(n_micro):
-            stack.x_pool["qkv"].copy_(host_x, non_blocking=True)
-            stack.microbatch(last=(m == n_micro - 1), do_allreduce=do_ar, first=(m == 0))
-        if do_ar:
-            torch.cuda.current_stream().wait_stream(stack.comm_stream)
+        stack.step(n_micro, do_ar, before_microbatch=lambda m: stack.x_pool["qkv"].copy_(host_x, non_blocking=True))
         host_out.copy_(last.gw.view(-1)[:1024], non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e2e_steps = max(1, min(args.steps, 5))
@@ -926,6 +921,8 @@ def main():
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs kept out of the persistent backward grids for NCCL when N > 1 (default: 0 at N = 2, 24 at N = 4, 32 at N >= 8)")
+    ap.add_argument("--no-overlap-refresh", action="store_true",
+                    help="re-quantize all weights at the start of a step instead of block by block behind the backward pass")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default 32)")
     ap.add_argument("--no-wgrad-stream", action="store_true",
                     help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")

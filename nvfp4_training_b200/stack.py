@@ -89,7 +89,7 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor", wgrad_side_stream=True):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor", wgrad_side_stream=True, overlap_refresh=True):
         """`seed` initialises the weights (the same on every rank of a data-parallel job: replicated
         weights), `input_seed` the synthetic activation / gradient pools (different per rank: each rank
         holds its own rows of the batch; default seed + 1000).
@@ -99,6 +99,14 @@ class LinearStack:
         GEMM epilogue."""
         assert mode in ("tensor", "emit")
         self.mode = mode
+        # a block's weights are re-quantized on the side stream right after the block's gradients are reduced (where
+        # a trainer would apply the block's optimizer update first), under the rest of the backward pass, instead of
+        # all weights at the start of the next step
+        self.overlap_refresh = overlap_refresh
+        self.after_reduce = None      # optional callable(block_index, projs), run on the side stream between a block's
+        #                               all-reduce and its re-quantization: the place of the block's optimizer update
+        self._weights_fresh = False
+        self.graphs_refresh_blk = None
         # weight-gradient GEMMs run on a side stream, joined at the end of each block's backward: they are off the
         # critical chain amax -> quantize -> dgrad, and fill the SMs that chain's kernels leave idle in their last waves
         self.wgrad_stream = torch.cuda.Stream(device=device) if wgrad_side_stream else None
@@ -189,20 +197,25 @@ class LinearStack:
         torch.mul(self.amax_cur.view(torch.float32).clamp(min=1e-30), EMIT_MARGIN, out=self.amax_use)
         self.amax_cur.zero_()
 
+    def _refresh_block(self, projs):
+        lo, hi = projs[0].lid, projs[-1].lid + 1
+        self.w_am[lo:hi].zero_()            # one fill for the block's amax words: the rest is a chain of kernels
+        for p in projs:
+            am = nvq.amax(p.w, out=self.w_am[p.lid:p.lid + 1], clear=False)
+            if p.q is None:
+                p.q, p.qt = nvq.quant_w2d(p.w, am=am)
+            else:
+                nvq.quant_w2d(p.w, am=am, out=(p.q, p.qt))      # in place: captured graphs keep these buffers
+
     def refresh_weights(self):
         """Quantize every weight once per optimizer step (the small-model/fp4torch.py:71-84 scheme).
         After `capture()` the 2 x 81 launches are one graph replay."""
+        self._weights_fresh = True
         if self.graph_refresh is not None:
             self.graph_refresh.replay()
             return
-        self.w_am.zero_()                   # one fill for all weights' amax words: the rest is a chain of kernels
         for projs in self.blocks:
-            for p in projs:
-                am = nvq.amax(p.w, out=self.w_am[p.lid:p.lid + 1], clear=False)
-                if p.q is None:
-                    p.q, p.qt = nvq.quant_w2d(p.w, am=am)
-                else:
-                    nvq.quant_w2d(p.w, am=am, out=(p.q, p.qt))      # in place: captured graphs keep these buffers
+            self._refresh_block(projs)
 
     def zero_grads(self):
         for projs in self.blocks:
@@ -331,6 +344,14 @@ class LinearStack:
         with torch.cuda.graph(g, pool=pool):
             self.refresh_weights()           # buffers exist already: the in-place form is captured
         self.graph_refresh = g
+        # per-block refresh graphs for the side stream: they run beside the backward graphs, so they get a pool of
+        # their own (they allocate nothing: every output exists)
+        self.graphs_refresh_blk = []
+        for projs in self.blocks:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._refresh_block(projs)
+            self.graphs_refresh_blk.append(g)
         torch.cuda.synchronize()
 
     def kernels_per_microbatch(self):
@@ -356,24 +377,39 @@ class LinearStack:
                 (self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
             else:
                 self._bwd_block(projs, first=first)
-            if last and do_allreduce and (nblk - 1 - i) in self.ar_after:
+            b = nblk - 1 - i
+            reduce_now = last and do_allreduce and b in self.ar_after
+            if reduce_now or (last and (self.overlap_refresh or self.after_reduce is not None)):
                 ev = torch.cuda.Event()
                 ev.record(cur)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ev)
-                    allreduce_sum_([self.ar_after[nblk - 1 - i]], self.group)
+                    if reduce_now:
+                        allreduce_sum_([self.ar_after[b]], self.group)
+                    if self.after_reduce is not None:
+                        self.after_reduce(b, projs)
+                    if self.overlap_refresh:
+                        # the block's weights for the next step
+                        if self.use_graphs and self.graphs_refresh_blk is not None:
+                            self.graphs_refresh_blk[b].replay()
+                        else:
+                            self._refresh_block(projs)
         if self.mode == "emit":
             self.roll_amax()
         return works
 
-    def step(self, n_micro, do_allreduce):
-        """One optimizer step's worth of this path: re-quantize weights, clear dW, n_micro
-        microbatches (the first overwrites dW, the others add), all-reduce.  Leaves the summed FP32
-        gradients in `p.gw`."""
+    def step(self, n_micro, do_allreduce, before_microbatch=None):
+        """One optimizer step's worth of this path: n_micro microbatches (the first overwrites dW, the others add),
+        all-reduce, every weight re-quantized once (block by block behind the last microbatch's backward pass, or
+        all at the start when `overlap_refresh` is off or the weights have never been quantized).  Leaves the summed
+        FP32 gradients in `p.gw`.  `before_microbatch(m)`: called before each microbatch, e.g. to stage its input."""
         if self.mode == "emit" and not self._calibrated:
             self.calibrate()
-        self.refresh_weights()
+        if not (self.overlap_refresh and self._weights_fresh):
+            self.refresh_weights()           # otherwise the previous step re-quantized each block behind its backward
         for m in range(n_micro):
+            if before_microbatch is not None:
+                before_microbatch(m)
             self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce, first=(m == 0))
-        if do_allreduce:
+        if do_allreduce or self.overlap_refresh or self.after_reduce is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)

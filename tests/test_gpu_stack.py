@@ -183,3 +183,46 @@ def test_amax_update_keeps_the_larger_value():
     assert words[1].item() == (x * 4).abs().max().item()
     assert words[2].item() == 0.0
     assert nvq.amax(x).item() == words[0].item()
+
+
+def test_stack_weights_requantized_behind_the_backward_pass():
+    """`overlap_refresh`: a block's weights are re-quantized on the side stream right after the block's backward (and
+    all-reduce), after the `after_reduce` hook where a trainer updates them, instead of all at the start of the next
+    step.  With a hook that changes the weights every step, after three steps the quantized weights give the same
+    forward output as those of a stack that re-quantizes everything at the start of each step (so the overlapped
+    refresh saw the updated weights), bit for bit, with graphs and without; the gradients agree as well."""
+    from nvfp4_training_b200 import _lib
+    from nvfp4_training_b200.stack import LinearStack, StackConfig
+    cfg = StackConfig(vocab=512, d=256, layers=2, heads=2, kv_heads=1, ff=384, lm_head=True)
+
+    def update(b, projs):
+        for p in projs:
+            p.w.mul_(1.25)           # stands for the block's optimizer update
+
+    grads, outs = [], []
+    for overlap, graphs in ((True, True), (False, True), (True, False), (False, False)):
+        st = LinearStack(cfg, 256, torch.device("cuda"), seed=7, use_graphs=graphs, overlap_refresh=overlap)
+        st.after_reduce = update
+        if graphs:
+            st.capture()
+        out = []
+        for _ in range(3):
+            st.step(2, do_allreduce=False)
+            torch.cuda.synchronize()
+            out.append([p.gw.clone() for blk in st.blocks for p in blk])
+        grads.append(out)
+        if not overlap:
+            st.refresh_weights()     # what the next step would start with
+        for projs in st.blocks:
+            st._fwd_block(projs, keep=True)
+        torch.cuda.synchronize()
+        outs.append([p.y.clone() for blk in st.blocks for p in blk])
+    _lib.check_status()
+    for other in outs[1:]:
+        for y0, y1 in zip(outs[0], other):
+            assert torch.equal(y0, y1)
+    assert outs[0][0].abs().max().item() > 0
+    for other in grads[1:]:
+        for s0, s1 in zip(grads[0], other):
+            for g0, g1 in zip(s0, s1):
+                assert torch.equal(g0, g1)
