@@ -639,7 +639,7 @@ def run_ours(args):
         # almost all the time and the budget measured best earlier (32 SMs) is kept.
         args.comm_sms = 0 if world <= 2 else 24 if world < 8 else 32
     if not args.nccl_ctas:
-        args.nccl_ctas = 32
+        args.nccl_ctas = args.comm_sms if args.comm_sms > 0 else 32      # NCCL stays inside the SMs set aside for it
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
@@ -923,7 +923,7 @@ def main():
                     help="SMs kept out of the persistent backward grids for NCCL when N > 1 (default: 0 at N = 2, 24 at N = 4, 32 at N >= 8)")
     ap.add_argument("--no-overlap-refresh", action="store_true",
                     help="re-quantize all weights at the start of a step instead of block by block behind the backward pass")
-    ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default 32)")
+    ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default: --comm-sms, or 32 when no SMs are set aside)")
     ap.add_argument("--no-wgrad-stream", action="store_true",
                     help="weight-gradient GEMMs on the main stream instead of a side stream beside the dgrad chain")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch of the library's kernels (off by default)")
