@@ -40,3 +40,20 @@ def test_check_status_reads_both_words():
     out = ctypes.c_int(-1)
     L.check(L.load().nvfp4_quant_tile_status(ctypes.byref(out), 0), "status")
     assert out.value == 0
+
+
+def test_scheduler_reset_entry_point():
+    """`nvfp4_gemm_reset_scheduler` clears the work counters of the CTA-pair GEMM (needed only after an abandoned
+    launch): callable at any time between launches, GEMMs before and after it give the same bytes."""
+    import torch
+    from nvfp4_training_b200 import _lib as L, nvq
+    lib = L.load()
+    torch.manual_seed(0)
+    qa = nvq.quant_rows(torch.randn(512, 2048, device="cuda").bfloat16())
+    qb = nvq.quant_rows(torch.randn(768, 2048, device="cuda").bfloat16())
+    y0 = nvq.mm(qa, qb)
+    torch.cuda.synchronize()
+    assert lib.nvfp4_gemm_reset_scheduler() == 0
+    y1 = nvq.mm(qa, qb)
+    assert torch.equal(y0, y1) and y0.abs().max().item() > 0
+    L.check_status()
