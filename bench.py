@@ -350,7 +350,7 @@ def isolated_kernels(cfg, T, peaks):
     achieved = tot_flops / tot_time / 1e12
     fp4_peak = 4.0 * peaks["bf16_tflops"]
     roof = {"bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
-            "traffic": None, "kernel": "gemm_nvf4_kernel (tcgen05.mma kind::mxf4nvf4 block16)",
+            "traffic": None, "kernel": "gemm_nvf4_pair_kernel (tcgen05.mma cta_group::2 kind::mxf4nvf4 block16)",
             "peak_basis": "4 x cuBLAS bf16 burst TFLOP/s (dense FP4 : bf16 = 4 : 1 on B200)",
             "frac_of_nominal_9000": achieved / 9000.0,
             "how": "all 15 GEMM shapes of the step timed alone with CUDA events, weighted by launches per step",
