@@ -610,6 +610,23 @@ def qref_rows(x):
     return codes.reshape(T, C), sbyte, gs
 
 
+def qref_rows_gs(x, gs):
+    """`q_rows_gs` of small-model/qref.py:33-42 (no column permutation): like `qref_rows` with a GIVEN per-row scale
+    gs [T] (not clamped, as in the reference).  Returns (codes [T, C], scale bytes [T, C/16]); a consumer reconstructs
+    E2M1(code) * dec(scale) * gs[row]."""
+    x = np.asarray(x, dtype=np.float32)
+    T, C = x.shape
+    gs = np.asarray(gs, dtype=np.float32).reshape(T)
+    xb = (x / gs[:, None]).astype(np.float32).reshape(T, C // 16, 16)
+    sbyte = e4m3_encode((np.abs(xb).max(axis=2) / FP4_MAX).astype(np.float32))
+    bs = e4m3_decode(sbyte)
+    y = (xb / np.maximum(bs, TINY)[..., None]).astype(np.float32)
+    codes = e2m1_rn_code(y)
+    zero = np.broadcast_to((sbyte == 0)[..., None], codes.shape)
+    codes = np.where(zero, np.signbit(xb).astype(np.uint8) << 3, codes).astype(np.uint8)
+    return codes.reshape(T, C), sbyte
+
+
 # ----------------------------------------------------------------------------- producer-fused emitters
 # Restatement of `rms_emit`, `swiglu_emit` and `mom_acc` of the reference's 1B trainer (llm-1b/emit.cu:97-222,
 # 343-363).  PARITY UNPINNED, like the emitters above: the reference holds no CPU implementation or fixture of these

@@ -89,6 +89,14 @@ def main():
     xr[5] = 0
     out["rowscale_x"] = bf16_bits(xr)
     out["rowscale_dq"] = torch.cat([model_ref.nvfp4_1d(xr[r:r + 1]) for r in range(xr.shape[0])]).numpy()
+    # the same with a GIVEN per-row scale (`q_rows_gs`, small-model/qref.py:33-42, without its column permutation),
+    # through the reference's own `e4m3` / `fp4_round`: here twice the row's own scale, 1.0 for the all-zero row
+    gs = xr.float().abs().amax(-1, keepdim=True) / 2688.0 * 2.0
+    gs[5] = 1.0
+    xb = (xr.float() / gs).reshape(xr.shape[0], xr.shape[1] // 16, 16)
+    bs = model_ref.e4m3(xb.abs().amax(-1, keepdim=True) / 6.0)
+    out["rowscale_gs"] = gs.reshape(-1).numpy()
+    out["rowscale_gs_dq"] = ((model_ref.fp4_round(xb / bs.clamp(min=1e-30)) * bs).reshape(xr.shape) * gs).numpy()
 
     # ---- 16x16 weight quantization (bf16 weights as in llm-1b, fp32 as in small-model)
     g = torch.Generator().manual_seed(2)

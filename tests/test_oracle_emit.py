@@ -151,3 +151,20 @@ def test_fused_producers_self_consistency():
     acc = sum(O.mom_acc(m, g, 0.5, 0.5, seed, 3).astype(np.float64) for seed in range(1, 65)) / 64
     exact = m.astype(np.float64) + 0.25 * g.astype(np.float64)
     assert np.mean(np.abs(acc - exact) / (np.abs(exact) * 2.0 ** -8)) < 0.15
+
+
+def test_qref_rows_gs_equals_the_reference_formula(golden):
+    """`qref_rows_gs` (restatement of `q_rows_gs`, small-model/qref.py:33-42) against the fixture made with the
+    reference's own `e4m3` / `fp4_round` and a given per-row scale (twice the row's own; 1.0 for the zero row)."""
+    x = O.bf16_bits_to_f32(golden["rowscale_x"])
+    gs = golden["rowscale_gs"]
+    codes, sbyte = O.qref_rows_gs(x, gs)
+    T, C = x.shape
+    deq = (O.E2M1_TABLE[codes].reshape(T, C // 16, 16) * O.e4m3_decode(sbyte)[:, :, None]).astype(np.float32).reshape(T, C)
+    deq = (deq * gs[:, None]).astype(np.float32)
+    assert np.array_equal(deq, golden["rowscale_gs_dq"])
+    # with the row's own scale it is `qref_rows`
+    c2, s2, g2 = O.qref_rows(x)
+    own = np.where(g2 > 0, g2, np.float32(1))
+    c3, s3 = O.qref_rows_gs(x, own)
+    assert np.array_equal(c2, c3) and np.array_equal(s2, s3)
