@@ -422,7 +422,9 @@ def verify_step(stack, n_micro, world, rank):
     mc = stack.micro_count
     stack.step(n_micro, do_allreduce=False)
     local = p.gw.clone()
-    local_head = stack.blocks[-1][0].gw.view(-1)[:65536].clone()
+    def ends(t):          # the first and the last 65536 values: rows the first and the last rank own
+        return torch.cat([t.view(-1)[:65536], t.view(-1)[-65536:]])
+    local_head = ends(stack.blocks[-1][0].gw).clone()
     stack.micro_count = mc
     gw = torch.empty_like(p.gw)
     for m in range(n_micro):
@@ -438,12 +440,11 @@ def verify_step(stack, n_micro, world, rank):
         stack.micro_count = mc
         stack.step(n_micro, do_allreduce=True)
         torch.cuda.synchronize()
-        sl = slice(0, 65536)
-        mine = torch.stack([local.view(-1)[sl], local_head])
+        mine = torch.stack([ends(local), local_head])
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         want = torch.stack(gathered).double().sum(0)
-        got = torch.stack([p.gw.view(-1)[sl], stack.blocks[-1][0].gw.view(-1)[:65536]]).double()
+        got = torch.stack([ends(p.gw), ends(stack.blocks[-1][0].gw)]).double()
         err = ((got - want).abs().max() / want.abs().max()).item()
         out["allreduce_max_err_over_max"] = err
         ok = ok and err <= 1e-6
@@ -651,7 +652,8 @@ def run_ours(args):
     mb, n_micro = plan["microbatch"], plan["n_micro"]
     stack = LinearStack(cfg, mb, torch.device("cuda", local), seed=0, input_seed=1000 + rank, use_graphs=not args.no_graphs,
                         comm_sms=args.comm_sms if world > 1 else 0, ar_blocks=args.ar_blocks,
-                        wgrad_side_stream=not args.no_wgrad_stream, overlap_refresh=not args.no_overlap_refresh)
+                        wgrad_side_stream=not args.no_wgrad_stream, overlap_refresh=not args.no_overlap_refresh,
+                        peer_reduce=args.peer_reduce and world > 1)
     if not args.no_graphs:
         stack.capture()
     do_ar = world > 1
@@ -713,6 +715,8 @@ def run_ours(args):
     if world > 1 and ms_ar > 0:
         comm = {"step_without_allreduce_ms": ms_noar, "comm_exposed_ms": ms - ms_noar, "allreduce_alone_ms": ms_ar,
                 "allreduce_bytes": ar_bytes, "gemm_sm_budget": args.comm_sms, "nccl_max_ctas": args.nccl_ctas,
+                "reduce": ("weight-gradient GEMM epilogues add into the owner rank's row slab through peer memory; "
+                           "NCCL barrier + in-place all-gather per block") if args.peer_reduce else "NCCL all-reduce per block",
                 "allreduce_alone_busbw_gbs": 2.0 * (world - 1) / world * ar_bytes / (ms_ar * 1e-3) / 1e9,
                 "how": "same step with the collective switched off; the block-by-block all-reduces of all gradient "
                        "buffers alone; CUDA events, max over ranks"}
@@ -921,6 +925,9 @@ def main():
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs kept out of the persistent backward grids for NCCL when N > 1 (default: 0 at N = 2, 24 at N = 4, 32 at N >= 8)")
+    ap.add_argument("--peer-reduce", action="store_true",
+                    help="N > 1: reduce-scatter inside the weight-gradient GEMM epilogues (adds into the owner rank's memory "
+                         "over NVLink) + all-gather, instead of NCCL all-reduce")
     ap.add_argument("--no-overlap-refresh", action="store_true",
                     help="re-quantize all weights at the start of a step instead of block by block behind the backward pass")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL_MAX_CTAS (default: --comm-sms, or 32 when no SMs are set aside)")

@@ -311,6 +311,24 @@ int nvfp4_gemm_reset_scheduler(void);
 int nvfp4_gemm_set_scheduler(int dynamic);
 
 /*
+ * The weight-gradient GEMM of a data-parallel rank with the gradient reduce-scatter in its epilogue (no reference
+ * counterpart: the reference's trainers are single-GPU; this replaces the reduce half of the dW all-reduce that a
+ * data-parallel wrapper around llm-1b/model.py:85 would issue).  C = A B^T is [M, N] FP32 with leading dimension
+ * ldc, laid out the same on every rank; rank r owns rows [r * M / n_owners, (r + 1) * M / n_owners) and owners[r] is
+ * the address of C in rank r's memory as this process sees it (a peer mapping; this rank's own buffer for itself).
+ * The product is ADDED into each owner's rows (FP32 reductions that commute: no ordering between ranks is needed).
+ * Protocol kept by the caller: every rank clears its owned rows, the ranks synchronise, any number of these calls
+ * run, the ranks synchronise again behind them, then each owner's rows hold the sum over ranks (an all-gather
+ * of the row slabs completes the all-reduce).  owners is a HOST array, read during the call.
+ * M % 256 == 0, (M / n_owners) % 128 == 0, 1 <= n_owners <= 8; other arguments as nvfp4_gemm (splitk 0 = library's
+ * choice).
+ */
+int nvfp4_gemm_scatter_rows(const void* a, const void* sa, long long lda, const void* b, const void* sb,
+                            long long ldb, void* const* owners, int n_owners, long long ldc, int M, int N, int K,
+                            int alpha_mode, const float* pa, const float* pb, float ka, float kb, int splitk,
+                            int* status, void* stream);
+
+/*
  * Same product for operands whose scales are in the LINEAR layout (row strides ldsa / ldsb bytes):
  * the scales are first rewritten into the swizzled layout inside `workspace`, then nvfp4_gemm runs.
  * This is the `fp4ops.gemm` contract (llm-1b/fp4ops.py:64-80: strided d and s views allowed).

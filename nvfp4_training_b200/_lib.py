@@ -44,6 +44,7 @@ SIGNATURES = {
     "nvfp4_e2m1x4_sr": (_i, [_vp, _vp, _vp, _ll, _vp]),
     "nvfp4_swizzle_scales": (_i, [_vp, _ll, _i, _i, _vp, _vp]),
     "nvfp4_gemm": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _i, _vp, _vp]),
+    "nvfp4_gemm_scatter_rows": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp, _vp]),
     "nvfp4_gemm_force_tile_n": (_i, [_i]),
     "nvfp4_gemm_set_sm_budget": (_i, [_i]),
     "nvfp4_gemm_linear_workspace_bytes": (_sz, [_i, _i, _i]),
@@ -89,6 +90,11 @@ def check(rc, what):
 
 def ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def ptr_array(addresses):
+    """A host array of `void*` for entry points that take one address per rank."""
+    return (ctypes.c_void_p * len(addresses))(*[int(a) for a in addresses])
 
 
 def seed_args(seed):

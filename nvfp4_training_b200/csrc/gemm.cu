@@ -473,6 +473,8 @@ __host__ __device__ constexpr u32 make_idesc_pair(int n) {
   return (1u << 7) | (1u << 10) | ((u32)(n >> 3) << 17) | ((u32)(256 >> 4) << 24);
 }
 
+constexpr int kMaxOwners = 8;
+
 struct PairParams {
   void* c;
   const float* pa;
@@ -488,6 +490,10 @@ struct PairParams {
   int ktiles_per_split;
   unsigned* counter;      // this launch's work counter (zero before the launch, zero again after it)
   int dynamic;            // 1: items after a cluster's first are drawn from the counter; 0: dealt out in advance (item = cluster + k * clusters)
+  // row-slab scatter (rows_per_owner > 0): rows [r * rows_per_owner, (r + 1) * rows_per_owner) of C are added into
+  // owner_c[r] (the same matrix in rank r's memory: a peer mapping, or p.c for this rank) instead of p.c
+  float* owner_c[kMaxOwners];
+  int rows_per_owner;
 };
 
 // ---- dynamic tile scheduler of the pair kernel
@@ -915,7 +921,9 @@ gemm_nvf4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       else if (p.alpha_mode == NVFP4_ALPHA_AMAX) alpha = ld_cg_f32(p.pa) * ld_cg_f32(p.pb) * p.kscale;
       else if (p.alpha_mode == NVFP4_ALPHA_ROW) alpha = ld_cg_f32(p.pa + row0 + lane) * ld_cg_f32(p.pb);   // each lane stages its own row
       const long long col0 = (long long)nt * BN + half * NC;
-      void* cbase = p.c_fp32 ? static_cast<void*>(static_cast<float*>(p.c) + row0 * p.ldc + col0)
+      // (a warp's 32 rows never straddle two owners: rows_per_owner is a multiple of 128)
+      float* cf = p.rows_per_owner ? p.owner_c[(int)row0 / p.rows_per_owner] : static_cast<float*>(p.c);
+      void* cbase = p.c_fp32 ? static_cast<void*>(cf + row0 * p.ldc + col0)
                              : static_cast<void*>(static_cast<__nv_bfloat16*>(p.c) + row0 * p.ldc + col0);
       staged_store<NC, C::kStageRowBytes>(r, alpha, sw, lane, cbase, p.ldc, p.c_fp32 != 0, p.atomic != 0,
                                           (int)min((long long)NC, (long long)p.N - col0));
@@ -1012,9 +1020,11 @@ using namespace nvfp4;
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, const void* sb, long long ldb,
-                          void* c, int c_dtype, long long ldc, int M, int N, int K, int alpha_mode, const float* pa,
-                          const float* pb, float ka, float kb, int accumulate, int splitk, int* status, void* stream) {
+// `owners` (null for the plain GEMM): n_owners base addresses of C, one per rank; see PairParams::owner_c
+static int gemm_impl(const void* a, const void* sa, long long lda, const void* b, const void* sb, long long ldb,
+                     void* c, int c_dtype, long long ldc, int M, int N, int K, int alpha_mode, const float* pa,
+                     const float* pb, float ka, float kb, int accumulate, int splitk, int* status, void* stream,
+                     void* const* owners, int n_owners, int rows_per_owner) {
   if (!a || !sa || !b || !sb || !c) return NVFP4_ERR_NULL;
   if (alpha_mode < NVFP4_ALPHA_ONE || alpha_mode > NVFP4_ALPHA_ROW) return NVFP4_ERR_ENUM;
   if (alpha_mode != NVFP4_ALPHA_ONE && (!pa || !pb)) return NVFP4_ERR_NULL;
@@ -1081,6 +1091,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   // CTA-pair kernels (an SM pair per 256-row tile): the fast path whenever M allows it
   bool use_pair = (M % 256 == 0) && g_force_bn != 128 && g_force_bn != 256;
   if (g_force_bn == 0 && (long long)(M / 256) * ((N + 255) / 256) * splitk < sms / 4) use_pair = false;   // too few tiles: finer tiles fill more SMs
+  if (owners) use_pair = true;                    // the scatter lives in the pair kernel's epilogue only
   if (use_pair) {
     // tile width: 256 moves the fewest operand bytes per FLOP but consecutive tiles wait for each other's
     // epilogue hand-off; 192 has two independent accumulators and handles any N; 128 as well, more bytes
@@ -1108,6 +1119,8 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
     pp.atomic = (accumulate || splitk > 1) ? 1 : 0;
     pp.splitk = splitk;
     pp.ktiles_per_split = per;
+    pp.rows_per_owner = owners ? rows_per_owner : 0;
+    for (int r = 0; r < kMaxOwners; r++) pp.owner_c[r] = (owners && r < n_owners) ? static_cast<float*>(owners[r]) : nullptr;
     // a counter of its own for every launch in flight: consecutive launches take consecutive slots, a slot comes
     // round again 4096 launches later
     static std::atomic<unsigned> launch_seq{0};
@@ -1155,6 +1168,33 @@ extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const vo
   p.ktiles_per_split = per;
   if (wide) return launch_gemm<256>(ma, mb, p, sms, di->attr256, st);
   return launch_gemm<128>(ma, mb, p, sms, di->attr128, st);
+}
+
+extern "C" int nvfp4_gemm(const void* a, const void* sa, long long lda, const void* b, const void* sb, long long ldb,
+                          void* c, int c_dtype, long long ldc, int M, int N, int K, int alpha_mode, const float* pa,
+                          const float* pb, float ka, float kb, int accumulate, int splitk, int* status, void* stream) {
+  return gemm_impl(a, sa, lda, b, sb, ldb, c, c_dtype, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, accumulate, splitk,
+                   status, stream, nullptr, 0, 0);
+}
+
+// The weight-gradient GEMM of a data-parallel rank with the reduce-scatter in its epilogue: C is [M, N] FP32 with the
+// same layout on every rank, rank r owns rows [r * M / n_owners, (r + 1) * M / n_owners), and this rank's product is
+// ADDED (red.global.add.v4.f32, through the peer mapping for r != this rank) into each owner's rows.  The caller has
+// cleared the owned rows on every rank and synchronised the ranks before the first launch of a step, and synchronises
+// them again (after this stream's work) before an owner reads its rows.
+extern "C" int nvfp4_gemm_scatter_rows(const void* a, const void* sa, long long lda, const void* b, const void* sb,
+                                       long long ldb, void* const* owners, int n_owners, long long ldc, int M, int N,
+                                       int K, int alpha_mode, const float* pa, const float* pb, float ka, float kb,
+                                       int splitk, int* status, void* stream) {
+  if (!owners) return NVFP4_ERR_NULL;
+  if (n_owners < 1 || n_owners > kMaxOwners || M <= 0 || (M % 256) || (M % n_owners) || ((M / n_owners) % 128))
+    return NVFP4_ERR_SHAPE;
+  for (int r = 0; r < n_owners; r++) {
+    if (!owners[r]) return NVFP4_ERR_NULL;
+    if (!al16(owners[r])) return NVFP4_ERR_ALIGN;
+  }
+  return gemm_impl(a, sa, lda, b, sb, ldb, owners[0], NVFP4_DTYPE_FP32, ldc, M, N, K, alpha_mode, pa, pb, ka, kb, 1,
+                   splitk, status, stream, owners, n_owners, M / n_owners);
 }
 
 extern "C" size_t nvfp4_gemm_linear_workspace_bytes(int M, int N, int K) {

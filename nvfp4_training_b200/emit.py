@@ -164,10 +164,17 @@ def mm(ad, as_, bd, bs, out_dtype=torch.bfloat16):
     return nvq.mm(a, b, out_dtype=out_dtype, scale=False)[0]
 
 
-def _gemm(ad, as_, bd, bs, out, alpha_mode, pa, pb, accumulate=False, splitk=1):
+def _gemm(ad, as_, bd, bs, out, alpha_mode, pa, pb, accumulate=False, splitk=1, owners=None):
     M, N, K = ad.shape[0], bd.shape[0], ad.shape[1] * 2
     assert bd.shape[1] * 2 == K and out.shape == (M, N) and out.stride(1) == 1
     L.require_cuda(ad, bd, out)
+    if owners is not None:       # add into the row slab every rank owns (nvq.mm's `owners`)
+        assert out.dtype == torch.float32
+        L.check(L.load().nvfp4_gemm_scatter_rows(L.ptr(ad), L.ptr(as_), ad.stride(0), L.ptr(bd), L.ptr(bs), bd.stride(0),
+                                                 L.ptr_array(owners), len(owners), out.stride(0), M, N, K, alpha_mode,
+                                                 L.ptr(pa), L.ptr(pb), 1.0, 1.0, splitk,
+                                                 L.ptr(L.status_word(ad.device)), L.stream()), "gemm (scatter)")
+        return out
     L.check(L.load().nvfp4_gemm(L.ptr(ad), L.ptr(as_), ad.stride(0), L.ptr(bd), L.ptr(bs), bd.stride(0), L.ptr(out),
                                 L.DTYPE_FP32 if out.dtype == torch.float32 else L.DTYPE_BF16, out.stride(0), M, N, K,
                                 alpha_mode, L.ptr(pa), L.ptr(pb), 1.0, 1.0, int(accumulate), splitk,
@@ -186,7 +193,8 @@ def dequant(d, s, rs):
     return nvq.dequant(nvq.Q(d.view(F4), s.view(F8), _one(d.device))) * rs[:, None]
 
 
-def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32, scale=False, amax_a=None, amax_b=None, out=None, accumulate=False):
+def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32, scale=False, amax_a=None, amax_b=None, out=None, accumulate=False,
+           owners=None):
     """wgrad: dW_raw = Q(H dy)^T Q(H x) [N, K]; true = raw * gsA * gsB with gs = amax_use/2688
     (llm-1b/emit.py:148-150).  scale=True: the two delayed amax words (device fp32 [1]) are given and
     the product by gsA * gsB happens in the epilogue; `out` / `accumulate`: in-place FP32 accumulation."""
@@ -195,7 +203,7 @@ def mm_col(a: ColQ, b: ColQ, out_dtype=torch.float32, scale=False, amax_a=None, 
     if out is None:
         out = torch.empty(a.d.shape[0], b.d.shape[0], dtype=out_dtype, device=a.d.device)
     return _gemm(a.d, a.s, b.d, b.s, out, L.ALPHA_AMAX, amax_a, amax_b, accumulate,
-                 splitk=0 if out.dtype == torch.float32 else 1)
+                 splitk=0 if out.dtype == torch.float32 else 1, owners=owners)
 
 
 def mm_row_w(q: RowQ, w: WQ, scale=False):

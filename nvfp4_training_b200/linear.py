@@ -65,7 +65,8 @@ def linear_fwd(x, qw, keep_xt=False, signs=_RHT_SIGNS, am_out=None):
 
 
 def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch.float32, signs=_RHT_SIGNS,
-               sr_mode=None, overwrite=False, qxt=None, am_gy=None, wgrad_stream=None, keep_alive=None, am_out=None):
+               sr_mode=None, overwrite=False, qxt=None, am_gy=None, wgrad_stream=None, keep_alive=None, am_out=None,
+               gw_owners=None):
     """dgrad + wgrad of llm-1b/model.py:55-69.  `seed` / `seed_cols` are ints or CUDA int32 words
     (the reference uses seed and seed ^ 0x5bd1e995).  With `gw_out` (fp32 [N, K]) the weight
     gradient is accumulated into it in place -- gradient accumulation over microbatches -- and
@@ -76,7 +77,10 @@ def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch
     `wgrad_stream`: the weight-gradient GEMM is off the backward's critical chain (nothing downstream reads dW before
     the optimizer), so it may run on this side stream beside the dgrad GEMM and whatever follows it: its CTAs fill
     the SMs the other kernels' last waves leave idle.  The caller joins the stream before it reads `gw_out` and
-    passes a list as `keep_alive`, which receives the operands the side stream still reads (drop them after the join)."""
+    passes a list as `keep_alive`, which receives the operands the side stream still reads (drop them after the join).
+    `gw_owners`: data-parallel reduce-scatter in the weight-gradient GEMM's epilogue: the addresses of `gw_out` on every
+    rank; the product is added into the row slab each rank owns (`nvq.mm(owners=)`; `overwrite` is then ignored: the
+    caller clears the slabs once per step)."""
     gy = gy.contiguous()
     ag = am_gy if am_gy is not None else (nvq.amax(gy) if am_out is None else nvq.amax(gy, out=am_out, clear=False))
     if _tileable(gy):
@@ -98,10 +102,10 @@ def linear_bwd(x, am_x, gy, qwt, seed, seed_cols, gw_out=None, wgrad_dtype=torch
         qxt = nvq.quant_cols_rht(x, signs, am=am_x)
     if side is not None:
         with torch.cuda.stream(side):
-            gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0)
+            gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0, owners=gw_owners)
         keep_alive.append((qgt, qxt))
     elif gw_out is not None:
-        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0)
+        gw = nvq.mm(qgt, qxt, out_dtype=torch.float32, out=gw_out, accumulate=not overwrite, splitk=0, owners=gw_owners)
     else:
         gw = nvq.mm(qgt, qxt, out_dtype=wgrad_dtype)
     return gx, gw

@@ -165,19 +165,30 @@ def quant_w2d(w, am=None, want=(True, True), out=None):
     return (Q(q, s, g) if want[0] else None, Q(qt, st, g) if want[1] else None)
 
 
-def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False, splitk=1):
+def mm(a: Q, b: Q, out_dtype=torch.bfloat16, scale=True, out=None, accumulate=False, splitk=1, owners=None):
     """a [M,K], b [N,K] (both K-major) -> a @ b^T [M, N].  If scale=False returns (raw, alpha)
     (llm-1b/nvq.py:90-96).  `out` / `accumulate` (fp32 only) are additions for in-place wgrad; `splitk=0` (fp32 only)
-    lets the library slice a long contraction over the SMs (sums then land in no fixed order)."""
+    lets the library slice a long contraction over the SMs (sums then land in no fixed order).
+    `owners` (fp32 `out` only): the addresses of `out` on every data-parallel rank (peer mappings; this rank's own
+    `out.data_ptr()` at its index); the product is then added into the row slab each rank owns instead of into `out`
+    (`nvfp4_gemm_scatter_rows`)."""
     M, N, K = a.d.shape[0], b.d.shape[0], a.d.shape[1] * 2
     assert b.d.shape[1] * 2 == K, (a.d.shape, b.d.shape)
     assert out_dtype in (torch.bfloat16, torch.float32)
     L.require_cuda(a.d, b.d)
     if out is None:
-        assert not accumulate
+        assert not accumulate and owners is None
         out = torch.empty(M, N, dtype=out_dtype, device=a.d.device)
     else:
         assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
+    if owners is not None:
+        assert out_dtype == torch.float32
+        L.check(L.load().nvfp4_gemm_scatter_rows(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), L.ptr(b.d), L.ptr(b.s), b.d.stride(0),
+                                                 L.ptr_array(owners), len(owners), out.stride(0), M, N, K,
+                                                 L.ALPHA_GS if scale else L.ALPHA_ONE, L.ptr(a.gs) if scale else None,
+                                                 L.ptr(b.gs) if scale else None, 1.0, 1.0, splitk,
+                                                 L.ptr(L.status_word(a.d.device)), L.stream()), "mm (scatter)")
+        return out
     L.check(L.load().nvfp4_gemm(L.ptr(a.d), L.ptr(a.s), a.d.stride(0), L.ptr(b.d), L.ptr(b.s), b.d.stride(0),
                                 L.ptr(out), L.DTYPE_FP32 if out_dtype == torch.float32 else L.DTYPE_BF16,
                                 out.stride(0), M, N, K, L.ALPHA_GS if scale else L.ALPHA_ONE,

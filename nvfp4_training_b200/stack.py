@@ -78,7 +78,7 @@ def allreduce_sum_(tensors, group=None):
 
 
 class _Proj:
-    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx", "qxt", "wq", "cx")
+    __slots__ = ("name", "N", "K", "w", "q", "qt", "gw", "lid", "am_x", "y", "gx", "qxt", "wq", "cx", "owners")
 
 
 def student_t(shape, gen, device, df=3):
@@ -89,16 +89,22 @@ def student_t(shape, gen, device, df=3):
 
 class LinearStack:
     def __init__(self, cfg: StackConfig, microbatch: int, device, seed=0, use_graphs=True, group=None,
-                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor", wgrad_side_stream=True, overlap_refresh=True):
+                 sr_mode=_lib.ROUND_SR_HW, comm_sms=0, ar_blocks=1, input_seed=None, mode="tensor", wgrad_side_stream=True, overlap_refresh=True,
+                 peer_reduce=False):
         """`seed` initialises the weights (the same on every rank of a data-parallel job: replicated
         weights), `input_seed` the synthetic activation / gradient pools (different per rank: each rank
         holds its own rows of the batch; default seed + 1000).
         `mode`: "tensor" = the per-tensor-scale contract of llm-1b/model.py (amax pass + one-read quantizer);
         "emit" = the operand emitters of the reference's trainer (llm-1b/model2.py:430-480): row operands with exact
         per-row scales, column operands with delayed per-tensor scales, no amax pass, `rs[row] * gs` applied in the
-        GEMM epilogue."""
+        GEMM epilogue.
+        `peer_reduce` (NCCL jobs on one NVLink domain): the reduce half of the gradient all-reduce moves into the
+        weight-gradient GEMMs: every rank owns a row slab of each dW, the GEMM epilogues add their tiles straight into
+        the owners' memory (symmetric memory, `nvfp4_gemm_scatter_rows`), and what is left for the collective library
+        is one barrier and an in-place all-gather of the slabs per block."""
         assert mode in ("tensor", "emit")
         self.mode = mode
+        self.peer_reduce = bool(peer_reduce)
         # a block's weights are re-quantized on the side stream right after the block's gradients are reduced (where
         # a trainer would apply the block's optimizer update first), under the rest of the backward pass, instead of
         # all weights at the start of the next step
@@ -141,9 +147,18 @@ class LinearStack:
         groups = [list(range(b, min(b + self.ar_blocks, nb))) for b in range(0, nb, self.ar_blocks)]
         if cfg.lm_head:
             groups.append([nb])
+        arena, arena_off = None, 0
+        if self.peer_reduce:
+            arena = self._peer_arena(sum(p.N * p.K for projs in self.blocks for p in projs))
         for grp in groups:
             projs = [p for b in grp for p in self.blocks[b]]
-            flat = torch.zeros(sum(p.N * p.K for p in projs), dtype=torch.float32, device=self.device)
+            n_flat = sum(p.N * p.K for p in projs)
+            if arena is None:
+                flat = torch.zeros(n_flat, dtype=torch.float32, device=self.device)
+            else:
+                flat = arena[arena_off:arena_off + n_flat]
+                self._peer_views(projs, arena_off)
+                arena_off += n_flat
             off = 0
             for p in projs:
                 p.gw = flat[off:off + p.N * p.K].view(p.N, p.K)
@@ -168,7 +183,7 @@ class LinearStack:
         self.micro_count = 0
         self._bump_seeds()
         self.comm_stream = torch.cuda.Stream(device=self.device)
-        self.graphs_fwd = self.graphs_bwd = None
+        self.graphs_fwd = self.graphs_bwd = self.graphs_bwd_scatter = None
         self.graph_refresh = None
         self.launches_per_micro = 0
 
@@ -179,8 +194,64 @@ class LinearStack:
         torch.nn.init.trunc_normal_(w, std=std, a=-3 * std, b=3 * std, generator=gen)
         p.w = w.bfloat16()
         p.gw = None      # a view of the block's flat gradient buffer, set by the constructor
-        p.q = p.qt = p.am_x = p.y = p.gx = p.qxt = p.wq = p.cx = None
+        p.q = p.qt = p.am_x = p.y = p.gx = p.qxt = p.wq = p.cx = p.owners = None
         return p
+
+    # ------------------------------------------------------------------ gradients reduced through peer memory
+    def _peer_arena(self, n_floats):
+        """One FP32 buffer for all weight gradients, at the same offsets on every rank, mapped into every rank's
+        address space."""
+        import os
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer stores only: no multicast binding
+        import torch.distributed._symmetric_memory as symm
+        assert dist.is_initialized() and dist.get_backend(self.group) == "nccl" and self.ar_blocks == 1
+        grp = self.group if self.group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(grp), dist.get_rank(grp)
+        assert 1 <= self.world <= 8
+        arena = symm.empty(n_floats, dtype=torch.float32, device=self.device)
+        self._peer_handle = symm.rendezvous(arena, grp)
+        self._peer_base = [int(self._peer_handle.buffer_ptrs[r]) for r in range(self.world)]
+        assert self._peer_base[self.rank] == arena.data_ptr()
+        arena.zero_()
+        self._bar_word = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._peer_ready = None
+        return arena
+
+    def _peer_views(self, projs, first_float):
+        off = first_float
+        for p in projs:
+            assert p.N % 256 == 0 and (p.N // self.world) % 128 == 0, (p.name, p.N, self.world)
+            p.owners = [base + 4 * off for base in self._peer_base]
+            off += p.N * p.K
+
+    def _slab(self, p):
+        n = p.N // self.world
+        return p.gw[self.rank * n:(self.rank + 1) * n]
+
+    def _peer_barrier(self):
+        torch.distributed.all_reduce(self._bar_word, group=self.group)
+
+    def _peer_begin_step(self):
+        """On the side stream, beside the forward pass: once every rank is past the previous step, clear the slabs
+        this rank owns, and let no rank start adding before all slabs are clear."""
+        cur = torch.cuda.current_stream()
+        self.comm_stream.wait_stream(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self._peer_barrier()
+            for projs in self.blocks:
+                for p in projs:
+                    self._slab(p).zero_()
+            self._peer_barrier()
+            self._peer_ready = torch.cuda.Event()
+            self._peer_ready.record()
+
+    def _peer_finish_block(self, projs):
+        """On the side stream, behind the block's last weight-gradient GEMM of this rank: once every rank is there,
+        all contributions have landed in the owners' slabs; the in-place all-gather hands every rank all slabs."""
+        self._peer_barrier()
+        for p in projs:
+            torch.distributed.all_gather_into_tensor(p.gw.view(-1), self._slab(p).reshape(-1), group=self.group)
 
     # ------------------------------------------------------------------ per-step pieces
     def _bump_seeds(self):
@@ -234,7 +305,7 @@ class LinearStack:
             y = emit.mm_row_w(rq, p.wq, scale=True)
             p.y = y if keep else None
 
-    def _bwd_block_emit(self, projs, keep=False, first=False):
+    def _bwd_block_emit(self, projs, keep=False, first=False, scatter=False):
         T = self.T
         alive = []          # operands the side stream still reads
         for p in reversed(projs):
@@ -246,11 +317,13 @@ class LinearStack:
             if self.wgrad_stream is not None:
                 self.wgrad_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(self.wgrad_stream):
-                    emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
+                    emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first,
+                                owners=p.owners if scatter else None)
                 alive.append(cg)
             gx = emit.mm_row_wt(rq, p.wq, scale=True)
             if self.wgrad_stream is None:
-                emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first)
+                emit.mm_col(cg, p.cx, scale=True, amax_a=use_g, amax_b=use_x, out=p.gw, accumulate=not first,
+                            owners=p.owners if scatter else None)
             p.gx = gx if keep else None
         if self.wgrad_stream is not None:
             torch.cuda.current_stream().wait_stream(self.wgrad_stream)
@@ -268,11 +341,12 @@ class LinearStack:
                                           am_out=self.am_words[0, p.lid:p.lid + 1])
             p.y = y if keep else None
 
-    def _bwd_block(self, projs, keep=False, first=False):
+    def _bwd_block(self, projs, keep=False, first=False, scatter=False):
         """`first`: the step's first microbatch overwrites dW instead of adding to it, so the
-        gradients need no clearing pass."""
+        gradients need no clearing pass.  `scatter` (`peer_reduce` stacks): the weight gradients are added into the
+        owner ranks' slabs instead of this rank's buffer."""
         if self.mode == "emit":
-            return self._bwd_block_emit(projs, keep, first)
+            return self._bwd_block_emit(projs, keep, first, scatter)
         alive = []
         lo, hi = projs[0].lid, projs[-1].lid + 1
         self.am_words[1, lo:hi].zero_()
@@ -280,7 +354,8 @@ class LinearStack:
             sd = self.seeds[p.lid]
             gx, _ = linear_bwd(None, p.am_x, self.gy_pool[p.name], p.qt, sd[0:1], sd[1:2],
                                gw_out=p.gw, signs=_RHT_SIGNS, sr_mode=self.sr_mode, overwrite=first, qxt=p.qxt,
-                               wgrad_stream=self.wgrad_stream, keep_alive=alive, am_out=self.am_words[1, p.lid:p.lid + 1])
+                               wgrad_stream=self.wgrad_stream, keep_alive=alive, am_out=self.am_words[1, p.lid:p.lid + 1],
+                               gw_owners=p.owners if scatter else None)
             p.gx = gx if keep else None
         if self.wgrad_stream is not None:
             torch.cuda.current_stream().wait_stream(self.wgrad_stream)
@@ -337,6 +412,13 @@ class LinearStack:
                     with torch.cuda.graph(g, pool=pool):
                         self._bwd_block(projs, first=first)
                     store.append(g)
+            if self.peer_reduce:
+                self.graphs_bwd_scatter = []
+                for projs in reversed(self.blocks):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool):
+                        self._bwd_block(projs, scatter=True)
+                    self.graphs_bwd_scatter.append(g)
         finally:
             lib.nvfp4_gemm_set_sm_budget(0)
             lib.nvfp4_gemm_set_scheduler(1)
@@ -372,11 +454,14 @@ class LinearStack:
                 self._fwd_block(projs)
         works = []
         nblk = len(self.blocks)
+        scatter = self.peer_reduce and do_allreduce       # every microbatch of the step adds into the owners' slabs
+        if scatter and first:
+            cur.wait_event(self._peer_ready)              # all slabs are clear
         for i, projs in enumerate(reversed(self.blocks)):
             if self.use_graphs and self.graphs_bwd is not None:
-                (self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
+                (self.graphs_bwd_scatter if scatter else self.graphs_bwd_first if first else self.graphs_bwd)[i].replay()
             else:
-                self._bwd_block(projs, first=first)
+                self._bwd_block(projs, first=first, scatter=scatter)
             b = nblk - 1 - i
             reduce_now = last and do_allreduce and b in self.ar_after
             if reduce_now or (last and (self.overlap_refresh or self.after_reduce is not None)):
@@ -384,7 +469,9 @@ class LinearStack:
                 ev.record(cur)
                 with torch.cuda.stream(self.comm_stream):
                     self.comm_stream.wait_event(ev)
-                    if reduce_now:
+                    if reduce_now and self.peer_reduce:
+                        self._peer_finish_block(projs)
+                    elif reduce_now:
                         allreduce_sum_([self.ar_after[b]], self.group)
                     if self.after_reduce is not None:
                         self.after_reduce(b, projs)
@@ -407,6 +494,8 @@ class LinearStack:
             self.calibrate()
         if not (self.overlap_refresh and self._weights_fresh):
             self.refresh_weights()           # otherwise the previous step re-quantized each block behind its backward
+        if self.peer_reduce and do_allreduce:
+            self._peer_begin_step()
         for m in range(n_micro):
             if before_microbatch is not None:
                 before_microbatch(m)

@@ -211,3 +211,52 @@ def test_gemm_rejects_bad_arguments(mods):
     assert lib.nvfp4_gemm(*args(a=None)) == -1
     assert lib.nvfp4_gemm(*args(cd=0, acc=1)) == -4
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("M,N,K,owners,splitk", [(1024, 512, 4096, 4, 1), (512, 384, 2048, 2, 1), (2048, 256, 8192, 8, 0),
+                                                  (256, 256, 1024, 1, 1)])
+def test_scatter_rows_adds_each_row_slab_into_its_owner(mods, M, N, K, owners, splitk):
+    """The weight-gradient GEMM with the reduce-scatter in its epilogue, on one GPU: every "rank's" copy of C is a
+    buffer of its own here.  Owner r receives product + what it held in rows [r M / n, (r + 1) M / n) and nothing
+    anywhere else; with one K slice the sums are bit-equal to the accumulating GEMM's."""
+    nvq, _, L = mods
+    qa = nvq.quant_rows(to_dev(make_x(M + 1, M, K)))
+    qb = nvq.quant_rows(to_dev(make_w(N + 2, N, K)))
+    want = torch.full((M, N), 0.5, device="cuda")
+    nvq.mm(qa, qb, out_dtype=torch.float32, out=want, accumulate=True, splitk=1)
+    bufs = [torch.full((M, N), 0.5, device="cuda") for _ in range(owners)]
+    nvq.mm(qa, qb, out_dtype=torch.float32, out=bufs[0], splitk=splitk, owners=[b.data_ptr() for b in bufs])
+    torch.cuda.synchronize()
+    L.check_status()
+    rows = M // owners
+    for r, b in enumerate(bufs):
+        mine = slice(r * rows, (r + 1) * rows)
+        if splitk == 1:
+            assert torch.equal(b[mine], want[mine]), r
+        else:
+            check_close(b[mine], want[mine].double().cpu().numpy(), bf16=False)
+        rest = torch.cat([b[:r * rows], b[(r + 1) * rows:]])
+        assert bool((rest == 0.5).all()), r
+
+
+def test_scatter_rows_rejects_bad_requests(mods):
+    nvq, _, L = mods
+    lib = L.load()
+    M, N, K = 768, 256, 1024
+    qa = nvq.quant_rows(to_dev(make_x(1, M, K)))
+    qb = nvq.quant_rows(to_dev(make_w(2, N, K)))
+    out = torch.zeros(M, N, device="cuda")
+
+    def call(ptrs, m=M):
+        return lib.nvfp4_gemm_scatter_rows(L.ptr(qa.d), L.ptr(qa.s), qa.d.stride(0), L.ptr(qb.d), L.ptr(qb.s), qb.d.stride(0),
+                                           L.ptr_array(ptrs) if ptrs is not None else None, len(ptrs or []), N, m, N, K,
+                                           L.ALPHA_GS, L.ptr(qa.gs), L.ptr(qb.gs), 1.0, 1.0, 1, None, L.stream())
+    p = out.data_ptr()
+    assert call(None) == -1                      # null
+    assert call([p] * 4) == -2                   # shape: 768 / 4 = 192 rows per owner are not whole 128-row tiles
+    assert call([p] * 9) == -2
+    assert call([p, 0, p]) == -1
+    assert call([p, p + 4, p]) == -3              # alignment
+    assert call([p] * 3) == 0                    # 256 rows each
+    torch.cuda.synchronize()
+    L.check_status()
