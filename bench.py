@@ -644,7 +644,10 @@ def run_ours(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # the collective's kernels go to a high-priority stream: when SMs come free between two kernels of the backward
+        # pass, the collective's CTAs are placed first, so an exchange starts as soon as its block is done
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=not args.nccl_normal_priority)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
     peaks, peak_src = load_peaks()
 
     cfg = StackConfig(layers=args.layers) if args.layers else StackConfig()
@@ -703,7 +706,7 @@ def run_ours(args):
     # ---- where a data-parallel step's time goes (N > 1), and the self-check of the results
     ms_noar = ms_ar = 0.0
     ar_bytes = 0
-    if world > 1 and not args.skip_isolated:
+    if world > 1 and (args.comm_breakdown or not args.skip_isolated):
         ms_noar, ms_ar, ar_bytes = comm_breakdown(stack, n_micro, max(2, min(args.steps, 5)))
     verify = None if args.no_verify else verify_step(stack, n_micro, world, rank)
 
@@ -925,6 +928,9 @@ def main():
     ap.add_argument("--ar-blocks", type=int, default=1, help="transformer blocks per gradient all-reduce")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="SMs kept out of the persistent backward grids for NCCL when N > 1 (default: 0 at N = 2, 24 at N = 4, 32 at N >= 8)")
+    ap.add_argument("--nccl-normal-priority", action="store_true", help="N > 1: NCCL's stream at normal instead of high priority")
+    ap.add_argument("--comm-breakdown", action="store_true",
+                    help="N > 1: time the step without the exchange and the exchange alone even with --skip-isolated")
     ap.add_argument("--peer-reduce", action="store_true",
                     help="N > 1: reduce-scatter inside the weight-gradient GEMM epilogues (adds into the owner rank's memory "
                          "over NVLink) + all-gather, instead of NCCL all-reduce")

@@ -183,6 +183,10 @@ class LinearStack:
         self.micro_count = 0
         self._bump_seeds()
         self.comm_stream = torch.cuda.Stream(device=self.device)
+        # a block's optimizer hook and weight re-quantization run on a stream of their own, behind the block's
+        # collective: on the collective's stream they would sit between two blocks' exchanges and keep the links
+        # idle meanwhile (with 8 ranks the exchanges fill most of the backward pass)
+        self.refresh_stream = torch.cuda.Stream(device=self.device)
         self.graphs_fwd = self.graphs_bwd = self.graphs_bwd_scatter = None
         self.graph_refresh = None
         self.launches_per_micro = 0
@@ -467,12 +471,17 @@ class LinearStack:
             if reduce_now or (last and (self.overlap_refresh or self.after_reduce is not None)):
                 ev = torch.cuda.Event()
                 ev.record(cur)
-                with torch.cuda.stream(self.comm_stream):
-                    self.comm_stream.wait_event(ev)
-                    if reduce_now and self.peer_reduce:
-                        self._peer_finish_block(projs)
-                    elif reduce_now:
-                        allreduce_sum_([self.ar_after[b]], self.group)
+                if reduce_now:
+                    with torch.cuda.stream(self.comm_stream):
+                        self.comm_stream.wait_event(ev)
+                        if self.peer_reduce:
+                            self._peer_finish_block(projs)
+                        else:
+                            allreduce_sum_([self.ar_after[b]], self.group)
+                        ev = torch.cuda.Event()
+                        ev.record()
+                with torch.cuda.stream(self.refresh_stream):
+                    self.refresh_stream.wait_event(ev)
                     if self.after_reduce is not None:
                         self.after_reduce(b, projs)
                     if self.overlap_refresh:
@@ -502,3 +511,4 @@ class LinearStack:
             self.microbatch(last=(m == n_micro - 1), do_allreduce=do_allreduce, first=(m == 0))
         if do_allreduce or self.overlap_refresh or self.after_reduce is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+            torch.cuda.current_stream().wait_stream(self.refresh_stream)
