@@ -637,7 +637,7 @@ def run_ours(args):
         # and no budget wins (75.2-77.1 ms per step against 77.2-79.7 with 16 SMs set aside, same boxes); with 4 ranks
         # it is in flight half the time and a budget wins again (42.4 ms with 24 SMs, 42.7 with 32, 44.1 without: the
         # quantizer's CTAs own fixed shares of tiles and suffer from starting late); with 8 ranks it is in flight
-        # almost all the time and the budget measured best earlier (32 SMs) is kept.
+        # almost all the time: 32 SMs (27.98 ms; 27.85 with 24, 28.28 with none, 30.81 with 16 SMs and 16 CTAs).
         args.comm_sms = 0 if world <= 2 else 24 if world < 8 else 32
     if not args.nccl_ctas:
         args.nccl_ctas = args.comm_sms if args.comm_sms > 0 else 32      # NCCL stays inside the SMs set aside for it
