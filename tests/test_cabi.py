@@ -53,6 +53,16 @@ def test_argument_validation_needs_no_device(lib):
     assert lib.nvfp4_gemm(p, p, 64, p, p, 64, p, 1, 128, 128, 128, 100, 0, None, None, 1.0, 1.0, 0, 1, None, None) == -2
     assert lib.nvfp4_gemm_linear(p, p, 64, 8, p, p, 64, 8, p, 1, 128, 128, 128, 128, 0, None, None, 1.0, 1.0, 0, 1,
                                  None, 0, None, None) == -6
+    # weight-gradient GEMM that adds row slabs into their owners: one address per rank, whole 128-row tiles per owner
+    own = lambda *a: (ctypes.c_void_p * len(a))(*a)
+    sc = lambda arr, n, M: lib.nvfp4_gemm_scatter_rows(p, p, 64, p, p, 64, arr, n, 128, M, 128, 128, 0, None, None, 1.0, 1.0, 1,
+                                                       None, None)
+    assert sc(None, 2, 512) == -1
+    assert sc(own(1 << 20, 1 << 21), 2, 384) == -2            # M % 256
+    assert sc(own(1 << 20, 1 << 21, 1 << 22, 1 << 23), 4, 768) == -2          # 192 rows per owner
+    assert sc(own(*[1 << 20] * 9), 9, 2304) == -2              # more than 8 owners
+    assert sc(own(1 << 20, None), 2, 512) == -1
+    assert sc(own(1 << 20, (1 << 21) + 8), 2, 512) == -3
     # tile quantizer and operand emitters
     assert lib.nvfp4_quant_tile(p, 128, 128, 128, None, None, None, None, 0, p, None, None, 0, 0, 0, 0, None, None, None) == -1
     assert lib.nvfp4_quant_tile(p, 128, 100, 128, p, p, p, p, 0, p, None, None, 0, 0, 0, 0, None, None, None) == -2
